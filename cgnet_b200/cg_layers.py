@@ -1,0 +1,461 @@
+"""The Clebsch-Gordan layer modules, API-compatible with the reference's ``CGNet/CG_layers.py``:
+
+    CGBN_cuda            CG product -> fragment norm -> per-degree complex channel mixing   (CG_layers.py:289-318)
+    CG_woFilter_cuda     the CG product alone                                               (CG_layers.py:205-286)
+    MyBatchNormWeightMM_cuda   fragment norm + mixing on a materialised product             (CG_layers.py:74-132)
+    precomputeCG         cached CG band table for a degree cut-off                          (CG_layers.py:153-165)
+
+Constructor arguments, attribute names, parameter names/shapes (``W``, ``bn_stds``, ``bn_eps``) and the
+list-or-flat calling convention are the reference's, so a model written against it runs unchanged and its
+checkpoints load.  All arithmetic happens in libcgnet_b200.so (hand-written sm_100a kernels behind a C ABI); torch
+supplies device memory, the current stream and autograd bookkeeping only.  There is no CPU path: tensors must live on
+a CUDA device.
+
+Differences from the reference, all additive:
+  * ``CGBN_cuda`` runs the whole layer through fused kernels that never write the quadratic mid activation to memory
+    (``fused=False`` selects the two-pass route through ``self.cg`` and ``self.bnWMM``);
+  * ``device`` is honoured everywhere (the reference hard-codes ``'cuda'`` in places);
+  * ``bn_cnt`` is also kept in a buffer so that it survives ``state_dict`` round trips (reference: a Python float that
+    a resume silently resets, ``CG_layers.py:92``); checkpoints without it still load;
+  * ``depthwise=True`` (channel-wise product, tau_l1 == tau_l2 required) is an extension with no reference counterpart;
+  * gradients of ``W`` are summed in a fixed order (the reference accumulates them with ``atomicAdd``).
+"""
+import functools
+import weakref
+
+import numpy as np
+import torch
+from torch import nn
+
+from . import _lib
+from . import cgutils as CGutils
+
+__all__ = ["CGBN_cuda", "CG_woFilter_cuda", "MyBatchNormWeightMM_cuda", "precomputeCG", "Plan", "get_plan"]
+
+
+def _stream_ptr(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check_cuda_f32(t, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (cgnet_b200 has no CPU path)")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32, got {t.dtype}")
+    return t.contiguous()
+
+
+class Plan:
+    """Owner of one ``cgb200_plan`` handle: index tables, CG table and work lists for a fixed
+    (lmax, tau_in, tau_out, triple list) on one device."""
+
+    def __init__(self, lmax, taus, tau_out, llls, device, depthwise=False):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("cgnet_b200 plans live on a CUDA device")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.lmax = int(lmax)
+        if self.lmax > lib.cgb200_max_lmax():
+            raise AssertionError(f"Does not support lmax={lmax}")
+        handle = _lib.vp()
+        a_in = _lib.i32(taus)
+        a_out = _lib.i32(tau_out) if tau_out is not None else None
+        a_l = _lib.i32(llls)
+        with torch.cuda.device(self.device):
+            _lib.check(lib.cgb200_plan_create(handle, self.lmax, a_in, a_out, a_l, len(llls),
+                                              _lib.PLAN_DEPTHWISE if depthwise else 0), "cgb200_plan_create")
+        self.handle = handle
+        self._finalizer = weakref.finalize(self, lib.cgb200_plan_destroy, handle)
+        self.n_F = self.query(_lib.Q_N_F)
+        self.n_FF = self.query(_lib.Q_N_FF)
+        self.n_O = self.query(_lib.Q_N_O)
+        self.w_len = self.query(_lib.Q_W_LEN)
+        self.sum_tff = self.query(_lib.Q_SUM_TFF)
+        self.tile = self.query(_lib.Q_TILE)
+
+    def query(self, what):
+        v = _lib.ctypes.c_int64()
+        _lib.check(_lib.load().cgb200_plan_query(self.handle, what, v), "cgb200_plan_query")
+        return int(v.value)
+
+    def t_ff(self):
+        out = (_lib.ctypes.c_int32 * (self.lmax + 1))()
+        _lib.check(_lib.load().cgb200_plan_t_ff(self.handle, out), "cgb200_plan_t_ff")
+        return list(out)
+
+    # ---- thin wrappers over the C ABI; every tensor must already be contiguous float32 on self.device ----
+    def cg_product_fwd(self, F):
+        B = F.shape[0]
+        FF = torch.empty(B, self.n_FF, 2, device=F.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_cg_product_fwd(self.handle, _ptr(F), _ptr(FF), B, _stream_ptr(self.device)),
+                       "cgb200_cg_product_fwd")
+        return FF
+
+    def cg_product_bwd(self, F, gFF):
+        gF = torch.empty_like(F)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_cg_product_bwd(self.handle, _ptr(F), _ptr(gFF), _ptr(gF), F.shape[0],
+                                                         _stream_ptr(self.device)), "cgb200_cg_product_bwd")
+        return gF
+
+    def fn_wmm_fwd(self, FF, W, stds, cnt, eps, flags):
+        B = FF.shape[0]
+        O = torch.empty(B, self.n_O, 2, device=FF.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_fn_wmm_fwd(self.handle, _ptr(FF), _ptr(W), _ptr(stds), cnt, eps, flags, _ptr(O), B,
+                                                     _stream_ptr(self.device)), "cgb200_fn_wmm_fwd")
+        return O
+
+    def fn_wmm_bwd(self, gO, FF, W, stds, eps, flags):
+        gFF = torch.empty_like(FF)
+        gW = torch.empty_like(W)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_fn_wmm_bwd(self.handle, _ptr(gO), _ptr(FF), _ptr(W), _ptr(stds), eps, flags,
+                                                     _ptr(gFF), _ptr(gW), FF.shape[0], _stream_ptr(self.device)),
+                       "cgb200_fn_wmm_bwd")
+        return gFF, gW
+
+    def _workspace(self, B):
+        n = int(_lib.load().cgb200_layer_workspace_bytes(self.handle, B))
+        if n < 0:
+            _lib.check(1, "cgb200_layer_workspace_bytes")
+        return torch.empty(max(n, 256), dtype=torch.uint8, device=self.device), n
+
+    def layer_fwd(self, F, W, stds, cnt, eps, flags):
+        B = F.shape[0]
+        O = torch.empty(B, self.n_O, 2, device=F.device, dtype=torch.float32)
+        ws, n = self._workspace(B)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_layer_fwd(self.handle, _ptr(F), _ptr(W), _ptr(stds), cnt, eps, flags, _ptr(O), B,
+                                                    _ptr(ws), n, _stream_ptr(self.device)), "cgb200_layer_fwd")
+        return O
+
+    def layer_bwd(self, F, W, stds, eps, flags, gO):
+        gF = torch.empty_like(F)
+        gW = torch.empty_like(W)
+        ws, n = self._workspace(F.shape[0])
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_layer_bwd(self.handle, _ptr(F), _ptr(W), _ptr(stds), eps, flags, _ptr(gO), _ptr(gF),
+                                                    _ptr(gW), F.shape[0], _ptr(ws), n, _stream_ptr(self.device)),
+                       "cgb200_layer_bwd")
+        return gF, gW
+
+
+@functools.lru_cache(maxsize=64)
+def _cached_plan(lmax, taus, tau_out, llls, device, depthwise):
+    return Plan(lmax, taus, tau_out, llls, device, depthwise)
+
+
+def get_plan(lmax, taus, tau_out, llls, device, depthwise=False):
+    """Plans are immutable, so modules with the same shape on the same device share one."""
+    dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    return _cached_plan(int(lmax), tuple(int(t) for t in taus), None if tau_out is None else tuple(int(t) for t in tau_out),
+                        tuple(int(c) for c in llls), str(dev), bool(depthwise))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# CG table helpers with the reference's names
+# ----------------------------------------------------------------------------------------------------------------
+def _precomputeCG_cuda(lmax, llls, device="cuda"):
+    """CG band table and its offsets as device tensors (reference: ``CG_layers.py:134-141``)."""
+    lib = _lib.load()
+    dev = torch.device(device)
+    offsets = CGutils.SparseLtuples.cal_CG_offsets(lmax, llls)
+    CG_coefs = torch.empty(offsets[-1], dtype=torch.float, device=dev)
+    a_l = _lib.i32(llls)
+    with torch.cuda.device(dev):
+        _lib.check(lib.cgb200_cg_table_build(_ptr(CG_coefs), offsets[-1], lmax, a_l, len(llls), _stream_ptr(dev)),
+                   "cgb200_cg_table_build")
+    return CG_coefs, torch.tensor(offsets, dtype=torch.int, device=dev)
+
+
+def _precomputeCG_MST(lmax, method="mst", device="cuda"):
+    assert method == "mst", "%s is not implemented" % method
+    llls = CGutils.SparseLtuples.sparse_rep_ltuples_sorted(CGutils.SparseLtuples.compute_mst_ltuples(lmax))[0]
+    return _precomputeCG_cuda(lmax, llls, device)
+
+
+@functools.lru_cache(10)
+def precomputeCG(lmax, method="mst", device="cuda"):
+    """Cached CG table for the full (``method=None``) or MST pair lists (reference: ``CG_layers.py:153-165``)."""
+    if method is None:
+        llls = CGutils.SparseLtuples.sparse_rep_ltuples_sorted(CGutils.SparseLtuples.compute_default_ltuples(lmax))[0]
+        return _precomputeCG_cuda(lmax, llls, device)
+    if method == "mst":
+        return _precomputeCG_MST(lmax, "mst", device)
+    raise NotImplementedError()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# autograd glue
+# ----------------------------------------------------------------------------------------------------------------
+class _CG_sparse_cuda(torch.autograd.Function):
+    """Product forward/backward (reference: ``CG_layers.py:168-203``)."""
+
+    @staticmethod
+    def forward(ctx, Fs, plan):
+        Fs = _check_cuda_f32(Fs, "activations")
+        ctx.plan = plan
+        ctx.save_for_backward(Fs)
+        return plan.cg_product_fwd(Fs)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (Fs,) = ctx.saved_tensors
+        return ctx.plan.cg_product_bwd(Fs, _check_cuda_f32(grad_output, "grad_output")), None
+
+
+def _fn_flags(bn_stds, update):
+    flags = 0
+    if bn_stds is not None:
+        flags |= _lib.FN_PRESENT
+        if update:
+            flags |= _lib.FN_UPDATE
+    return flags
+
+
+class _MyBatchNormWeightMM_cuda(torch.autograd.Function):
+    """Norm + mixing forward/backward on a materialised product (reference: ``CG_layers.py:14-72``).  As there, the
+    forward updates ``bn_stds`` in place when asked to and the backward uses the updated values."""
+
+    @staticmethod
+    def forward(ctx, FF, W, plan, bn_stds, bn_cnt, bn_eps, bn_updateflag):
+        FF = _check_cuda_f32(FF, "FF")
+        W = _check_cuda_f32(W, "W")
+        flags = _fn_flags(bn_stds, bn_updateflag)
+        out = plan.fn_wmm_fwd(FF, W, bn_stds, float(bn_cnt), float(bn_eps), flags)
+        ctx.plan, ctx.eps, ctx.flags = plan, float(bn_eps), flags & _lib.FN_PRESENT
+        ctx.save_for_backward(FF, W, None if bn_stds is None else bn_stds.detach().clone())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        FF, W, stds = ctx.saved_tensors
+        gFF, gW = ctx.plan.fn_wmm_bwd(_check_cuda_f32(grad_output, "grad_output"), FF, W, stds, ctx.eps, ctx.flags)
+        return gFF, gW, None, None, None, None, None
+
+
+class _CGBN_fused(torch.autograd.Function):
+    """Whole layer through the fused kernels: the mid activation is regenerated in the backward, never stored."""
+
+    @staticmethod
+    def forward(ctx, Fs, W, plan, bn_stds, bn_cnt, bn_eps, bn_updateflag):
+        Fs = _check_cuda_f32(Fs, "activations")
+        W = _check_cuda_f32(W, "W")
+        flags = _fn_flags(bn_stds, bn_updateflag)
+        out = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags)
+        ctx.plan, ctx.eps, ctx.flags = plan, float(bn_eps), flags & _lib.FN_PRESENT
+        ctx.save_for_backward(Fs, W, None if bn_stds is None else bn_stds.detach().clone())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        Fs, W, stds = ctx.saved_tensors
+        gF, gW = ctx.plan.layer_bwd(Fs, W, stds, ctx.eps, ctx.flags, _check_cuda_f32(grad_output, "grad_output"))
+        return gF, gW, None, None, None, None, None
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# modules
+# ----------------------------------------------------------------------------------------------------------------
+def _flatten_input(activations):
+    if isinstance(activations, (list, tuple)):
+        B = activations[0].shape[0]
+        return torch.cat([v.reshape(B, -1, 2) for v in activations], dim=1)
+    return activations
+
+
+class MyBatchNormWeightMM_cuda(nn.Module):
+    """Fragment norm and per-degree mixing weights (reference: ``CG_layers.py:74-132``).
+
+    Parameters: ``W`` flat ``(sum_l t_FF[l]*tau_out[l], 2)`` = ``weight_scale * U[0,1)``; ``bn_stds`` flat
+    ``(sum_l t_FF[l],)`` = ``U[0,1)`` (``None`` without batchnorm), not trainable; ``bn_eps`` ``(1,)``.  ``init='debug'``
+    seeds torch and numpy with 0 first, as the reference does.
+    """
+
+    def __init__(self, lmax, t_FF, tau_out, batchnorm=True, weight_scale=0.05, init="random", eps=1e-5, device="cuda",
+                 plan=None):
+        super().__init__()
+        self.lmax = lmax
+        self._init_method = init
+        self.weight_scale = weight_scale
+        self.t_FF = np.asarray(t_FF)
+        assert len(self.t_FF) - 1 == lmax
+        self.t_O = tau_out
+        m = 1 + 2 * np.arange(lmax + 1)
+        self.cumu_tm_FF = np.concatenate([[0], (self.t_FF * m).cumsum()])
+        self.cumu_tm_O = np.concatenate([[0], (np.asarray(tau_out) * m).cumsum()])
+        self.cumu_tm_W = np.concatenate([[0], (self.t_FF * np.asarray(tau_out)).cumsum()])
+        self.batchnorm = batchnorm
+        self.bn_stds = None
+        self.bn_eps = nn.Parameter(eps * torch.ones(1), requires_grad=False)
+        self._eps = float(eps)
+        self.register_buffer("bn_cnt_buf", torch.ones(1, dtype=torch.float64))
+        self.W = None
+        self._device = torch.device(device)
+        self.reset_parameters()
+        self._plan = plan   # set by CGBN_cuda; a stand-alone module builds a mixing-only plan lazily
+        self.to(device)
+
+    @property
+    def bn_cnt(self):
+        return float(self.bn_cnt_buf.item())
+
+    @bn_cnt.setter
+    def bn_cnt(self, v):
+        self.bn_cnt_buf.fill_(float(v))
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        # checkpoints written by the reference have no counter: keep the current one instead of failing
+        key = prefix + "bn_cnt_buf"
+        if key not in state_dict:
+            state_dict[key] = self.bn_cnt_buf.detach().clone()
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+        self._cnt_cache = None
+
+    def reset_parameters(self):
+        if self._init_method not in {"debug", "random"}:
+            raise NotImplementedError()
+        if self._init_method == "debug":
+            torch.manual_seed(0)
+            np.random.seed(0)
+        if self.batchnorm:
+            std_flat_np = np.random.rand(int(np.sum(self.t_FF)))
+            self.bn_stds = nn.Parameter(torch.tensor(std_flat_np, dtype=torch.float), requires_grad=False)
+        wlength = int(np.sum(self.t_FF * np.asarray(self.t_O)))
+        wbig = self.weight_scale * torch.rand(wlength, 2, device=self._device, dtype=torch.float)
+        self.W = nn.Parameter(wbig, requires_grad=True)
+        self._cnt_cache = 1.0
+
+    def _count(self):
+        # the counter is read on the host every training step; keep a host copy so the buffer needs no device sync
+        if getattr(self, "_cnt_cache", None) is None:
+            self._cnt_cache = self.bn_cnt
+        return self._cnt_cache
+
+    def _bump(self):
+        self._cnt_cache = self._count() + 1.0
+        self.bn_cnt_buf.fill_(self._cnt_cache)
+
+    def _mix_plan(self):
+        if self._plan is None:
+            # Stand-alone use: mixing never looks at the pairs, only at the channel counts.  A depthwise plan with one
+            # pseudo-triple (l, l, l) per degree and tau_in = t_FF reproduces exactly those counts.
+            L1 = self.lmax + 1
+            llls = [(l * L1 + l) * L1 + l for l in range(L1) if self.t_FF[l] > 0]
+            self._plan = get_plan(self.lmax, self.t_FF, self.t_O, llls, self.W.device, depthwise=True)
+            assert self._plan.t_ff() == [int(t) for t in self.t_FF]
+        return self._plan
+
+    def forward(self, FF):
+        update = bool(self.batchnorm and self.training)
+        out = _MyBatchNormWeightMM_cuda.apply(FF, self.W, self._mix_plan(), self.bn_stds, self._count(), self._eps, update)
+        if update:
+            self._bump()
+        return out
+
+
+class CG_woFilter_cuda(nn.Module):
+    """The CG product of an activation with itself (reference: ``CG_layers.py:205-286``).
+
+    ``lll_mode``: ``None`` (all pairs), ``'mst'``, ``'debug'`` or an explicit per-degree list of ``(l1, l2)`` lists.
+    """
+
+    def __init__(self, lmax, taus, lll_mode=None, device="cuda", tau_out=None, depthwise=False):
+        super().__init__()
+        self.lmax = lmax
+        self.t_F = taus
+        self.cum_taus = CGutils.cumulative_tm(taus)
+        self._device = torch.device(device)
+        if lll_mode is None:
+            ltuples = CGutils.SparseLtuples.compute_default_ltuples(lmax)
+        elif isinstance(lll_mode, str) and lll_mode == "mst":
+            ltuples = CGutils.SparseLtuples.compute_mst_ltuples(lmax)
+        elif isinstance(lll_mode, str) and lll_mode == "debug":
+            ltuples = CGutils.SparseLtuples.compute_debug_ltuples(lmax)
+        else:
+            ltuples = lll_mode
+        self.lll_mode = lll_mode if (lll_mode is None or isinstance(lll_mode, str)) else "custom"
+        self.depthwise = bool(depthwise)
+        self.lll_list, self.l_l1_to_lllidx_offsets = CGutils.SparseLtuples.sparse_rep_ltuples_sorted(ltuples)
+        self.t_FF, self._t_offsets = CGutils.SparseLtuples.cal_new_tau_and_offsets(lmax, taus, self.lll_list, depthwise)
+        self.cumu_tm_FF = CGutils.cumulative_tm(self.t_FF)
+        self.plan = get_plan(lmax, taus, tau_out, self.lll_list, device, depthwise)
+        assert self.plan.t_ff() == [int(t) for t in self.t_FF], "host and library disagree on the mid-channel counts"
+        self._cg_cache = None
+
+    # CG table as tensors, for callers that look at them (the kernels use the plan's resident copy)
+    def _cg_tensors(self):
+        if self._cg_cache is None:
+            if self.lll_mode is None or self.lll_mode == "mst":
+                self._cg_cache = precomputeCG(self.lmax, self.lll_mode, str(self.plan.device))
+            else:
+                self._cg_cache = _precomputeCG_cuda(self.lmax, self.lll_list, device=self.plan.device)
+        return self._cg_cache
+
+    @property
+    def CGspace(self):
+        return self._cg_tensors()[0]
+
+    @property
+    def CG_offsets(self):
+        return self._cg_tensors()[1]
+
+    def cal_new_tau_and_offsets(self, taus):
+        return CGutils.SparseLtuples.cal_new_tau_and_offsets(self.lmax, taus, self.lll_list, self.depthwise)
+
+    def forward(self, activations, straight_output=True):
+        new_activations = _flatten_input(activations)
+        if not new_activations.is_cuda:
+            raise RuntimeError("activations must be CUDA tensors (cgnet_b200 has no CPU path)")
+        output = _CG_sparse_cuda.apply(new_activations, self.plan)
+        if not straight_output:
+            output = CGutils.reshape_out(output, self.t_FF)
+        return output
+
+
+class CGBN_cuda(nn.Module):
+    """One CG layer: product, fragment norm, mixing (reference: ``CG_layers.py:289-318``).
+
+    ``forward(fs, straight_output=False)`` takes a list of ``(B, tau_l, 2l+1, 2)`` tensors or the flat
+    ``(B, sum_l tau_l(2l+1), 2)`` tensor and returns a list (default) or the flat tensor.
+    """
+
+    def __init__(self, lmax, taus_fs, tau_out, batchnorm=True, sparse_flag=False, device="cuda", weight_scale=0.05,
+                 init="random", eps=1e-5, fused=True, depthwise=False, lll_mode=None):
+        super().__init__()
+        self.lmax = lmax
+        self._init_method = init
+        self.sparse_flag = sparse_flag
+        self.fused = fused
+        mode = lll_mode if lll_mode is not None else ("mst" if sparse_flag else None)
+        self.cg = CG_woFilter_cuda(lmax, taus_fs, lll_mode=mode, device=device, tau_out=tau_out, depthwise=depthwise)
+        self.t_F = self.cg.t_F
+        self.t_FF = self.cg.t_FF
+        self.tau_out = tau_out
+        self.bnWMM = MyBatchNormWeightMM_cuda(lmax, self.t_FF, tau_out, batchnorm, weight_scale, init, eps, device,
+                                              plan=self.cg.plan)
+        self.to(device)
+
+    def forward(self, fs, straight_output=False):
+        bn = self.bnWMM
+        if self.fused:
+            x = _flatten_input(fs)
+            update = bool(bn.batchnorm and bn.training)
+            new_fs = _CGBN_fused.apply(x, bn.W, self.cg.plan, bn.bn_stds, bn._count(), bn._eps, update)
+            if update:
+                bn._bump()
+        else:
+            new_fs = bn(self.cg(fs, straight_output=True))
+        if not straight_output:
+            new_fs = CGutils.reshape_out(new_fs, self.tau_out)
+        return new_fs

@@ -1,0 +1,247 @@
+// Shared definitions of libcgnet_b200: plan tables as the kernels see them, error plumbing, and the register-tiled
+// generator of CG-product values that every kernel touching the product is built from.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/cgnet_b200.h"
+
+namespace cgb200 {
+
+constexpr int kMaxLmax = 511;        // same ceiling the reference asserts (cudaCG_sparse.cu:23)
+constexpr int kMaxTile = 6;          // largest channel-tile edge the register-tiled kernels are instantiated for
+
+// One admissible (l, l1, l2) triple with everything a kernel needs to find its operands and its outputs.
+struct TripleRec {
+    int l, l1, l2;
+    int tau1, tau2;       // channel counts of the two operand fragments
+    int nch;              // mid channels this triple produces: tau1*tau2 (tau1 in depthwise mode)
+    int toff;             // first mid channel of the triple inside degree l
+    int kglob;            // the same, counted over all degrees (index into stds)
+    int f1off, f2off;     // start of fragment l1 / l2 inside one sample of F, in complex elements
+    int cgoff;            // start of the triple's band table, in floats (tables beyond 2^31 floats are rejected)
+    int nt1, nt2;         // channel tiles along t1 and t2 (tile edge = Plan::tile)
+    int cell0;            // index of the triple's first cell
+    int64_t ffoff;        // start of the triple's block inside one sample of FF, in complex elements
+    int64_t woff;         // column of the triple inside W_l: cumW[l] + toff (row stride t_FF[l]), complex elements
+};
+
+// A cell = one (tile of t1) x (tile of t2) block of one triple: the unit of work a thread computes for one (b, m).
+struct CellRec {
+    int triple;
+    short t1_0, t2_0;
+};
+
+// Work item of the forward product kernel: a run of cells of one triple with ncell * (2l+1) <= kGenThreads.
+struct GenItem {
+    int triple;
+    int cell0;   // first cell (absolute index)
+    int ncell;
+};
+constexpr int kGenThreads = 256;
+
+// Work entry of the fused input-gradient kernel: one triple in which a given fragment takes part, the role it plays
+// there (0: first operand, 1: second operand) and the first channel of the tile of the *other* operand.
+struct GfEntry {
+    int triple;
+    short role;
+    short in0;
+};
+constexpr int kGfOut = 2;   // channels of the output fragment a block of the input-gradient kernel owns
+
+// Plan tables in device memory.
+struct PlanDev {
+    int lmax;
+    int tile;
+    int depthwise;
+    int n_triples;
+    int n_cells;
+    int has_out;
+    int64_t n_F, n_FF, n_O, w_len;
+    int sum_tff;
+    const TripleRec* triples;
+    const CellRec* cells;
+    const int* cell_begin;       // [lmax+2]  cells of degree l are cell_begin[l] .. cell_begin[l+1]
+    const int* triple_begin;     // [lmax+2]
+    const int* tF;               // [lmax+1]
+    const int* tO;               // [lmax+1]
+    const int* tFF;              // [lmax+1]
+    const int64_t* cumF;         // [lmax+2] complex elements
+    const int64_t* cumFF;
+    const int64_t* cumO;
+    const int64_t* cumW;
+    const int* cumT;             // [lmax+2] running sum of tFF
+    const int* role1_begin;      // [lmax+2] triples whose first operand is fragment l
+    const int* role1_list;
+    const int* role2_begin;      // [lmax+2] triples whose second operand is fragment l
+    const int* role2_list;
+    const float* cg;
+};
+
+void set_error(const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+// Kernel identifiers for launch accounting and the optional per-kernel CUDA-event timing (cgb200_timing_*).
+enum KernelId {
+    K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
+    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_COUNT
+};
+// Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
+// the launching stream before and after it.
+void launch_begin(int kid, cudaStream_t st);
+void launch_end(int kid, cudaStream_t st);
+
+#define CGB_CUDA(call)                                         \
+    do {                                                       \
+        cudaError_t e__ = (call);                              \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call);  \
+    } while (0)
+
+#define CGB_REQUIRE(cond, msg)                  \
+    do {                                        \
+        if (!(cond)) {                          \
+            set_error(msg);                     \
+            return CGB200_ERR_ARGUMENT;         \
+        }                                       \
+    } while (0)
+
+}  // namespace cgb200
+
+// Run a statement with TT / DD bound to the plan's tile edge and depthwise flag as compile-time constants.
+#define CGB_DISPATCH_TILE(T_, DW_, ...)                                          \
+    switch ((T_) * 2 + ((DW_) ? 1 : 0)) {                                        \
+        case 2: { constexpr int TT = 1; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        case 3: { constexpr int TT = 1; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }    \
+        case 4: { constexpr int TT = 2; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        case 5: { constexpr int TT = 2; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }    \
+        case 6: { constexpr int TT = 3; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        case 7: { constexpr int TT = 3; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }    \
+        case 8: { constexpr int TT = 4; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        case 9: { constexpr int TT = 4; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }    \
+        case 10: { constexpr int TT = 5; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }  \
+        case 11: { constexpr int TT = 5; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        case 12: { constexpr int TT = 6; constexpr bool DD = false; (void)TT; (void)DD; __VA_ARGS__; break; }  \
+        case 13: { constexpr int TT = 6; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }   \
+        default: cgb200::set_error("internal: tile edge out of range"); return CGB200_ERR_UNSUPPORTED;  \
+    }
+
+// The opaque handle of the C ABI.
+struct cgb200_plan {
+    int device = 0;
+    int num_sms = 148;
+    int flags = 0;
+    cgb200::PlanDev d{};
+    std::vector<int> tF, tO, tFF, cumT;
+    std::vector<int64_t> cumF, cumFF, cumO, cumW;
+    std::vector<cgb200::TripleRec> triples;
+    std::vector<cgb200::CellRec> cells;
+    std::vector<int> cell_begin, triple_begin;
+    int max_n = 1;                    // 2*lmax+1
+    int64_t cg_len = 0;               // floats in the CG table
+    std::vector<cgb200::GenItem> gen_items;
+    const cgb200::GenItem* d_gen_items = nullptr;
+    size_t gen_band_bytes = 0;        // largest CG band of a triple, padded to 16 bytes
+    size_t gen_sample_bytes = 0;      // largest zero-padded operand pair of a triple, per sample
+    std::vector<int> gw_begin;        // [n_triples+1] warp-tasks of the fused weight-gradient kernel per triple
+    const int* d_gw_begin = nullptr;
+    int gw_i = 1;                     // t1 channels per weight-gradient task
+    std::vector<cgb200::GfEntry> gf_entries;
+    std::vector<int> gf_begin;        // [lmax+2] entries of fragment l
+    const cgb200::GfEntry* d_gf_entries = nullptr;
+    const int* d_gf_begin = nullptr;
+    std::vector<int> gf_blocks;       // (fragment, first channel) per block of the input-gradient kernel
+    const int* d_gf_blocks = nullptr;
+    std::vector<void*> allocations;   // every cudaMalloc of the plan, freed on destroy
+};
+
+#ifdef __CUDACC__
+namespace cgb200 {
+
+__device__ __forceinline__ float2 cmul(float2 a, float2 b) { return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x); }
+// acc += a * b
+__device__ __forceinline__ void cfma(float2& acc, float2 a, float2 b) {
+    acc.x = fmaf(a.x, b.x, acc.x);
+    acc.x = fmaf(-a.y, b.y, acc.x);
+    acc.y = fmaf(a.x, b.y, acc.y);
+    acc.y = fmaf(a.y, b.x, acc.y);
+}
+// acc += conj(a) * b
+__device__ __forceinline__ void cfma_conj(float2& acc, float2 a, float2 b) {
+    acc.x = fmaf(a.x, b.x, acc.x);
+    acc.x = fmaf(a.y, b.y, acc.x);
+    acc.y = fmaf(a.x, b.y, acc.y);
+    acc.y = fmaf(-a.y, b.x, acc.y);
+}
+
+// Register-tiled generator of CG-product values for one sample and one m.  Full product (DW == false):
+//     v[i*T + j] = sum_{m2} C[m][m2] * F1[i][m - m2] * F2[j][m2],     i < T, j < T
+// depthwise product (DW == true):
+//     v[i]       = sum_{m2} C[m][m2] * F1[i][m - m2] * F2[i][m2],     i < T
+// (CGNet/cudaCG/cudaCG_sparse.cu:162-174 computes a single (i, j) per thread).  Per m2 step a thread of the full
+// product loads 2T+1 values for 4*T*T fused multiply-adds, which keeps the loop arithmetic-bound for T >= 3.
+//   Crow   the band row of this m, indexed by m2 + l2
+//   F1     rows of the first operand, row stride s1 (>= 2*l1+1), element [i*s1 + (m1 + l1)]; rows beyond the
+//          fragment's channel count must be readable (callers stage zero-padded tiles or over-allocate) and their
+//          results are masked by the caller through tile_valid()
+//   F2     likewise for the second operand with row stride s2
+//   es     distance between consecutive elements of a row (1 for a plain row; the padded batch size when the
+//          operands are stored sample-fastest and every lane of the warp reads its own sample)
+template <int T, bool DW>
+struct TileShape {
+    static constexpr int NV = DW ? T : T * T;
+};
+
+template <int T, bool DW>
+__device__ __forceinline__ void gen_tile(float2 (&v)[TileShape<T, DW>::NV], const float* __restrict__ Crow,
+                                         const float2* __restrict__ F1, int s1, const float2* __restrict__ F2, int s2,
+                                         int m, int l1, int l2, int64_t es = 1) {
+    constexpr int NV = TileShape<T, DW>::NV;
+    const int lo = max(-l2, m - l1), hi = min(l2, m + l1);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = make_float2(0.f, 0.f);
+    for (int m2 = lo; m2 <= hi; ++m2) {
+        const float c = Crow[m2 + l2];
+        float2 b[T];
+#pragma unroll
+        for (int j = 0; j < T; ++j) b[j] = F2[(int64_t)(j * s2 + m2 + l2) * es];
+#pragma unroll
+        for (int i = 0; i < T; ++i) {
+            float2 a = F1[(int64_t)(i * s1 + (m - m2) + l1) * es];
+            a.x *= c;
+            a.y *= c;
+            if (DW) {
+                cfma(v[i], a, b[i]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < T; ++j) cfma(v[i * T + j], a, b[j]);
+            }
+        }
+    }
+}
+
+// Mid channel (relative to the triple's first) of tile entry idx, and whether the entry exists.
+template <int T, bool DW>
+__device__ __forceinline__ int tile_channel(int idx, int t1_0, int t2_0, int tau2) {
+    return DW ? (t1_0 + idx) : ((t1_0 + idx / T) * tau2 + t2_0 + idx % T);
+}
+template <int T, bool DW>
+__device__ __forceinline__ bool tile_valid(int idx, int t1_0, int t2_0, int tau1, int tau2) {
+    return DW ? (t1_0 + idx < tau1) : ((t1_0 + idx / T < tau1) && (t2_0 + idx % T < tau2));
+}
+
+// Largest k with cum[k] <= e, for a non-decreasing table cum[0..n] (cum[0] == 0, e < cum[n]).
+__device__ __forceinline__ int find_degree(const int64_t* __restrict__ cum, int n, int64_t e) {
+    int lo = 0, hi = n;   // invariant: cum[lo] <= e < cum[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cum[mid] <= e) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+}  // namespace cgb200
+#endif

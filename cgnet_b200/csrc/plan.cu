@@ -1,0 +1,489 @@
+// Plan construction (host side) and the Clebsch-Gordan table kernel.
+//
+// The plan replaces the seven int32 index tensors the reference keeps on its Python modules
+// (CGNet/CG_layers.py:244-250 and :104-108) and the per-call constant uploads of its launchers
+// (CGNet/cudaCG/cudaCG_sparse.cu:336-339): everything that depends only on (lmax, tau_in, tau_out, triples) is
+// computed once here and stays resident on the device.
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <algorithm>
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cgb200 {
+
+static thread_local std::string g_last_error;
+// Launch accounting is process-wide: autograd runs the backward kernels on its own thread.
+static std::atomic<int64_t> g_launches{0};
+static std::mutex g_timing_mutex;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int cuda_fail(cudaError_t e, const char* what) {
+    g_last_error = std::string("CUDA error in ") + what + ": " + cudaGetErrorString(e);
+    return CGB200_ERR_CUDA;
+}
+
+static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_product_bwd", "fn_stats", "wmm_fwd",
+                                            "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
+                                            "fused_grad_w", "fused_grad_f"};
+struct TimedLaunch {
+    int kid;
+    cudaEvent_t a, b;
+};
+static std::atomic<bool> g_timing{false};
+static std::vector<TimedLaunch> g_timed;          // guarded by g_timing_mutex
+static std::vector<cudaEvent_t> g_event_pool;     // guarded by g_timing_mutex
+static thread_local size_t g_open = 0;            // index in g_timed of this thread's launch in flight
+
+static cudaEvent_t take_event() {
+    if (!g_event_pool.empty()) {
+        cudaEvent_t e = g_event_pool.back();
+        g_event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+void launch_begin(int kid, cudaStream_t st) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (g_timing.load(std::memory_order_relaxed)) {
+        std::lock_guard<std::mutex> lock(g_timing_mutex);
+        TimedLaunch t{kid, take_event(), take_event()};
+        cudaEventRecord(t.a, st);
+        g_open = g_timed.size();
+        g_timed.push_back(t);
+    }
+}
+void launch_end(int kid, cudaStream_t st) {
+    (void)kid;
+    if (g_timing.load(std::memory_order_relaxed)) {
+        std::lock_guard<std::mutex> lock(g_timing_mutex);
+        if (g_open < g_timed.size()) cudaEventRecord(g_timed[g_open].b, st);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// CG table.  One block per triple, threads stride over the (2l+1)(2l2+1) band entries; Racah's sum in double with a
+// log-factorial table, the same arithmetic as CGNet/cudaCG/cudaCG_sparse.cu:33-57 (the reference runs one *thread*
+// per triple and leaves entries outside the band untouched; here they are written as zero).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ double lf(const double* t, int n) { return n < 2 ? 0.0 : t[n]; }
+
+__global__ void cg_table_kernel(float* __restrict__ cg, const int* __restrict__ llls, const int64_t* __restrict__ offs,
+                                int n_triples, int L1, const double* __restrict__ logfact) {
+    const int k = blockIdx.x;
+    if (k >= n_triples) return;
+    const int code = llls[k];
+    const int l = code / (L1 * L1), l1 = (code / L1) % L1, l2 = code % L1;
+    const int n2 = 2 * l2 + 1, n = 2 * l + 1;
+    float* out = cg + offs[k];
+    const double logA0 = 0.5 * (log(2.0 * l + 1.0) + lf(logfact, l + l1 - l2) + lf(logfact, l - l1 + l2) +
+                                lf(logfact, l1 + l2 - l) - lf(logfact, l1 + l2 + l + 1));
+    for (int e = threadIdx.x; e < n * n2; e += blockDim.x) {
+        const int m = e / n2 - l, m2 = e % n2 - l2, m1 = m - m2;
+        float v = 0.f;
+        if (m1 >= -l1 && m1 <= l1) {
+            const int a = l2 - m1 - l, b = l1 + m2 - l, c = l1 + l2 - l, d = l1 - m1, f = l2 + m2;
+            const int lo = max(0, max(a, b)), hi = min(c, min(d, f));
+            const double logA = logA0 + 0.5 * (lf(logfact, l + m) + lf(logfact, l - m) + lf(logfact, l1 - m1) +
+                                               lf(logfact, l1 + m1) + lf(logfact, l2 - m2) + lf(logfact, l2 + m2));
+            double s = 0.0;
+            for (int t = lo; t <= hi; ++t) {
+                const double logB = lf(logfact, t) + lf(logfact, c - t) + lf(logfact, d - t) + lf(logfact, f - t) +
+                                    lf(logfact, t - a) + lf(logfact, t - b);
+                const double term = exp(logA - logB);
+                s += (t & 1) ? -term : term;
+            }
+            v = (float)s;
+        }
+        out[e] = v;
+    }
+}
+
+static int decode_and_check(int lmax, const int32_t* llls, int n, std::vector<int>& ls, std::vector<int>& l1s,
+                            std::vector<int>& l2s) {
+    CGB_REQUIRE(lmax >= 0 && lmax <= kMaxLmax, "lmax out of range [0, 511]");
+    CGB_REQUIRE(n >= 0 && (n == 0 || llls != nullptr), "triple list is null");
+    const int L1 = lmax + 1;
+    ls.resize(n);
+    l1s.resize(n);
+    l2s.resize(n);
+    for (int k = 0; k < n; ++k) {
+        const int c = llls[k];
+        CGB_REQUIRE(c >= 0 && (int64_t)c < (int64_t)L1 * L1 * L1, "triple code out of range");
+        const int l = c / (L1 * L1), l1 = (c / L1) % L1, l2 = c % L1;
+        CGB_REQUIRE(l2 <= l1, "triples must come with l2 <= l1");
+        CGB_REQUIRE(l >= l1 - l2 && l <= l1 + l2, "triple violates |l1-l2| <= l <= l1+l2");
+        CGB_REQUIRE(k == 0 || l >= ls[k - 1], "triples must be grouped by non-decreasing l");
+        ls[k] = l;
+        l1s[k] = l1;
+        l2s[k] = l2;
+    }
+    return CGB200_OK;
+}
+
+static int build_table(float* cg_dev, int64_t cg_len, int lmax, const int32_t* llls, int n, cudaStream_t st) {
+    std::vector<int> ls, l1s, l2s;
+    int rc = decode_and_check(lmax, llls, n, ls, l1s, l2s);
+    if (rc) return rc;
+    std::vector<int64_t> offs(n + 1, 0);
+    for (int k = 0; k < n; ++k) offs[k + 1] = offs[k] + (int64_t)(2 * ls[k] + 1) * (2 * l2s[k] + 1);
+    CGB_REQUIRE(cg_len == offs[n], "cg_len does not match the triple list");
+    if (n == 0) return CGB200_OK;
+    CGB_REQUIRE(cg_dev != nullptr, "cg_dev is null");
+    const int nlf = 3 * lmax + 4;
+    std::vector<double> logfact(nlf, 0.0);
+    for (int i = 2; i < nlf; ++i) logfact[i] = logfact[i - 1] + log((double)i);   // cudaCG_utils.cu:83-90
+    double* d_lf = nullptr;
+    int* d_llls = nullptr;
+    int64_t* d_offs = nullptr;
+    CGB_CUDA(cudaMalloc(&d_lf, nlf * sizeof(double)));
+    CGB_CUDA(cudaMalloc(&d_llls, n * sizeof(int)));
+    CGB_CUDA(cudaMalloc(&d_offs, (n + 1) * sizeof(int64_t)));
+    CGB_CUDA(cudaMemcpyAsync(d_lf, logfact.data(), nlf * sizeof(double), cudaMemcpyHostToDevice, st));
+    CGB_CUDA(cudaMemcpyAsync(d_llls, llls, n * sizeof(int), cudaMemcpyHostToDevice, st));
+    CGB_CUDA(cudaMemcpyAsync(d_offs, offs.data(), (n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    launch_begin(K_CG_TABLE, st);
+    cg_table_kernel<<<n, 128, 0, st>>>(cg_dev, d_llls, d_offs, n, lmax + 1, d_lf);
+    launch_end(K_CG_TABLE, st);
+    CGB_CUDA(cudaGetLastError());
+    CGB_CUDA(cudaStreamSynchronize(st));   // one-off set-up call: the host vectors and temporaries die here
+    cudaFree(d_lf);
+    cudaFree(d_llls);
+    cudaFree(d_offs);
+    return CGB200_OK;
+}
+
+template <typename T>
+static int upload(cgb200_plan* p, const std::vector<T>& v, const T** out) {
+    void* d = nullptr;
+    const size_t bytes = std::max<size_t>(v.size(), 1) * sizeof(T);
+    CGB_CUDA(cudaMalloc(&d, bytes));
+    p->allocations.push_back(d);
+    if (!v.empty()) CGB_CUDA(cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    *out = (const T*)d;
+    return CGB200_OK;
+}
+
+// Channel-tile edge: the largest fraction of useful lanes in the T x T register tiles, weighted by each triple's work,
+// with a mild preference for 4..5 (enough arithmetic per shared-memory load, moderate register use).
+static int choose_tile(const std::vector<TripleRec>& tr, bool dw) {
+    if (const char* env = getenv("CGB200_TILE")) {
+        const int t = atoi(env);
+        if (t >= 1 && t <= kMaxTile) return t;
+    }
+    static const double pref[kMaxTile + 1] = {0, 0.55, 0.80, 0.93, 1.00, 1.00, 0.96};
+    int best = 1;
+    double best_score = -1;
+    for (int T = 1; T <= kMaxTile; ++T) {
+        double useful = 0, spent = 0;
+        for (const auto& t : tr) {
+            const double w = (double)(2 * t.l + 1) * (2 * t.l2 + 1);
+            const double n1 = (t.tau1 + T - 1) / T, n2 = (t.tau2 + T - 1) / T;
+            if (dw) {
+                useful += w * t.tau1;
+                spent += w * n1 * T;
+            } else {
+                useful += w * t.tau1 * t.tau2;
+                spent += w * n1 * n2 * T * T;
+            }
+        }
+        const double score = (spent > 0 ? useful / spent : 1.0) * pref[T];
+        if (score > best_score + 1e-9) {
+            best_score = score;
+            best = T;
+        }
+    }
+    return best;
+}
+
+}  // namespace cgb200
+
+using namespace cgb200;
+
+extern "C" {
+
+const char* cgb200_last_error(void) { return g_last_error.c_str(); }
+int cgb200_version(void) { return 100; }
+int cgb200_max_lmax(void) { return kMaxLmax; }
+int64_t cgb200_launch_count(int reset) {
+    return reset ? g_launches.exchange(0) : g_launches.load();
+}
+
+int cgb200_kernel_count(void) { return K_COUNT; }
+const char* cgb200_kernel_name(int kid) { return (kid >= 0 && kid < K_COUNT) ? kKernelNames[kid] : ""; }
+
+void cgb200_timing_enable(int on) { g_timing.store(on != 0); }
+
+int cgb200_timing_read(double* ms, int64_t* launches, int reset) {
+    CGB_REQUIRE(ms != nullptr && launches != nullptr, "null argument");
+    for (int k = 0; k < K_COUNT; ++k) {
+        ms[k] = 0.0;
+        launches[k] = 0;
+    }
+    std::lock_guard<std::mutex> lock(g_timing_mutex);
+    for (const TimedLaunch& t : g_timed) {
+        CGB_CUDA(cudaEventSynchronize(t.b));
+        float dt = 0.f;
+        CGB_CUDA(cudaEventElapsedTime(&dt, t.a, t.b));
+        ms[t.kid] += dt;
+        launches[t.kid] += 1;
+    }
+    if (reset) {
+        for (const TimedLaunch& t : g_timed) {
+            g_event_pool.push_back(t.a);
+            g_event_pool.push_back(t.b);
+        }
+        g_timed.clear();
+    }
+    return CGB200_OK;
+}
+
+int64_t cgb200_cg_table_length(int lmax, const int32_t* llls, int n) {
+    std::vector<int> ls, l1s, l2s;
+    if (decode_and_check(lmax, llls, n, ls, l1s, l2s)) return -1;
+    int64_t len = 0;
+    for (int k = 0; k < n; ++k) len += (int64_t)(2 * ls[k] + 1) * (2 * l2s[k] + 1);
+    return len;
+}
+
+int cgb200_cg_table_build(float* cg_dev, int64_t cg_len, int lmax, const int32_t* llls, int n, void* stream) {
+    return build_table(cg_dev, cg_len, lmax, llls, n, (cudaStream_t)stream);
+}
+
+int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const int32_t* tau_out,
+                       const int32_t* llls, int n, int flags) {
+    CGB_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    CGB_REQUIRE(tau_in != nullptr, "tau_in is null");
+    std::vector<int> ls, l1s, l2s;
+    int rc = decode_and_check(lmax, llls, n, ls, l1s, l2s);
+    if (rc) return rc;
+    const bool dw = (flags & CGB200_PLAN_DEPTHWISE) != 0;
+    const int L1 = lmax + 1;
+
+    cgb200_plan* p = new cgb200_plan();
+    struct Guard {
+        cgb200_plan* p;
+        ~Guard() { if (p) cgb200_plan_destroy(p); }
+    } guard{p};
+    p->flags = flags;
+    CGB_CUDA(cudaGetDevice(&p->device));
+    CGB_CUDA(cudaDeviceGetAttribute(&p->num_sms, cudaDevAttrMultiProcessorCount, p->device));
+    p->max_n = 2 * lmax + 1;
+
+    p->tF.assign(tau_in, tau_in + L1);
+    for (int l = 0; l < L1; ++l) CGB_REQUIRE(p->tF[l] >= 0 && p->tF[l] <= 32767, "tau_in out of range [0, 32767]");
+    const bool has_out = tau_out != nullptr;
+    if (has_out) {
+        p->tO.assign(tau_out, tau_out + L1);
+        for (int l = 0; l < L1; ++l) CGB_REQUIRE(p->tO[l] >= 0, "tau_out must be non-negative");
+    } else {
+        p->tO.assign(L1, 0);
+    }
+
+    p->cumF.assign(L1 + 1, 0);
+    for (int l = 0; l < L1; ++l) p->cumF[l + 1] = p->cumF[l] + (int64_t)p->tF[l] * (2 * l + 1);
+    CGB_REQUIRE(p->cumF[L1] < (1ll << 30), "input activation too long");
+
+    // mid-channel counts and per-triple offsets (CGNet/CG_layers.py:253-262)
+    std::vector<int64_t> tff64(L1, 0);
+    p->triples.resize(n);
+    int64_t cgoff = 0;
+    for (int k = 0; k < n; ++k) {
+        TripleRec& t = p->triples[k];
+        t.l = ls[k];
+        t.l1 = l1s[k];
+        t.l2 = l2s[k];
+        t.tau1 = p->tF[t.l1];
+        t.tau2 = p->tF[t.l2];
+        if (dw) CGB_REQUIRE(t.tau1 == t.tau2, "depthwise product needs tau_l1 == tau_l2 for every pair");
+        t.nch = dw ? t.tau1 : t.tau1 * t.tau2;
+        CGB_REQUIRE(tff64[t.l] + t.nch < (1ll << 31), "too many mid channels in one degree");
+        t.toff = (int)tff64[t.l];
+        tff64[t.l] += t.nch;
+        t.f1off = (int)p->cumF[t.l1];
+        t.f2off = (int)p->cumF[t.l2];
+        CGB_REQUIRE(cgoff < (1ll << 31) - (1 << 20), "CG table too long");
+        t.cgoff = (int)cgoff;
+        cgoff += (int64_t)(2 * t.l + 1) * (2 * t.l2 + 1);
+    }
+    p->tFF.resize(L1);
+    p->cumT.assign(L1 + 1, 0);
+    p->cumFF.assign(L1 + 1, 0);
+    p->cumO.assign(L1 + 1, 0);
+    p->cumW.assign(L1 + 1, 0);
+    for (int l = 0; l < L1; ++l) {
+        p->tFF[l] = (int)tff64[l];
+        CGB_REQUIRE((int64_t)p->cumT[l] + tff64[l] < (1ll << 31), "too many mid channels");
+        p->cumT[l + 1] = p->cumT[l] + p->tFF[l];
+        p->cumFF[l + 1] = p->cumFF[l] + tff64[l] * (2 * l + 1);
+        p->cumO[l + 1] = p->cumO[l] + (int64_t)p->tO[l] * (2 * l + 1);
+        p->cumW[l + 1] = p->cumW[l] + tff64[l] * p->tO[l];
+    }
+    for (auto& t : p->triples) {
+        t.kglob = p->cumT[t.l] + t.toff;
+        t.ffoff = p->cumFF[t.l] + (int64_t)t.toff * (2 * t.l + 1);
+        t.woff = p->cumW[t.l] + t.toff;
+    }
+
+    const int T = choose_tile(p->triples, dw);
+    p->triple_begin.assign(L1 + 1, 0);
+    p->cell_begin.assign(L1 + 1, 0);
+    for (int k = 0; k < n; ++k) {
+        TripleRec& t = p->triples[k];
+        t.nt1 = (t.tau1 + T - 1) / T;
+        t.nt2 = dw ? 1 : (t.tau2 + T - 1) / T;
+        t.cell0 = (int)p->cells.size();
+        for (int i1 = 0; i1 < t.nt1; ++i1)
+            for (int i2 = 0; i2 < t.nt2; ++i2) {
+                CellRec c;
+                c.triple = k;
+                c.t1_0 = (short)(i1 * T);
+                c.t2_0 = (short)(dw ? i1 * T : i2 * T);
+                p->cells.push_back(c);
+            }
+        CGB_REQUIRE(p->cells.size() < (size_t)(1u << 30), "too many work cells");
+        p->triple_begin[t.l + 1] = k + 1;
+        p->cell_begin[t.l + 1] = (int)p->cells.size();
+    }
+    for (int l = 0; l < L1; ++l) {   // degrees without triples inherit the running end
+        p->triple_begin[l + 1] = std::max(p->triple_begin[l + 1], p->triple_begin[l]);
+        p->cell_begin[l + 1] = std::max(p->cell_begin[l + 1], p->cell_begin[l]);
+    }
+
+    // which triples use fragment l as first / second operand (for the gather-style input gradient)
+    std::vector<int> r1b(L1 + 1, 0), r2b(L1 + 1, 0), r1l, r2l;
+    for (int l = 0; l < L1; ++l) {
+        for (int k = 0; k < n; ++k) {
+            if (p->triples[k].l1 == l) r1l.push_back(k);
+            if (p->triples[k].l2 == l) r2l.push_back(k);
+        }
+        r1b[l + 1] = (int)r1l.size();
+        r2b[l + 1] = (int)r2l.size();
+    }
+
+    PlanDev& d = p->d;
+    d.lmax = lmax;
+    d.tile = T;
+    d.depthwise = dw ? 1 : 0;
+    d.n_triples = n;
+    d.n_cells = (int)p->cells.size();
+    d.has_out = has_out ? 1 : 0;
+    d.n_F = p->cumF[L1];
+    d.n_FF = p->cumFF[L1];
+    d.n_O = p->cumO[L1];
+    d.w_len = p->cumW[L1];
+    d.sum_tff = p->cumT[L1];
+    if ((rc = upload(p, p->triples, &d.triples))) return rc;
+    if ((rc = upload(p, p->cells, &d.cells))) return rc;
+    if ((rc = upload(p, p->cell_begin, &d.cell_begin))) return rc;
+    if ((rc = upload(p, p->triple_begin, &d.triple_begin))) return rc;
+    if ((rc = upload(p, p->tF, &d.tF))) return rc;
+    if ((rc = upload(p, p->tO, &d.tO))) return rc;
+    if ((rc = upload(p, p->tFF, &d.tFF))) return rc;
+    if ((rc = upload(p, p->cumF, &d.cumF))) return rc;
+    if ((rc = upload(p, p->cumFF, &d.cumFF))) return rc;
+    if ((rc = upload(p, p->cumO, &d.cumO))) return rc;
+    if ((rc = upload(p, p->cumW, &d.cumW))) return rc;
+    if ((rc = upload(p, p->cumT, &d.cumT))) return rc;
+    if ((rc = upload(p, r1b, &d.role1_begin))) return rc;
+    if ((rc = upload(p, r1l, &d.role1_list))) return rc;
+    if ((rc = upload(p, r2b, &d.role2_begin))) return rc;
+    if ((rc = upload(p, r2l, &d.role2_list))) return rc;
+
+    // work items of the forward product kernel
+    for (int k = 0; k < n; ++k) {
+        const TripleRec& t = p->triples[k];
+        const int nn = 2 * t.l + 1, n1 = 2 * t.l1 + 1, n2 = 2 * t.l2 + 1;
+        const int per = std::max(1, kGenThreads / nn);
+        const int ncells = t.nt1 * t.nt2;
+        for (int c0 = 0; c0 < ncells; c0 += per) p->gen_items.push_back({k, t.cell0 + c0, std::min(per, ncells - c0)});
+        p->gen_band_bytes = std::max(p->gen_band_bytes, (size_t)((nn * n2 * 4 + 15) & ~15));
+        const size_t rows2 = dw ? (size_t)t.nt1 * T : (size_t)t.nt2 * T;
+        p->gen_sample_bytes = std::max(p->gen_sample_bytes, ((size_t)t.nt1 * T * n1 + rows2 * n2) * sizeof(float2));
+    }
+    if ((rc = upload(p, p->gen_items, &p->d_gen_items))) return rc;
+
+    // warp-tasks of the fused weight-gradient kernel: (t1 group, t2 tile, tau_out tile) per triple
+    static const int kGwI[kMaxTile + 1] = {0, 4, 4, 3, 2, 2, 1};
+    p->gw_i = dw ? T : kGwI[T];
+    p->gw_begin.assign(n + 1, 0);
+    for (int k = 0; k < n; ++k) {
+        const TripleRec& t = p->triples[k];
+        const int64_t no = (p->tO[t.l] + T - 1) / T;
+        const int64_t ni = (t.tau1 + p->gw_i - 1) / p->gw_i;
+        const int64_t cnt = dw ? ni * no : ni * t.nt2 * no;
+        CGB_REQUIRE(p->gw_begin[k] + cnt < (1ll << 31), "too many weight-gradient tasks");
+        p->gw_begin[k + 1] = p->gw_begin[k] + (int)cnt;
+    }
+    if ((rc = upload(p, p->gw_begin, &p->d_gw_begin))) return rc;
+    // entries of the fused input-gradient kernel, per fragment
+    p->gf_begin.assign(L1 + 1, 0);
+    for (int l = 0; l < L1; ++l) {
+        for (int k = 0; k < n; ++k) {
+            const TripleRec& t = p->triples[k];
+            if (t.l1 == l)
+                for (int j = 0; j < (dw ? 1 : t.nt2); ++j) p->gf_entries.push_back({k, 0, (short)(j * T)});
+            if (t.l2 == l)
+                for (int i = 0; i < (dw ? 1 : t.nt1); ++i) p->gf_entries.push_back({k, 1, (short)(i * T)});
+        }
+        p->gf_begin[l + 1] = (int)p->gf_entries.size();
+    }
+    if ((rc = upload(p, p->gf_entries, &p->d_gf_entries))) return rc;
+    if ((rc = upload(p, p->gf_begin, &p->d_gf_begin))) return rc;
+    for (int l = 0; l < L1; ++l)
+        for (int t = 0; t < p->tF[l]; t += kGfOut) {
+            p->gf_blocks.push_back(l);
+            p->gf_blocks.push_back(t);
+        }
+    if ((rc = upload(p, p->gf_blocks, &p->d_gf_blocks))) return rc;
+
+    float* cg = nullptr;
+    CGB_CUDA(cudaMalloc(&cg, std::max<int64_t>(cgoff, 1) * sizeof(float)));
+    p->allocations.push_back(cg);
+    if ((rc = build_table(cg, cgoff, lmax, llls, n, nullptr))) return rc;
+    d.cg = cg;
+    p->cg_len = cgoff;
+
+    guard.p = nullptr;
+    *out = p;
+    return CGB200_OK;
+}
+
+void cgb200_plan_destroy(cgb200_plan* p) {
+    if (!p) return;
+    for (void* a : p->allocations) cudaFree(a);
+    delete p;
+}
+
+int cgb200_plan_query(const cgb200_plan* p, int what, int64_t* v) {
+    CGB_REQUIRE(p != nullptr && v != nullptr, "null argument");
+    switch (what) {
+        case CGB200_Q_N_F: *v = p->d.n_F; break;
+        case CGB200_Q_N_FF: *v = p->d.n_FF; break;
+        case CGB200_Q_N_O: *v = p->d.n_O; break;
+        case CGB200_Q_W_LEN: *v = p->d.w_len; break;
+        case CGB200_Q_SUM_TFF: *v = p->d.sum_tff; break;
+        case CGB200_Q_CG_LEN: *v = p->cg_len; break;
+        case CGB200_Q_N_TRIPLES: *v = p->d.n_triples; break;
+        case CGB200_Q_TILE: *v = p->d.tile; break;
+        default: set_error("unknown query"); return CGB200_ERR_ARGUMENT;
+    }
+    return CGB200_OK;
+}
+
+int cgb200_plan_t_ff(const cgb200_plan* p, int32_t* out) {
+    CGB_REQUIRE(p != nullptr && out != nullptr, "null argument");
+    for (size_t l = 0; l < p->tFF.size(); ++l) out[l] = p->tFF[l];
+    return CGB200_OK;
+}
+
+const float* cgb200_plan_cg_table(const cgb200_plan* p) { return p ? p->d.cg : nullptr; }
+
+}  // extern "C"

@@ -1,0 +1,159 @@
+/*
+ * cgnet_b200 -- C ABI of the B200 (sm_100a) Clebsch-Gordan layer library, libcgnet_b200.so.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns an int status (CGB200_OK == 0).
+ * Device pointers are ordinary CUDA device addresses owned by the caller; nothing here allocates or frees a caller
+ * buffer.  `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  No call synchronises the
+ * device; work is ordered on `stream` only.  After a non-zero status, cgb200_last_error() (thread-local) says why.
+ *
+ * Data layout (the reference project's, zlin7/CGNet; file:line below are paths inside that project):
+ *   activation   float[B][N][2]            N = sum_l tau_l (2l+1); fragment l starts at cum[l] = sum_{l'<l} tau_l'(2l'+1);
+ *                                          inside it element (t, m) sits at t(2l+1) + (m+l); last axis (re, im)
+ *                                          (CGNet/cudaCG/cudaCG_sparse.cu:17, CGNet/CGutils.py:190-197)
+ *   triples      int32 codes (l(L+1)+l1)(L+1)+l2 with l2 <= l1, grouped by l, inside l ordered by l1
+ *                                          (CGNet/CGutils.py:122-140)
+ *   mid channel  of triple k in degree l:  t_offsets[k] + t1*tau_l2 + t2            (CGNet/CG_layers.py:253-262)
+ *   CG table     float, per triple a (2l+1) x (2l2+1) band, entry [m+l][m2+l2] = <l1 m-m2; l2 m2 | l m>, zero when
+ *                |m-m2| > l1                                                          (CGNet/cudaCG/cudaCG_sparse.cu:68-92)
+ *   weights      float[sum_l tau_out[l] t_FF[l]][2]; degree l is a row-major (tau_out[l], t_FF[l]) complex matrix
+ *                                          (CGNet/cudaCG/cudaCG_FNWMM.cu:18, CGNet/CG_layers.py:98)
+ *   stds         float[sum_l t_FF[l]]      one moving standard deviation per mid channel (CGNet/CG_layers.py:116-117)
+ */
+#ifndef CGNET_B200_H_
+#define CGNET_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CGB200_OK               0
+#define CGB200_ERR_ARGUMENT     1   /* null pointer, negative size, misaligned buffer, inconsistent plan            */
+#define CGB200_ERR_UNSUPPORTED  2   /* shape outside what the kernels handle (see cgb200_last_error)               */
+#define CGB200_ERR_CUDA         3   /* a CUDA runtime call failed; the message carries cudaGetErrorString          */
+#define CGB200_ERR_WORKSPACE    4   /* workspace too small                                                          */
+
+/* fragment-norm flags, same bit meaning as the reference's `bn_flags` (CGNet/CG_layers.py:22-33) */
+#define CGB200_FN_PRESENT       0x1 /* stds is valid: divide every mid channel by max(eps, stds[k])                */
+#define CGB200_FN_UPDATE        0x2 /* training: first fold this batch's statistics into stds, in place            */
+
+/* plan flags */
+#define CGB200_PLAN_DEPTHWISE   0x1 /* channel-wise product (t1 == t2 only; needs tau_l1 == tau_l2).  Not in the
+                                       reference (its 'mst' mode keeps the full tau_l1 x tau_l2 product)           */
+
+typedef struct cgb200_plan cgb200_plan;
+
+const char* cgb200_last_error(void);
+int cgb200_version(void);
+
+/* Largest lmax accepted.  Replaces `sparse_maxL` (CGNet/cudaCG/cudaCG_all.cpp:124-126). */
+int cgb200_max_lmax(void);
+
+/*
+ * Build the CG band table for a triple list on the device.
+ * Replaces `sparse_precomputeCG` (CGNet/cudaCG/cudaCG_all.cpp:112-121 -> cudaCG_sparse.cu:304-319).
+ *   cg_dev      device float[cg_len], fully overwritten (entries outside the band become 0)
+ *   llls_host   HOST int32[n_llls] triple codes;  the offsets follow from them: off[k+1] = off[k] + (2l+1)(2l2+1)
+ */
+int cgb200_cg_table_build(float* cg_dev, int64_t cg_len, int lmax, const int32_t* llls_host, int n_llls, void* stream);
+/* Length the table needs for a triple list (CGNet/CGutils.py:154-158). */
+int64_t cgb200_cg_table_length(int lmax, const int32_t* llls_host, int n_llls);
+
+/*
+ * A plan holds everything that depends only on (lmax, tau_in, tau_out, triple list): the index tables the
+ * reference keeps as seven int32 tensors on its module (CGNet/CG_layers.py:244-250, :104-108), the CG table
+ * (CGNet/CG_layers.py:134-141) and the work lists of the kernels.  Host arrays are copied.  tau_out may be NULL
+ * for a product-only plan.  The plan belongs to the CUDA device that is current when it is created.
+ */
+int  cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const int32_t* tau_out,
+                        const int32_t* llls_host, int n_llls, int flags);
+void cgb200_plan_destroy(cgb200_plan* plan);
+
+/* Sizes derived by the plan, in complex elements per sample unless stated. */
+#define CGB200_Q_N_F        0   /* input activation length                                    */
+#define CGB200_Q_N_FF       1   /* CG-product (mid) activation length                         */
+#define CGB200_Q_N_O        2   /* output activation length (0 without tau_out)               */
+#define CGB200_Q_W_LEN      3   /* complex weights                                            */
+#define CGB200_Q_SUM_TFF    4   /* mid channels = length of stds                              */
+#define CGB200_Q_CG_LEN     5   /* floats in the CG table                                     */
+#define CGB200_Q_N_TRIPLES  6
+#define CGB200_Q_TILE       7   /* channel-tile edge chosen for the register-tiled kernels    */
+int cgb200_plan_query(const cgb200_plan* plan, int what, int64_t* value);
+/* Per-degree mid-channel counts t_FF[0..lmax] (CGNet/CG_layers.py:253-262), for cross-checking the host's own. */
+int cgb200_plan_t_ff(const cgb200_plan* plan, int32_t* t_ff_host);
+/* Device address of the plan's CG table (float[CGB200_Q_CG_LEN]); valid until the plan is destroyed. */
+const float* cgb200_plan_cg_table(const cgb200_plan* plan);
+
+/*
+ * CG product  F -> FF.   Replaces `sparse_forward` (CGNet/cudaCG/cudaCG_all.cpp:39-71 -> cudaCG_sparse.cu:96-184).
+ *   F   device float[B][N_F][2]     FF  device float[B][N_FF][2], every element written
+ */
+int cgb200_cg_product_fwd(const cgb200_plan* plan, const float* F, float* FF, int64_t B, void* stream);
+
+/*
+ * Gradient of the CG product with respect to its input.
+ * Replaces `sparse_backward` (CGNet/cudaCG/cudaCG_all.cpp:73-108 -> cudaCG_sparse.cu:186-298).
+ *   gFF device float[B][N_FF][2]    gF  device float[B][N_F][2], every element written (no pre-zeroing needed)
+ */
+int cgb200_cg_product_bwd(const cgb200_plan* plan, const float* F, const float* gFF, float* gF, int64_t B, void* stream);
+
+/*
+ * Fragment norm + channel mixing  FF -> O.
+ * Replaces `FN_WMM_forward` (CGNet/cudaCG/cudaCG_all.cpp:137-165 -> cudaCG_FNWMM.cu:29-123,215-245).
+ *   flags & CGB200_FN_UPDATE: stds[k] <- stds[k]*cnt/(cnt+1) + sigma_k/(cnt+1) first, sigma_k the standard deviation
+ *   of |FF[b,k,m]| over (b, m) computed in double; then O_l = W_l diag(1/max(eps, stds)) FF_l.
+ *   stds may be NULL when CGB200_FN_PRESENT is clear.
+ */
+int cgb200_fn_wmm_fwd(const cgb200_plan* plan, const float* FF, const float* W, float* stds, float cnt, float eps,
+                      int flags, float* O, int64_t B, void* stream);
+
+/*
+ * Gradients of the mixing.
+ * Replaces `FN_WMM_backward` (CGNet/cudaCG/cudaCG_all.cpp:172-205 -> cudaCG_FNWMM.cu:126-211,250-282).
+ *   gW  device float[W_LEN][2], fully written, summed over the batch in a fixed order (the reference uses atomicAdd)
+ *   gFF device float[B][N_FF][2], fully written.  The statistics carry no gradient, as in the reference.
+ */
+int cgb200_fn_wmm_bwd(const cgb200_plan* plan, const float* gO, const float* FF, const float* W, const float* stds,
+                      float eps, int flags, float* gFF, float* gW, int64_t B, void* stream);
+
+/*
+ * The whole layer in one pass, F -> O, without ever writing FF to memory.
+ * Replaces the sequence `sparse_forward` + `FN_WMM_forward` issued by CGBN_cuda.forward (CGNet/CG_layers.py:313-318).
+ * Same meaning of stds / cnt / eps / flags as cgb200_fn_wmm_fwd.
+ *   workspace  device scratch of at least cgb200_layer_workspace_bytes(plan, B) bytes, 256-byte aligned, contents
+ *              undefined on entry and exit.
+ */
+int cgb200_layer_fwd(const cgb200_plan* plan, const float* F, const float* W, float* stds, float cnt, float eps,
+                     int flags, float* O, int64_t B, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * Gradients of the whole layer, (F, W, stds, gO) -> (gF, gW), regenerating FF on the fly.
+ * Replaces `FN_WMM_backward` + `sparse_backward` issued by autograd (CGNet/CG_layers.py:54-72, 194-203).
+ * `stds` must be the values the forward used (i.e. after its update).
+ */
+int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, const float* stds, float eps, int flags,
+                     const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,
+                     void* stream);
+
+/* Scratch bytes the two fused calls need for a batch of B samples (the larger of the two). */
+int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
+
+/* Number of kernels this library launched in this process since the last reset (bench accounting). */
+int64_t cgb200_launch_count(int reset);
+
+/*
+ * Optional per-kernel timing for benchmarks (no reference counterpart).  While enabled (process-wide), every
+ * kernel launch is bracketed by CUDA events on its stream.  cgb200_timing_read waits for the recorded launches and
+ * returns, per kernel id in [0, cgb200_kernel_count()), the summed device time in milliseconds and the number of
+ * launches; `reset` non-zero forgets the recorded launches.  Do not enable it inside a CUDA-graph capture.
+ */
+int cgb200_kernel_count(void);
+const char* cgb200_kernel_name(int kernel_id);
+void cgb200_timing_enable(int on);
+int cgb200_timing_read(double* ms_per_kernel, int64_t* launches_per_kernel, int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* CGNET_B200_H_ */

@@ -228,10 +228,10 @@ def cg_product(frags, taus, lmax, llls, depthwise=False):
         if depthwise:
             assert taus[l1] == taus[l2]
             kp = z[l1].unsqueeze(3) * z[l2].unsqueeze(2)                          # (B, t, m1, m2)
-            kp = kp.reshape(B, taus[l1], -1)
+            kp = kp.reshape(B, taus[l1], (2 * l1 + 1) * (2 * l2 + 1))
         else:
             kp = z[l1][:, :, None, :, None] * z[l2][:, None, :, None, :]          # (B, t1, t2, m1, m2)
-            kp = kp.reshape(B, taus[l1] * taus[l2], -1)
+            kp = kp.reshape(B, taus[l1] * taus[l2], (2 * l1 + 1) * (2 * l2 + 1))
         out[l].append(torch.matmul(kp, C.t()))                                     # (B, t1*t2, 2l+1)
     res = []
     for l in range(lmax + 1):
@@ -251,6 +251,8 @@ def fragment_norm_stats(ff_frags):
     sig = []
     for f in ff_frags:
         a = f.detach().to(torch.float64).numpy()
+        if a.shape[1] == 0:
+            continue
         sig.append(np.std(np.linalg.norm(a, ord=2, axis=3), axis=(0, 2)))
     return np.concatenate(sig) if sig else np.zeros(0)
 
@@ -304,8 +306,12 @@ def cgbn_layer(frags, taus, tau_out, lmax, llls, W, stds=None, eps=1e-5, cnt=1.0
 # The reference's CPU algorithm with its own cost profile (materialised Kronecker products, one small bmm per triple on
 # split re/im tensors): this is what the CPU-baseline leg of the benchmark times.
 # --------------------------------------------------------------------------------------------------------------------
-def twin_forward(frags, taus, tau_out, lmax, llls, W, stds=None, eps=1e-5):
-    """Inference forward of one layer done the way ``CG_layers_python.py`` does it: per triple, repeat-materialised
+def twin_forward(frags, taus, tau_out, lmax, llls, W, stds=None, eps=1e-5, training=False, cnt=1.0):
+    """Forward of one layer done the way ``CG_layers_python.py`` does it (torch ops, so autograd gives the backward
+    with the same cost profile).  With ``training=True`` the fragment-norm statistics are first folded into a copy of
+    ``stds`` as ``MyBatchNormList.forward`` does (``CG_layers_python.py:172-179``) and ``(out, new_stds)`` is returned.
+
+    Per triple, repeat-materialised
     Kronecker product on separate real/imaginary tensors (``Complex_math.py:12-35,46-63``), batched matmul with the
     dense CG matrix repeated over the batch (``CG_layers_python.py:106-111``), concatenation per degree, division by
     max(eps, std), then ``Complex_bmm`` with the weights repeated over the batch (``CGutils.py:15-21``)."""
@@ -326,8 +332,12 @@ def twin_forward(frags, taus, tau_out, lmax, llls, W, stds=None, eps=1e-5):
         C = torch.from_numpy(cg_dense(l1, l2, l)).to(kr.dtype).repeat(B, 1, 1)
         new[l].append(torch.stack([torch.bmm(C, kr), torch.bmm(C, ki)], 3).permute(0, 2, 1, 3))
     ff = [torch.cat(v, 1) for v in new]
+    new_stds = None
     if stds is not None:
-        ff = fragment_norm_apply(ff, stds, eps)
+        new_stds = np.asarray(stds, dtype=np.float32)
+        if training:
+            new_stds = fragment_norm_update(new_stds, fragment_norm_stats(ff), cnt)
+        ff = fragment_norm_apply(ff, new_stds, eps)
     out, off = [], 0
     for l, f in enumerate(ff):
         k, to = f.shape[1], int(tau_out[l])
@@ -336,4 +346,4 @@ def twin_forward(frags, taus, tau_out, lmax, llls, W, stds=None, eps=1e-5):
         wr, wi = wl[..., 0], wl[..., 1]
         fr, fi = f[..., 0], f[..., 1]
         out.append(torch.stack([torch.bmm(wr, fr) - torch.bmm(wi, fi), torch.bmm(wr, fi) + torch.bmm(wi, fr)], 3))
-    return out
+    return (out, new_stds) if training else out
