@@ -75,6 +75,12 @@ struct PlanDev {
     const int64_t* cumO;
     const int64_t* cumW;
     const int* cumT;             // [lmax+2] running sum of tFF
+    // "slab" layout of an activation for the fused kernels: samples in groups of 32 (one per lane), inside a group
+    // fragment l starts at cumS[l] and holds its channels in tiles of `tile`: element (t, m) sits at
+    // ((t/tile * (2l+1) + m+l) * tile + t%tile); channels beyond tau_l are zero.  One element = 32 lanes of float2.
+    const int* cumSF;            // [lmax+2] input activation
+    const int* cumSO;            // [lmax+2] output activation
+    int nSF, nSO;
     const int* role1_begin;      // [lmax+2] triples whose first operand is fragment l
     const int* role1_list;
     const int* role2_begin;      // [lmax+2] triples whose second operand is fragment l
@@ -137,6 +143,7 @@ struct cgb200_plan {
     cgb200::PlanDev d{};
     std::vector<int> tF, tO, tFF, cumT;
     std::vector<int64_t> cumF, cumFF, cumO, cumW;
+    std::vector<int> cumSF, cumSO;
     std::vector<cgb200::TripleRec> triples;
     std::vector<cgb200::CellRec> cells;
     std::vector<int> cell_begin, triple_begin;
@@ -155,6 +162,9 @@ struct cgb200_plan {
     const int* d_gf_begin = nullptr;
     std::vector<int> gf_blocks;       // (fragment, first channel) per block of the input-gradient kernel
     const int* d_gf_blocks = nullptr;
+    std::vector<int> fwd_rows;        // (l, m+l) rows of the output, most expensive first (dynamic scheduling order)
+    const int* d_fwd_rows = nullptr;
+    int max_tau_out = 0;
     std::vector<void*> allocations;   // every cudaMalloc of the plan, freed on destroy
 };
 
@@ -220,6 +230,42 @@ __device__ __forceinline__ void gen_tile(float2 (&v)[TileShape<T, DW>::NV], cons
                 for (int j = 0; j < T; ++j) cfma(v[i * T + j], a, b[j]);
             }
         }
+    }
+}
+
+// The same generator for operands in slab layout (see PlanDev): S1 / S2 point at this lane's element (m = -l, channel
+// 0) of the t1 tile / t2 tile, so the T channels of a tile at one m are 32 float2 apart and consecutive m are T*32
+// apart: every inner-loop offset is a compile-time constant.  Works for global and for shared-memory slabs.
+template <int T, bool DW>
+__device__ __forceinline__ void gen_slab(float2 (&v)[TileShape<T, DW>::NV], const float* __restrict__ Crow,
+                                         const float2* __restrict__ S1, const float2* __restrict__ S2, int m, int l1,
+                                         int l2) {
+    constexpr int NV = TileShape<T, DW>::NV;
+    const int lo = max(-l2, m - l1), hi = min(l2, m + l1);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = make_float2(0.f, 0.f);
+    const float2* p2 = S2 + (lo + l2) * (T * 32);
+    const float2* p1 = S1 + (m - lo + l1) * (T * 32);
+    const float* pc = Crow + lo + l2;
+    for (int k = hi - lo; k >= 0; --k) {
+        const float c = *pc++;
+        float2 b[T];
+#pragma unroll
+        for (int j = 0; j < T; ++j) b[j] = p2[j * 32];
+#pragma unroll
+        for (int i = 0; i < T; ++i) {
+            float2 a = p1[i * 32];
+            a.x *= c;
+            a.y *= c;
+            if (DW) {
+                cfma(v[i], a, b[i]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < T; ++j) cfma(v[i * T + j], a, b[j]);
+            }
+        }
+        p2 += T * 32;
+        p1 -= T * 32;
     }
 }
 

@@ -1,18 +1,24 @@
 // The whole CG layer without a materialised mid activation: cgb200_layer_fwd / cgb200_layer_bwd.
 //
-// Layout idea: the activations are first transposed to sample-fastest order, Ft[element][Bp] (Bp = batch rounded up
-// to 32, padded with zeros), and every warp works on one group of 32 samples, one sample per lane.  Then everything
-// except the sample is uniform across a warp: the (l, l1, l2, m, m2) band loops never diverge, CG coefficients, mixing
-// weights and norm factors are warp-uniform loads, operand loads are 256-byte coalesced lines that stay in L1, and the
-// sums over the batch that the statistics and the weight gradient need are fixed-order warp-shuffle trees.  No float
-// atomics anywhere: every output element has exactly one owner and every sum a fixed order.
+// Layout idea: the activations are first rearranged into "slabs" (see PlanDev): samples in groups of 32, one sample
+// per lane, and inside a group every fragment stored tile-interleaved, [channel tile][m][channel in tile][32 lanes].
+// A warp works on one group, so everything except the sample is uniform across it: the (l, l1, l2, m, m2) band loops
+// never diverge, CG coefficients, mixing weights and norm factors are warp-uniform loads, operand loads are whole
+// 256-byte lines whose offsets inside the inner loops are compile-time constants, and the sums over the batch that the
+// statistics and the weight gradient need are fixed-order warp-shuffle trees.  No float atomics anywhere: every output
+// element has exactly one owner and every sum a fixed order, so results are bit-identical from run to run.
 //
-//   prep          F (and gO) -> Ft (gOt); 1/max(eps, std) per mid channel when the statistics are not being updated
+//   prep          F (and gO) -> slabs; 1/max(eps, std) per mid channel when the statistics are not being updated
 //   stats         training only: per mid channel std of |FF| over (b, m) from on-the-fly FF; moving average; 1/max(eps,.)
 //   fwd           O[b, l, :, m] = sum over the cells of degree l of  W_l[:, k] * (FF[b, k, m] / std_k)
+//                 two variants: rows (l, m) as independent blocks reading the slab through L1, or - when a group's
+//                 whole slab fits in shared memory - persistent blocks that stage the slab once and pull rows from a
+//                 cost-sorted queue
 //   grad_w        gW_l[to, (t1,t2)] = (1/std) sum_{b, m2} conj(F2[t2, m2]) * sum_m C[m, m2] conj(F1[t1, m-m2]) gO[to, m]
 //   grad_f        gF via gFF tiles built from gO and W in registers, contracted with conj(F) and C into per-warp
 //                 shared-memory accumulators that one block owns
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -20,8 +26,9 @@
 namespace cgb200 {
 
 constexpr int kWarp = 32;
-constexpr int kFwdWarps = 8;     // warps of a forward block = slices of the degree's cell list
-constexpr int kFwdTo = 16;       // output channels accumulated in registers per pass
+constexpr int kFwdWarps = 8;      // warps of a forward block = slices of the degree's cell list
+constexpr int kFwdTo = 16;        // output channels accumulated in registers per pass
+constexpr int kSlabWarps = 16;    // warps of a persistent forward block
 constexpr int kGwWarps = 4;
 constexpr int kGfWarpsMax = 8;
 
@@ -37,25 +44,37 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// prep: up to two transposes src[B][N] -> dst[N][Bp] in one launch (blockIdx.z picks the job), plus the norm factors.
+// prep: up to two rearrangements src[B][N] -> slab in one launch (blockIdx.z picks the job), the norm factors, and the
+// reset of the forward kernel's row counters.
 // ---------------------------------------------------------------------------------------------------------------
 struct PrepJob {
-    const float2* src;
-    float2* dst;
+    const float2* src;     // [B][N]
+    float2* dst;           // [G][nS][32]
     int64_t N;
+    const int64_t* cum;    // [lmax+2] fragment starts in src
+    const int* cumS;       // [lmax+2] fragment starts in the slab
+    const int* tau;        // [lmax+1]
+    int nS;
+    int has_pad;           // some fragment's channel count is not a multiple of the tile
 };
+
 __global__ void __launch_bounds__(256)
-prep_kernel(PrepJob j0, PrepJob j1, int B, int Bp, const float* __restrict__ stds, float eps, float* __restrict__ inv,
-            int n_inv) {
+prep_kernel(PrepJob j0, PrepJob j1, int lmax, int T, int B, const float* __restrict__ stds, float eps,
+            float* __restrict__ inv, int n_inv, int* __restrict__ counters, int n_counters) {
     __shared__ float2 tile[32][33];
     const PrepJob job = blockIdx.z == 0 ? j0 : j1;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    if (blockIdx.z == 0 && inv != nullptr) {   // norm factors ride along with job 0
+    const int64_t flat_block = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+    if (blockIdx.z == 0) {
         const int64_t stride = (int64_t)gridDim.x * gridDim.y * 256;
-        for (int64_t k = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + threadIdx.x; k < n_inv; k += stride)
-            inv[k] = stds ? 1.f / fmaxf(eps, stds[k]) : 1.f;
+        if (inv != nullptr)
+            for (int64_t k = flat_block * 256 + threadIdx.x; k < n_inv; k += stride)
+                inv[k] = stds ? 1.f / fmaxf(eps, stds[k]) : 1.f;
+        if (flat_block == 0)
+            for (int k = threadIdx.x; k < n_counters; k += 256) counters[k] = 0;
     }
     const int g = blockIdx.y;
+    float2* dst = job.dst + (int64_t)g * job.nS * 32;
     for (int64_t e0 = (int64_t)blockIdx.x * 32; e0 < job.N; e0 += (int64_t)gridDim.x * 32) {
         __syncthreads();
 #pragma unroll
@@ -68,7 +87,27 @@ prep_kernel(PrepJob j0, PrepJob j1, int B, int Bp, const float* __restrict__ std
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int64_t e = e0 + ty + 8 * k;
-            if (e < job.N) job.dst[e * Bp + g * 32 + tx] = tile[tx][ty + 8 * k];
+            if (e < job.N) {
+                const int l = find_degree(job.cum, lmax + 1, e);
+                const int n = 2 * l + 1;
+                const int r = (int)(e - job.cum[l]);
+                const int t = r / n, mi = r - t * n;
+                const int es = job.cumS[l] + ((t / T) * n + mi) * T + t % T;
+                dst[(int64_t)es * 32 + tx] = tile[tx][ty + 8 * k];
+            }
+        }
+    }
+    if (job.has_pad) {   // zero the channels that pad a fragment to whole tiles
+        for (int es = blockIdx.x * 8 + ty; es < job.nS; es += gridDim.x * 8) {
+            int lo = 0, hi = lmax + 1;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (job.cumS[mid] <= es) lo = mid; else hi = mid;
+            }
+            const int n = 2 * lo + 1;
+            const int r = es - job.cumS[lo];
+            const int t = (r / (T * n)) * T + r % T;
+            if (t >= job.tau[lo]) dst[(int64_t)es * 32 + tx] = make_float2(0.f, 0.f);
         }
     }
 }
@@ -88,25 +127,24 @@ __device__ __forceinline__ float moving_std_f(float old, double sigma, float cnt
 
 template <int T, bool DW>
 __global__ void __launch_bounds__(256)
-fused_stats_kernel(PlanDev P, const float2* __restrict__ Ft, float* __restrict__ stds, float* __restrict__ inv, float cnt,
-                   float eps, int B, int Bp) {
+fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__ stds, float* __restrict__ inv, float cnt,
+                   float eps, int B, int G) {
     constexpr int NV = TileShape<T, DW>::NV;
     __shared__ double red[8][NV][2];
-    const CellRec cell = P.cells[blockIdx.x];
+    const CellRec cell = P.cells[P.n_cells - 1 - blockIdx.x];   // the last degrees carry the long bands: start them first
     const TripleRec tr = P.triples[cell.triple];
     const int n = 2 * tr.l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = Bp >> 5;
     float s1[NV], s1c[NV], s2[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) s1[i] = s1c[i] = s2[i] = 0.f;
     const float* C = P.cg + tr.cgoff;
+    const int o1 = P.cumSF[tr.l1] + (cell.t1_0 / T) * n1 * T, o2 = P.cumSF[tr.l2] + (cell.t2_0 / T) * n2 * T;
     for (int task = warp; task < G * n; task += 8) {
         const int g = task / n, mi = task - g * n;
-        const float2* f1 = Ft + ((int64_t)tr.f1off + cell.t1_0 * n1) * Bp + g * 32 + lane;
-        const float2* f2 = Ft + ((int64_t)tr.f2off + cell.t2_0 * n2) * Bp + g * 32 + lane;
+        const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
         float2 v[NV];
-        gen_tile<T, DW>(v, C + mi * n2, f1, n1, f2, n2, mi - tr.l, tr.l1, tr.l2, Bp);
+        gen_slab<T, DW>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float nrm = v[i].x * v[i].x + v[i].y * v[i].y;
@@ -143,83 +181,119 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ Ft, float* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// forward: block = (degree l, m, sample group); its warps take the cells of the degree round-robin, each lane keeps
-// up to kFwdTo output channels of its sample in registers; the warps' partial sums are added in index order.
+// forward.  One output row = (degree l, m) for one sample group.  The warps of a block take the cells of the degree
+// round-robin, each lane keeps up to kFwdTo output channels of its sample in registers, and the warps' partial sums
+// are added in warp order.  `slab` is this lane's view of the group's input slab (global or shared memory).
 // ---------------------------------------------------------------------------------------------------------------
-template <int T, bool DW>
-__global__ void __launch_bounds__(kFwdWarps * kWarp)
-fused_fwd_kernel(PlanDev P, const float2* __restrict__ Ft, const float2* __restrict__ W, const float* __restrict__ inv,
-                 float2* __restrict__ O, int B, int Bp) {
+template <int T, bool DW, int NW>
+__device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restrict__ slab, const float2* __restrict__ W,
+                                        const float* __restrict__ inv, float2* __restrict__ O, float2* __restrict__ red,
+                                        int red_to, int l, int mi, int b, int B, int warp, int lane) {
     constexpr int NV = TileShape<T, DW>::NV;
-    __shared__ float2 red[kFwdWarps][kFwdTo][kWarp];
-    // blockIdx.x enumerates (l, m): index l*l + (m + l)
-    int l = (int)sqrtf((float)blockIdx.x);
-    while ((l + 1) * (l + 1) <= (int)blockIdx.x) ++l;
-    while (l * l > (int)blockIdx.x) --l;
-    const int mi = blockIdx.x - l * l;
     const int n = 2 * l + 1;
-    const int g = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int to_n = P.tO[l];
-    if (to_n == 0) return;
     const int tff = P.tFF[l];
     const int c_begin = P.cell_begin[l], c_end = P.cell_begin[l + 1];
     const float2* Wl = W + P.cumW[l];
-    const int b = g * 32 + lane;
-
-    for (int to0 = 0; to0 < to_n; to0 += kFwdTo) {
+    const int step = min(kFwdTo, red_to);
+    for (int to0 = 0; to0 < to_n; to0 += step) {
         float2 o[kFwdTo];
 #pragma unroll
         for (int t = 0; t < kFwdTo; ++t) o[t] = make_float2(0.f, 0.f);
-        for (int c = c_begin + warp; c < c_end; c += kFwdWarps) {
+        for (int c = c_begin + warp; c < c_end; c += NW) {
             const CellRec cell = P.cells[c];
             const TripleRec tr = P.triples[cell.triple];
             const int n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
-            const float2* f1 = Ft + ((int64_t)tr.f1off + cell.t1_0 * n1) * Bp + g * 32 + lane;
-            const float2* f2 = Ft + ((int64_t)tr.f2off + cell.t2_0 * n2) * Bp + g * 32 + lane;
+            const int o1 = P.cumSF[tr.l1] + (cell.t1_0 / T) * n1 * T, o2 = P.cumSF[tr.l2] + (cell.t2_0 / T) * n2 * T;
             float2 v[NV];
-            gen_tile<T, DW>(v, P.cg + tr.cgoff + mi * n2, f1, n1, f2, n2, mi - l, tr.l1, tr.l2, Bp);
+            gen_slab<T, DW>(v, P.cg + tr.cgoff + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - l, tr.l1, tr.l2);
+            const float* iv = inv + tr.kglob;
+            const float2* w0 = Wl + (int64_t)to0 * tff + tr.toff;
 #pragma unroll
             for (int idx = 0; idx < NV; ++idx) {
                 if (!tile_valid<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau1, tr.tau2)) continue;   // warp-uniform
                 const int ch = tile_channel<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau2);
-                const float s = __ldg(inv + tr.kglob + ch);
+                const float s = __ldg(iv + ch);
                 const float2 x = make_float2(v[idx].x * s, v[idx].y * s);
-                const float2* w = Wl + (int64_t)to0 * tff + tr.toff + ch;
+                const float2* w = w0 + ch;
 #pragma unroll
                 for (int t = 0; t < kFwdTo; ++t)
-                    if (to0 + t < to_n) cfma(o[t], __ldg(w + (int64_t)t * tff), x);
+                    if (t < step && to0 + t < to_n) cfma(o[t], __ldg(w + (int64_t)t * tff), x);
             }
         }
-        __syncthreads();   // protects `red` from the previous pass
+        __syncthreads();   // protects `red` from the previous pass / row
 #pragma unroll
-        for (int t = 0; t < kFwdTo; ++t) red[warp][t][lane] = o[t];
+        for (int t = 0; t < kFwdTo; ++t)
+            if (t < step) red[(warp * red_to + t) * 32 + lane] = o[t];
         __syncthreads();
-        for (int t = warp; t < kFwdTo && to0 + t < to_n; t += kFwdWarps) {
-            float2 s = red[0][t][lane];
-#pragma unroll
-            for (int w = 1; w < kFwdWarps; ++w) {
-                s.x += red[w][t][lane].x;
-                s.y += red[w][t][lane].y;
+        for (int t = warp; t < step && to0 + t < to_n; t += NW) {
+            float2 s = red[t * 32 + lane];
+            for (int w = 1; w < NW; ++w) {
+                const float2 q = red[(w * red_to + t) * 32 + lane];
+                s.x += q.x;
+                s.y += q.y;
             }
             if (b < B) O[(int64_t)b * P.n_O + P.cumO[l] + (int64_t)(to0 + t) * n + mi] = s;
         }
     }
 }
 
+// rows as independent blocks; the slab is read through L1.  grid = (rows, groups)
+template <int T, bool DW>
+__global__ void __launch_bounds__(kFwdWarps * kWarp)
+fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restrict__ SF, const float2* __restrict__ W,
+                 const float* __restrict__ inv, float2* __restrict__ O, int B) {
+    __shared__ float2 red[kFwdWarps * kFwdTo * kWarp];
+    const int l = rows[2 * blockIdx.x], mi = rows[2 * blockIdx.x + 1];
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    fwd_row<T, DW, kFwdWarps>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, kFwdTo, l, mi, g * 32 + lane, B, warp,
+                              lane);
+}
+
+// persistent blocks: block (p, g) copies group g's slab into shared memory once, then pulls rows (most expensive
+// first) from the group's counter until none is left.  grid = (blocks per group, groups)
+template <int T, bool DW>
+__global__ void __launch_bounds__(kSlabWarps * kWarp)
+fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const float2* __restrict__ SF,
+                      const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ O, int B,
+                      int* __restrict__ counters, int red_to) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int next_row;
+    float2* slab = reinterpret_cast<float2*>(smem_raw);
+    float2* red = slab + (size_t)P.nSF * 32;
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const float4* src = reinterpret_cast<const float4*>(SF + (int64_t)g * P.nSF * 32);
+        float4* dst = reinterpret_cast<float4*>(slab);
+        for (int i = threadIdx.x; i < P.nSF * 16; i += blockDim.x) dst[i] = src[i];
+    }
+    for (;;) {
+        __syncthreads();   // slab staged / previous row finished with next_row
+        if (threadIdx.x == 0) next_row = atomicAdd(counters + g, 1);
+        __syncthreads();
+        const int r = next_row;
+        if (r >= n_rows) break;
+        fwd_row<T, DW, kSlabWarps>(P, slab + lane, W, inv, O, red, red_to, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B, warp,
+                                   lane);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
-// weight gradient, full product.  Warp-task = (triple, I consecutive t1, one t2 tile, one tau_out tile).  A lane keeps
-// acc[o][i][j] for its own sample; the sample groups are visited in order and the lanes summed at the end.
+// weight gradient, full product.  Warp-task = (triple, I consecutive t1 inside one tile, one t2 tile, one tau_out
+// tile).  A lane keeps acc[o][i][j] for its own sample; the sample groups are visited in order and the lanes summed at
+// the end.  Tasks are taken from the end of the list first: the high degrees have the long bands.
 // ---------------------------------------------------------------------------------------------------------------
 template <int T, int I>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
-fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ Ft,
-                const float2* __restrict__ gOt, const float* __restrict__ inv, float2* __restrict__ gW, int Bp) {
+fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ SF,
+                const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G) {
+    constexpr int NI = (T + I - 1) / I;   // t1 groups per tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int task = blockIdx.x * kGwWarps + warp;
-    if (task >= n_tasks) return;
-    // triple of this task: last k with task_begin[k] <= task
-    int lo = 0, hi = P.n_triples;
+    const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
+    if (task < 0) return;
+    int lo = 0, hi = P.n_triples;   // triple of this task: last k with task_begin[k] <= task
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (task_begin[mid] <= task) lo = mid; else hi = mid;
@@ -229,12 +303,16 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
     const int to_n = P.tO[l], tff = P.tFF[l];
     const int no = (to_n + T - 1) / T;
     int r = task - task_begin[lo];
-    const int io = r % no;
+    const int qo = r % no;
     r /= no;
-    const int ij = r % tr.nt2, ii = r / tr.nt2;
-    const int t1_0 = ii * I, t2_0 = ij * T, to0 = io * T;
+    const int q2 = r % tr.nt2;
+    r /= tr.nt2;
+    const int gi = r % NI, q1 = r / NI;
+    const int j0 = gi * I;
     const float* C = P.cg + tr.cgoff;
-    const int G = Bp >> 5;
+    int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
+#pragma unroll
+    for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
 
     float2 acc[T][I][T];
 #pragma unroll
@@ -245,9 +323,9 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
             for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
 
     for (int g = 0; g < G; ++g) {
-        const float2* f1 = Ft + ((int64_t)tr.f1off + t1_0 * n1) * Bp + g * 32 + lane;
-        const float2* f2 = Ft + ((int64_t)tr.f2off + t2_0 * n2) * Bp + g * 32 + lane;
-        const float2* go = gOt + (P.cumO[l] + (int64_t)to0 * n) * Bp + g * 32 + lane;
+        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
+        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
+        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l] + qo * n * T) * 32 + lane;
         for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
             float2 Y[T][I];
 #pragma unroll
@@ -255,25 +333,32 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
 #pragma unroll
                 for (int i = 0; i < I; ++i) Y[o][i] = make_float2(0.f, 0.f);
             const int mlo = max(-l, m2 - tr.l1), mhi = min(l, m2 + tr.l1);
-            for (int m = mlo; m <= mhi; ++m) {
-                const float c = C[(m + l) * n2 + m2 + tr.l2];
+            const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
+            const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
+            const float2* pg = go + (mlo + l) * (T * 32);
+            for (int k = mhi - mlo; k >= 0; --k) {
+                const float c = *pc;
                 float2 a[I];
 #pragma unroll
                 for (int i = 0; i < I; ++i) {
-                    a[i] = f1[(int64_t)(i * n1 + (m - m2) + tr.l1) * Bp];
+                    a[i] = p1[jrow[i] * 32];
                     a[i].x *= c;
                     a[i].y *= c;
                 }
 #pragma unroll
                 for (int o = 0; o < T; ++o) {
-                    const float2 gv = go[(int64_t)(o * n + m + l) * Bp];
+                    const float2 gv = pg[o * 32];
 #pragma unroll
                     for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
                 }
+                pc += n2;
+                p1 += T * 32;
+                pg += T * 32;
             }
+            const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
             float2 bj[T];
 #pragma unroll
-            for (int j = 0; j < T; ++j) bj[j] = f2[(int64_t)(j * n2 + m2 + tr.l2) * Bp];
+            for (int j = 0; j < T; ++j) bj[j] = p2[j * 32];
 #pragma unroll
             for (int o = 0; o < T; ++o)
 #pragma unroll
@@ -289,10 +374,11 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
 #pragma unroll
             for (int j = 0; j < T; ++j) {
                 const float sx = warp_sum(acc[o][i][j].x), sy = warp_sum(acc[o][i][j].y);
-                if (lane == 0 && to0 + o < to_n && t1_0 + i < tr.tau1 && t2_0 + j < tr.tau2) {
-                    const int ch = (t1_0 + i) * tr.tau2 + t2_0 + j;
+                const int t1 = q1 * T + j0 + i, t2 = q2 * T + j, to = qo * T + o;
+                if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
+                    const int ch = t1 * tr.tau2 + t2;
                     const float s = inv[tr.kglob + ch];
-                    gW[P.cumW[l] + (int64_t)(to0 + o) * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
+                    gW[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
                 }
             }
 }
@@ -300,11 +386,11 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
 // weight gradient, depthwise product: warp-task = (triple, t tile, tau_out tile); FF tile generated directly.
 template <int T>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
-fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ Ft,
-                   const float2* __restrict__ gOt, const float* __restrict__ inv, float2* __restrict__ gW, int Bp) {
+fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ SF,
+                   const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int task = blockIdx.x * kGwWarps + warp;
-    if (task >= n_tasks) return;
+    const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
+    if (task < 0) return;
     int lo = 0, hi = P.n_triples;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -315,24 +401,22 @@ fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, c
     const int to_n = P.tO[l], tff = P.tFF[l];
     const int no = (to_n + T - 1) / T;
     const int r = task - task_begin[lo];
-    const int io = r % no, ii = r / no;
-    const int t0 = ii * T, to0 = io * T;
-    const int G = Bp >> 5;
+    const int qo = r % no, q = r / no;
     float2 acc[T][T];
 #pragma unroll
     for (int o = 0; o < T; ++o)
 #pragma unroll
         for (int i = 0; i < T; ++i) acc[o][i] = make_float2(0.f, 0.f);
     for (int g = 0; g < G; ++g) {
-        const float2* f1 = Ft + ((int64_t)tr.f1off + t0 * n1) * Bp + g * 32 + lane;
-        const float2* f2 = Ft + ((int64_t)tr.f2off + t0 * n2) * Bp + g * 32 + lane;
-        const float2* go = gOt + (P.cumO[l] + (int64_t)to0 * n) * Bp + g * 32 + lane;
+        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q * n1 * T) * 32 + lane;
+        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q * n2 * T) * 32 + lane;
+        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l] + qo * n * T) * 32 + lane;
         for (int mi = 0; mi < n; ++mi) {
             float2 v[T];
-            gen_tile<T, true>(v, P.cg + tr.cgoff + mi * n2, f1, n1, f2, n2, mi - l, tr.l1, tr.l2, Bp);
+            gen_slab<T, true>(v, P.cg + tr.cgoff + mi * n2, f1, f2, mi - l, tr.l1, tr.l2);
 #pragma unroll
             for (int o = 0; o < T; ++o) {
-                const float2 gv = go[(int64_t)(o * n + mi) * Bp];
+                const float2 gv = go[(mi * T + o) * 32];
 #pragma unroll
                 for (int i = 0; i < T; ++i) cfma_conj(acc[o][i], v[i], gv);
             }
@@ -343,25 +427,28 @@ fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, c
 #pragma unroll
         for (int i = 0; i < T; ++i) {
             const float sx = warp_sum(acc[o][i].x), sy = warp_sum(acc[o][i].y);
-            if (lane == 0 && to0 + o < to_n && t0 + i < tr.tau1) {
-                const float s = inv[tr.kglob + t0 + i];
-                gW[P.cumW[l] + (int64_t)(to0 + o) * tff + tr.toff + t0 + i] = make_float2(sx * s, sy * s);
+            const int t = q * T + i, to = qo * T + o;
+            if (lane == 0 && to < to_n && t < tr.tau1) {
+                const float s = inv[tr.kglob + t];
+                gW[P.cumW[l] + (int64_t)to * tff + tr.toff + t] = make_float2(sx * s, sy * s);
             }
         }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// input gradient.  Block = (fragment lt, kGfOut of its channels, sample group) and owns those elements of gF.  Its
-// warps take the fragment's entries (triple, role, tile of the other operand) round-robin; for every m a warp builds
-// the gFF tile  g = (1/std) sum_to conj(W[to, k]) gO[to, m]  in registers and contracts it with conj(other operand)
-// and C into its private shared-memory accumulator acc[channel][m_t][lane] (CGNet/cudaCG/cudaCG_FNWMM.cu:169-211
-// followed by cudaCG_sparse.cu:231-289, without the trip of gFF through memory).
+// input gradient.  Block = (fragment lt, kGfOut of its channels, sample group) and owns those elements of gF.  All
+// warps walk the fragment's entries (triple, role, tile of the other operand) together and split the m of the entry,
+// so the other operand's tile stays hot in L1; for its m a warp builds the gFF tile
+//     g = (1/std) sum_to conj(W[to, k]) gO[to, m]
+// in registers and contracts it with conj(other operand) and C into its private shared-memory accumulator
+// acc[channel][m_t][lane] (CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289, without the
+// trip of gFF through memory).  The warps' accumulators are added in warp order at the end.
 // ---------------------------------------------------------------------------------------------------------------
 template <int T, bool DW>
 __global__ void __launch_bounds__(kGfWarpsMax * kWarp)
 fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __restrict__ entry_begin,
-                const int* __restrict__ block_frag, const float2* __restrict__ Ft, const float2* __restrict__ gOt,
-                const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ gF, int B, int Bp) {
+                const int* __restrict__ block_frag, const float2* __restrict__ SF, const float2* __restrict__ SG,
+                const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ gF, int B) {
     constexpr int OUT = kGfOut;
     constexpr int TI = DW ? 1 : T;   // tile of the other operand
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -374,22 +461,31 @@ fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __res
     for (int i = lane; i < OUT * nt * 32; i += 32) acc[i] = make_float2(0.f, 0.f);
     __syncwarp();
     const int tau_t = P.tF[lt];
+    const float2* slabF = SF + (int64_t)g * P.nSF * 32 + lane;
+    const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
 
-    for (int e = entry_begin[lt] + warp; e < entry_begin[lt + 1]; e += nwarps) {
+    for (int e = entry_begin[lt]; e < entry_begin[lt + 1]; ++e) {
         const GfEntry en = entries[e];
         const TripleRec tr = P.triples[en.triple];
         const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
+        if (warp >= n) continue;
         const int to_n = P.tO[l], tff = P.tFF[l];
         const float* C = P.cg + tr.cgoff;
-        const float2* go = gOt + P.cumO[l] * Bp + g * 32 + lane;
+        const float2* go = slabG + P.cumSO[l] * 32;
         const float2* Wl = W + P.cumW[l] + tr.toff;
         const bool first = en.role == 0;   // the owned fragment is the first operand of this triple
-        // other operand rows
-        const int in0 = DW ? t_0 : en.in0;
-        const float2* fo = first ? Ft + ((int64_t)tr.f2off + in0 * n2) * Bp + g * 32 + lane
-                                 : Ft + ((int64_t)tr.f1off + in0 * n1) * Bp + g * 32 + lane;
+        const int in0 = DW ? (t_0 / T) * T : en.in0;   // first channel of the other operand's tile
+        const int lo_ = first ? tr.l2 : tr.l1, no_ = first ? n2 : n1;
+        const float2* fo = slabF + (P.cumSF[lo_] + (in0 / T) * no_ * T) * 32;
         const int tau_o = first ? tr.tau2 : tr.tau1;
-        // mid channel and norm factor of every tile entry (out channel a, other channel c)
+        // depthwise: the other operand's channel equals the owned channel; its element for m index 0, per owned channel
+        const float2* fdw[OUT];
+#pragma unroll
+        for (int a = 0; a < OUT; ++a) {
+            const int t = min(t_0 + a, max(tau_t - 1, 0));
+            fdw[a] = slabF + (P.cumSF[lo_] + ((t / T) * no_) * T + t % T) * 32;
+        }
+        // mid channel and norm factor of every tile entry (owned channel a, other channel c)
         int ch[OUT][TI];
         float sc[OUT][TI];
 #pragma unroll
@@ -401,7 +497,7 @@ fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __res
                 ch[a][c] = ok ? (DW ? t_0 + a : t1 * tr.tau2 + t2) : -1;
                 sc[a][c] = ok ? inv[tr.kglob + ch[a][c]] : 0.f;
             }
-        for (int mi = 0; mi < n; ++mi) {
+        for (int mi = warp; mi < n; mi += nwarps) {
             const int m = mi - l;
             float2 gt[OUT][TI];
 #pragma unroll
@@ -409,7 +505,7 @@ fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __res
 #pragma unroll
                 for (int c = 0; c < TI; ++c) gt[a][c] = make_float2(0.f, 0.f);
             for (int to = 0; to < to_n; ++to) {
-                const float2 gv = go[(int64_t)(to * n + mi) * Bp];
+                const float2 gv = go[(((to / T) * n + mi) * T + to % T) * 32];
                 const float2* w = Wl + (int64_t)to * tff;
 #pragma unroll
                 for (int a = 0; a < OUT; ++a)
@@ -425,12 +521,14 @@ fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __res
                     gt[a][c].y *= sc[a][c];
                 }
             const int lo = max(-tr.l2, m - tr.l1), hi = min(tr.l2, m + tr.l1);
-            for (int m2 = lo; m2 <= hi; ++m2) {
-                const float cg = C[mi * n2 + m2 + tr.l2];
-                // position of the other operand's element and of the owned element along their m axes
-                const int mo = first ? (m2 + tr.l2) : (m - m2 + tr.l1);
-                const int mt = first ? (m - m2 + tr.l1) : (m2 + tr.l2);
-                const int so = first ? n2 : n1;
+            const float* pc = C + mi * n2 + lo + tr.l2;
+            // the other operand's m index runs up (its own m2) when the owned fragment is first, down otherwise;
+            // the owned element's m index runs the other way
+            const int dir = first ? 1 : -1;
+            const float2* po = fo + (first ? lo + tr.l2 : m - lo + tr.l1) * (T * 32);
+            float2* pa = acc + (first ? m - lo + tr.l1 : lo + tr.l2) * 32 + lane;
+            for (int k = hi - lo; k >= 0; --k) {
+                const float cg = *pc++;
                 float2 x[OUT];
 #pragma unroll
                 for (int a = 0; a < OUT; ++a) x[a] = make_float2(0.f, 0.f);
@@ -439,28 +537,30 @@ fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __res
 #pragma unroll
                     for (int a = 0; a < OUT; ++a)
                         if (ch[a][0] >= 0) {
-                            const float2 f = fo[(int64_t)(a * so + mo) * Bp];
+                            const float2 f = fdw[a][(po - fo)];
                             cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), gt[a][0]);
                         }
                 } else {
 #pragma unroll
                     for (int c = 0; c < TI; ++c) {
-                        float2 f = fo[(int64_t)(c * so + mo) * Bp];
+                        float2 f = po[c * 32];
                         f.x *= cg;
                         f.y *= cg;
 #pragma unroll
                         for (int a = 0; a < OUT; ++a)
-                            if (ch[a][c] >= 0) cfma_conj(x[a], f, gt[a][c]);   // masked entries may hold anything
+                            if (ch[a][c] >= 0) cfma_conj(x[a], f, gt[a][c]);
                     }
                 }
 #pragma unroll
                 for (int a = 0; a < OUT; ++a) {
-                    float2* p = acc + (a * nt + mt) * 32 + lane;
+                    float2* p = pa + a * nt * 32;
                     float2 cur = *p;
                     cur.x += x[a].x;
                     cur.y += x[a].y;
                     *p = cur;
                 }
+                po += dir * (T * 32);
+                pa -= dir * 32;
             }
         }
     }
@@ -487,27 +587,28 @@ using namespace cgb200;
 namespace {
 
 struct Workspace {
-    float2* Ft;
-    float2* Gt;     // gOt in the backward
+    float2* SF;
+    float2* SG;     // slab of gO in the backward
     float* inv;
+    int* counters;  // one row counter per sample group
     int64_t bytes;
 };
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
-// Ft and gOt get kMaxTile*(2*lmax+1) spare rows: masked tile entries read (and discard) rows past a fragment's end.
 Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
-    const int64_t Bp = (B + 31) / 32 * 32;
-    const int64_t pad = (int64_t)kMaxTile * p->max_n;
+    const int64_t G = (B + 31) / 32;
     Workspace w;
     int64_t off = 0;
     char* c = (char*)base;
-    w.Ft = (float2*)(c + off);
-    off += align256((p->d.n_F + pad) * Bp * (int64_t)sizeof(float2));
-    w.Gt = (float2*)(c + off);
-    off += align256((p->d.n_O + pad) * Bp * (int64_t)sizeof(float2));
+    w.SF = (float2*)(c + off);
+    off += align256(std::max<int64_t>(p->d.nSF, 1) * G * 32 * (int64_t)sizeof(float2));
+    w.SG = (float2*)(c + off);
+    off += align256(std::max<int64_t>(p->d.nSO, 1) * G * 32 * (int64_t)sizeof(float2));
     w.inv = (float*)(c + off);
     off += align256(std::max<int64_t>(p->d.sum_tff, 1) * (int64_t)sizeof(float));
+    w.counters = (int*)(c + off);
+    off += align256(G * (int64_t)sizeof(int));
     w.bytes = off;
     return w;
 }
@@ -515,7 +616,7 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
 int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_bytes) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(p->d.has_out, "the plan was created without tau_out");
-    CGB_REQUIRE(B >= 0 && B <= (1ll << 20), "batch size out of range (at most 2^20 samples per call)");
+    CGB_REQUIRE(B >= 0 && B <= 65535 * 32, "batch size out of range (at most 2097120 samples per call of the fused layer)");
     int dev = -1;
     CGB_CUDA(cudaGetDevice(&dev));
     CGB_REQUIRE(dev == p->device, "the plan belongs to another CUDA device than the current one");
@@ -532,19 +633,25 @@ int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_byte
 
 bool al8(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 7) == 0; }
 
-int launch_prep(const PrepJob& a, const PrepJob& b, int njobs, int B, int Bp, const float* stds, float eps, float* inv,
-                int n_inv, cudaStream_t st) {
+bool has_pad(const std::vector<int>& tau, int T) {
+    for (int t : tau)
+        if (t % T) return true;
+    return false;
+}
+
+int launch_prep(const cgb200_plan* p, const PrepJob& a, const PrepJob& b, int njobs, int B, int G, const float* stds, float eps,
+                float* inv, int* counters, cudaStream_t st) {
     const int64_t maxN = std::max(a.N, njobs > 1 ? b.N : 0);
-    const int gx = (int)std::min<int64_t>((maxN + 31) / 32, 4096);
+    const int gx = (int)std::min<int64_t>((maxN + 31) / 32, 2048);
     launch_begin(K_PREP, st);
-    prep_kernel<<<dim3(std::max(gx, 1), Bp / 32, njobs), 256, 0, st>>>(a, b, B, Bp, stds, eps, inv, n_inv);
+    prep_kernel<<<dim3(std::max(gx, 1), G, njobs), 256, 0, st>>>(a, b, p->d.lmax, p->d.tile, B, stds, eps, inv, p->d.sum_tff,
+                                                              counters, G);
     launch_end(K_PREP, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;
 }
 
 }  // namespace
-
 
 template <int T>
 struct GwI {
@@ -572,23 +679,42 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     CGB_REQUIRE(F != nullptr && O != nullptr && (W != nullptr || p->d.w_len == 0), "null buffer");
     CGB_REQUIRE(al8(F) && al8(W) && al8(O), "buffers must be 8-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    const int Bp = (int)((B + 31) / 32 * 32);
+    const int G = (int)((B + 31) / 32);
     Workspace ws = carve(p, B, workspace);
+    const int T = p->d.tile;
 
-    PrepJob jf{(const float2*)F, ws.Ft, p->d.n_F}, none{nullptr, nullptr, 0};
-    if ((rc = launch_prep(jf, none, 1, (int)B, Bp, fn ? stds : nullptr, eps, update ? nullptr : ws.inv, p->d.sum_tff, st)))
+    PrepJob jf{(const float2*)F, ws.SF, p->d.n_F, p->d.cumF, p->d.cumSF, p->d.tF, p->d.nSF, has_pad(p->tF, T) ? 1 : 0};
+    PrepJob none{};
+    if ((rc = launch_prep(p, jf, none, 1, (int)B, G, fn ? stds : nullptr, eps, update ? nullptr : ws.inv, ws.counters, st)))
         return rc;
     if (update && p->d.n_cells > 0) {
         launch_begin(K_STATS, st);
-        CGB_DISPATCH_TILE(p->d.tile, p->d.depthwise,
-                          (fused_stats_kernel<TT, DD><<<p->d.n_cells, 256, 0, st>>>(p->d, ws.Ft, stds, ws.inv, cnt, eps, (int)B, Bp)));
+        CGB_DISPATCH_TILE(T, p->d.depthwise,
+                          (fused_stats_kernel<TT, DD><<<p->d.n_cells, 256, 0, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G)));
         launch_end(K_STATS, st);
         CGB_CUDA(cudaGetLastError());
     }
-    const dim3 grid((p->d.lmax + 1) * (p->d.lmax + 1), Bp / 32);
+    const int n_rows = (int)p->fwd_rows.size() / 2;
+    if (n_rows == 0) return CGB200_OK;
+    // persistent shared-memory variant when one group's slab (plus the reduction buffer) fits in an SM
+    const int red_to = std::min(kFwdTo, std::max(p->max_tau_out, 1));
+    const size_t slab_bytes = (size_t)p->d.nSF * 32 * sizeof(float2);
+    const size_t smem = slab_bytes + (size_t)kSlabWarps * red_to * 32 * sizeof(float2);
+    const char* force = getenv("CGB200_FWD");
+    const bool use_slab = force ? (force[0] == 's') : (smem <= 200 * 1024 && G <= p->num_sms);
     launch_begin(K_FWD, st);
-    CGB_DISPATCH_TILE(p->d.tile, p->d.depthwise,
-                      (fused_fwd_kernel<TT, DD><<<grid, kFwdWarps * kWarp, 0, st>>>(p->d, ws.Ft, (const float2*)W, ws.inv, (float2*)O, (int)B, Bp)));
+    if (use_slab && smem <= 227 * 1024) {
+        const int per_group = std::max(1, std::min(n_rows, p->num_sms / G));
+        CGB_DISPATCH_TILE(T, p->d.depthwise, {
+            auto kern = fused_fwd_slab_kernel<TT, DD>;
+            CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<dim3(per_group, G), kSlabWarps * kWarp, smem, st>>>(p->d, p->d_fwd_rows, n_rows, ws.SF, (const float2*)W, ws.inv,
+                                                                    (float2*)O, (int)B, ws.counters, red_to);
+        });
+    } else {
+        CGB_DISPATCH_TILE(T, p->d.depthwise,
+                          (fused_fwd_kernel<TT, DD><<<dim3(n_rows, G), kFwdWarps * kWarp, 0, st>>>(p->d, p->d_fwd_rows, ws.SF, (const float2*)W, ws.inv, (float2*)O, (int)B)));
+    }
     launch_end(K_FWD, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;
@@ -612,28 +738,29 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     }
     CGB_REQUIRE(F != nullptr && gF != nullptr && (gO != nullptr || p->d.n_O == 0), "null buffer");
     CGB_REQUIRE(p->d.w_len == 0 || (W != nullptr && gW != nullptr), "W or gW is null");
-    const int Bp = (int)((B + 31) / 32 * 32);
+    const int G = (int)((B + 31) / 32);
     Workspace ws = carve(p, B, workspace);
+    const int T = p->d.tile;
 
-    PrepJob jf{(const float2*)F, ws.Ft, p->d.n_F}, jg{(const float2*)gO, ws.Gt, p->d.n_O};
-    if ((rc = launch_prep(jf, jg, p->d.n_O > 0 ? 2 : 1, (int)B, Bp, fn ? stds : nullptr, eps, ws.inv, p->d.sum_tff, st))) return rc;
+    PrepJob jf{(const float2*)F, ws.SF, p->d.n_F, p->d.cumF, p->d.cumSF, p->d.tF, p->d.nSF, has_pad(p->tF, T) ? 1 : 0};
+    PrepJob jg{(const float2*)gO, ws.SG, p->d.n_O, p->d.cumO, p->d.cumSO, p->d.tO, p->d.nSO, has_pad(p->tO, T) ? 1 : 0};
+    if ((rc = launch_prep(p, jf, jg, p->d.n_O > 0 ? 2 : 1, (int)B, G, fn ? stds : nullptr, eps, ws.inv, ws.counters, st))) return rc;
 
-    // weight gradient
+    // weight gradient: every (to, k) of every degree with both output and mid channels belongs to exactly one task
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
     if (n_tasks > 0) {
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         launch_begin(K_GW, st);
         if (p->d.depthwise) {
-            CGB_DISPATCH_TILE(p->d.tile, false,
-                              (fused_gw_dw_kernel<TT><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.Ft, ws.Gt, ws.inv, (float2*)gW, Bp)));
+            CGB_DISPATCH_TILE(T, false,
+                              (fused_gw_dw_kernel<TT><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G)));
         } else {
-            CGB_DISPATCH_TILE(p->d.tile, false,
-                              (fused_gw_kernel<TT, GwI<TT>::value><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.Ft, ws.Gt, ws.inv, (float2*)gW, Bp)));
+            CGB_DISPATCH_TILE(T, false,
+                              (fused_gw_kernel<TT, GwI<TT>::value><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G)));
         }
         launch_end(K_GW, st);
         CGB_CUDA(cudaGetLastError());
     }
-    // degrees with output channels but no mid channels have no weights; every other weight was written above
 
     // input gradient
     if (p->d.n_F > 0) {
@@ -646,10 +773,10 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         }
         const size_t smem = per_warp * nwarps;
         launch_begin(K_GF, st);
-        CGB_DISPATCH_TILE(p->d.tile, p->d.depthwise, {
+        CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = fused_gf_kernel<TT, DD>;
             if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<dim3(nblk, Bp / 32), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_entries, p->d_gf_begin, p->d_gf_blocks, ws.Ft, ws.Gt, (const float2*)W, ws.inv, (float2*)gF, (int)B, Bp);
+            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_entries, p->d_gf_begin, p->d_gf_blocks, ws.SF, ws.SG, (const float2*)W, ws.inv, (float2*)gF, (int)B);
         });
         launch_end(K_GF, st);
         CGB_CUDA(cudaGetLastError());

@@ -357,6 +357,40 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         p->cell_begin[l + 1] = std::max(p->cell_begin[l + 1], p->cell_begin[l]);
     }
 
+    // slab layouts (tile-interleaved, see PlanDev) and the forward kernel's row order
+    p->cumSF.assign(L1 + 1, 0);
+    p->cumSO.assign(L1 + 1, 0);
+    for (int l = 0; l < L1; ++l) {
+        const int64_t a = (int64_t)p->cumSF[l] + (int64_t)((p->tF[l] + T - 1) / T) * T * (2 * l + 1);
+        const int64_t b = (int64_t)p->cumSO[l] + (int64_t)((p->tO[l] + T - 1) / T) * T * (2 * l + 1);
+        CGB_REQUIRE(a < (1ll << 26) && b < (1ll << 26), "activation too long for the fused kernels");
+        p->cumSF[l + 1] = (int)a;
+        p->cumSO[l + 1] = (int)b;
+        p->max_tau_out = std::max(p->max_tau_out, p->tO[l]);
+    }
+    {
+        std::vector<std::pair<double, int>> rows;   // (cost, l*(2*lmax+1)+mi)
+        for (int l = 0; l < L1; ++l) {
+            if (p->tO[l] == 0) continue;
+            for (int mi = 0; mi < 2 * l + 1; ++mi) {
+                double cost = 0;
+                for (int k = p->triple_begin[l]; k < p->triple_begin[l + 1]; ++k) {
+                    const TripleRec& t = p->triples[k];
+                    const int m = mi - l;
+                    const int band = std::min(t.l2, m + t.l1) - std::max(-t.l2, m - t.l1) + 1;
+                    const double cells = (double)t.nt1 * t.nt2;
+                    cost += cells * (band * (dw ? 6.0 * T : 4.0 * T * T + 4.0 * T) + (dw ? T : T * T) * (4.0 * p->tO[l] + 4));
+                }
+                rows.push_back({cost, l * (2 * lmax + 1) + mi});
+            }
+        }
+        std::stable_sort(rows.begin(), rows.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+        for (auto& r : rows) {
+            p->fwd_rows.push_back(r.second / (2 * lmax + 1));
+            p->fwd_rows.push_back(r.second % (2 * lmax + 1));
+        }
+    }
+
     // which triples use fragment l as first / second operand (for the gather-style input gradient)
     std::vector<int> r1b(L1 + 1, 0), r2b(L1 + 1, 0), r1l, r2l;
     for (int l = 0; l < L1; ++l) {
@@ -392,6 +426,11 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     if ((rc = upload(p, p->cumO, &d.cumO))) return rc;
     if ((rc = upload(p, p->cumW, &d.cumW))) return rc;
     if ((rc = upload(p, p->cumT, &d.cumT))) return rc;
+    if ((rc = upload(p, p->cumSF, &d.cumSF))) return rc;
+    if ((rc = upload(p, p->cumSO, &d.cumSO))) return rc;
+    if ((rc = upload(p, p->fwd_rows, &p->d_fwd_rows))) return rc;
+    d.nSF = p->cumSF[L1];
+    d.nSO = p->cumSO[L1];
     if ((rc = upload(p, r1b, &d.role1_begin))) return rc;
     if ((rc = upload(p, r1l, &d.role1_list))) return rc;
     if ((rc = upload(p, r2b, &d.role2_begin))) return rc;
@@ -417,7 +456,8 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     for (int k = 0; k < n; ++k) {
         const TripleRec& t = p->triples[k];
         const int64_t no = (p->tO[t.l] + T - 1) / T;
-        const int64_t ni = (t.tau1 + p->gw_i - 1) / p->gw_i;
+        // t1 groups never straddle a channel tile: ceil(T / I) groups per tile
+        const int64_t ni = dw ? t.nt1 : (int64_t)t.nt1 * ((T + p->gw_i - 1) / p->gw_i);
         const int64_t cnt = dw ? ni * no : ni * t.nt2 * no;
         CGB_REQUIRE(p->gw_begin[k] + cnt < (1ll << 31), "too many weight-gradient tasks");
         p->gw_begin[k + 1] = p->gw_begin[k] + (int)cnt;
