@@ -36,6 +36,40 @@ struct CellRec {
     short t1_0, t2_0;
 };
 
+// Everything a fused kernel needs about one cell in a single 32-byte record (one uniform load instead of a chain of
+// dependent ones through CellRec and TripleRec).
+struct CellInfo {
+    int cgoff;        // band table of the triple
+    int o1, o2;       // slab offsets (in elements of 32 lanes) of the t1 tile / t2 tile at m index 0
+    int wch0;         // toff + first mid channel of the cell: column inside W_l
+    int kch0;         // kglob + first mid channel of the cell: index into stds / inv
+    int tau2;         // channel (t1_0+i, t2_0+j) of the cell is wch0 + i*tau2 + j   (depthwise: wch0 + i)
+    short l1, l2;
+    short v1, v2;     // valid channels of the tile along t1 / t2
+};
+
+// One warp-task of the fused weight-gradient kernel.
+struct GwTask {
+    int triple;
+    short q1, gi;     // t1 tile and group of I rows inside it
+    short q2, qo;     // t2 tile, tau_out tile
+};
+
+// One entry of the fused input-gradient kernel with its triple's data inlined.
+struct GfInfo {
+    int cgoff;
+    int go_off;       // cumSO[l]: slab offset of the output-gradient fragment
+    int fo_off;       // slab offset of the other operand's tile (depthwise: of the other operand's fragment)
+    int kglob;
+    int tau2, tff, to_n;
+    int tau_o;        // channels of the other operand
+    short l, l1, l2;
+    short role;       // 0: the owned fragment is the first operand, 1: the second
+    short in0;        // first channel of the other operand's tile
+    short pad_;
+    int64_t woff;     // cumW[l] + toff
+};
+
 // Work item of the forward product kernel: a run of cells of one triple with ncell * (2l+1) <= kGenThreads.
 struct GenItem {
     int triple;
@@ -65,6 +99,7 @@ struct PlanDev {
     int sum_tff;
     const TripleRec* triples;
     const CellRec* cells;
+    const CellInfo* cell_info;
     const int* cell_begin;       // [lmax+2]  cells of degree l are cell_begin[l] .. cell_begin[l+1]
     const int* triple_begin;     // [lmax+2]
     const int* tF;               // [lmax+1]
@@ -146,6 +181,11 @@ struct cgb200_plan {
     std::vector<int> cumSF, cumSO;
     std::vector<cgb200::TripleRec> triples;
     std::vector<cgb200::CellRec> cells;
+    std::vector<cgb200::CellInfo> cell_info;
+    std::vector<cgb200::GwTask> gw_tasks;
+    const cgb200::GwTask* d_gw_tasks = nullptr;
+    std::vector<cgb200::GfInfo> gf_info;
+    const cgb200::GfInfo* d_gf_info = nullptr;
     std::vector<int> cell_begin, triple_begin;
     int max_n = 1;                    // 2*lmax+1
     int64_t cg_len = 0;               // floats in the CG table
@@ -162,6 +202,14 @@ struct cgb200_plan {
     const int* d_gf_begin = nullptr;
     std::vector<int> gf_blocks;       // (fragment, first channel) per block of the input-gradient kernel
     const int* d_gf_blocks = nullptr;
+    // blocks of the cell-staged input-gradient kernel for several degrees of splitting: level s splits the entry
+    // list of the most expensive fragment s ways and the others in proportion to their cost
+    static constexpr int kGfLevels = 6;               // s = 1, 2, 4, 8, 16, 32
+    std::vector<int> gf2_blocks[kGfLevels];           // (fragment, owned tile, part, parts) per block
+    const int* d_gf2_blocks[kGfLevels] = {nullptr};
+    std::vector<int> gf2_parts[kGfLevels];            // [lmax+1] parts per fragment
+    const int* d_gf2_parts[kGfLevels] = {nullptr};
+    int gf2_max_parts[kGfLevels] = {0};
     std::vector<int> fwd_rows;        // (l, m+l) rows of the output, most expensive first (dynamic scheduling order)
     const int* d_fwd_rows = nullptr;
     int max_tau_out = 0;

@@ -30,7 +30,6 @@ constexpr int kFwdWarps = 8;      // warps of a forward block = slices of the de
 constexpr int kFwdTo = 16;        // output channels accumulated in registers per pass
 constexpr int kSlabWarps = 16;    // warps of a persistent forward block
 constexpr int kGwWarps = 4;
-constexpr int kGfWarpsMax = 8;
 
 __device__ __forceinline__ double warp_sum(double v) {
 #pragma unroll
@@ -131,14 +130,18 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
                    float eps, int B, int G) {
     constexpr int NV = TileShape<T, DW>::NV;
     __shared__ double red[8][NV][2];
-    const CellRec cell = P.cells[P.n_cells - 1 - blockIdx.x];   // the last degrees carry the long bands: start them first
+    extern __shared__ __align__(16) float sband[];   // the triple's CG band, (2l+1) x (2l2+1)
+    const int cidx = P.n_cells - 1 - blockIdx.x;     // the last degrees carry the long bands: start them first
+    const CellRec cell = P.cells[cidx];
     const TripleRec tr = P.triples[cell.triple];
     const int n = 2 * tr.l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < n * n2; i += 256) sband[i] = P.cg[tr.cgoff + i];
+    __syncthreads();
     float s1[NV], s1c[NV], s2[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) s1[i] = s1c[i] = s2[i] = 0.f;
-    const float* C = P.cg + tr.cgoff;
+    const float* C = sband;
     const int o1 = P.cumSF[tr.l1] + (cell.t1_0 / T) * n1 * T, o2 = P.cumSF[tr.l2] + (cell.t2_0 / T) * n2 * T;
     for (int task = warp; task < G * n; task += 8) {
         const int g = task / n, mi = task - g * n;
@@ -185,10 +188,18 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
 // round-robin, each lane keeps up to kFwdTo output channels of its sample in registers, and the warps' partial sums
 // are added in warp order.  `slab` is this lane's view of the group's input slab (global or shared memory).
 // ---------------------------------------------------------------------------------------------------------------
+// Per-warp staging area of the forward kernels: the mixing-weight tile of the current cell, its norm factors and the
+// CG band row of the current (cell, m), loaded by the lanes together (coalesced, all loads in flight at once) and then
+// read back as broadcasts.  Without it every one of those warp-uniform values is a dependent load at L2 latency.
+__host__ __device__ inline int fwd_stage_bytes(int step, int nv, int max_n) {
+    return ((step * nv * 8 + nv * 4 + max_n * 4) + 15) & ~15;
+}
+
 template <int T, bool DW, int NW>
 __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restrict__ slab, const float2* __restrict__ W,
                                         const float* __restrict__ inv, float2* __restrict__ O, float2* __restrict__ red,
-                                        int red_to, int l, int mi, int b, int B, int warp, int lane) {
+                                        unsigned char* __restrict__ stage, int red_to, int l, int mi, int b, int B, int warp,
+                                        int lane) {
     constexpr int NV = TileShape<T, DW>::NV;
     const int n = 2 * l + 1;
     const int to_n = P.tO[l];
@@ -196,30 +207,47 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
     const int c_begin = P.cell_begin[l], c_end = P.cell_begin[l + 1];
     const float2* Wl = W + P.cumW[l];
     const int step = min(kFwdTo, red_to);
+    float2* wbuf = reinterpret_cast<float2*>(stage);          // [step][NV]
+    float* ibuf = reinterpret_cast<float*>(wbuf + step * NV);  // [NV]
+    float* cbuf = ibuf + NV;                                   // [2*l2+1]
     for (int to0 = 0; to0 < to_n; to0 += step) {
         float2 o[kFwdTo];
 #pragma unroll
         for (int t = 0; t < kFwdTo; ++t) o[t] = make_float2(0.f, 0.f);
-        for (int c = c_begin + warp; c < c_end; c += NW) {
-            const CellRec cell = P.cells[c];
-            const TripleRec tr = P.triples[cell.triple];
-            const int n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
-            const int o1 = P.cumSF[tr.l1] + (cell.t1_0 / T) * n1 * T, o2 = P.cumSF[tr.l2] + (cell.t2_0 / T) * n2 * T;
+        int c = c_begin + warp;
+        CellInfo ci;
+        if (c < c_end) ci = P.cell_info[c];
+        while (c < c_end) {
+            const int cn = c + NW;
+            CellInfo nxt;
+            if (cn < c_end) nxt = P.cell_info[cn];   // in flight while this cell is computed
+            const int n2 = 2 * ci.l2 + 1;
+            __syncwarp();   // the previous cell's readers are done with the staging area
+            for (int e = lane; e < step * NV; e += 32) {
+                const int t = e / NV, idx = e - t * NV;
+                const int i = DW ? idx : idx / T, j = DW ? 0 : idx % T;
+                const bool ok = (i < ci.v1) && (DW || j < ci.v2) && (to0 + t < to_n);
+                wbuf[e] = ok ? __ldg(Wl + (int64_t)(to0 + t) * tff + ci.wch0 + (DW ? i : i * ci.tau2 + j)) : make_float2(0.f, 0.f);
+            }
+            for (int idx = lane; idx < NV; idx += 32) {
+                const int i = DW ? idx : idx / T, j = DW ? 0 : idx % T;
+                const bool ok = (i < ci.v1) && (DW || j < ci.v2);
+                ibuf[idx] = ok ? __ldg(inv + ci.kch0 + (DW ? i : i * ci.tau2 + j)) : 0.f;
+            }
+            for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
+            __syncwarp();
             float2 v[NV];
-            gen_slab<T, DW>(v, P.cg + tr.cgoff + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - l, tr.l1, tr.l2);
-            const float* iv = inv + tr.kglob;
-            const float2* w0 = Wl + (int64_t)to0 * tff + tr.toff;
+            gen_slab<T, DW>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
 #pragma unroll
             for (int idx = 0; idx < NV; ++idx) {
-                if (!tile_valid<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau1, tr.tau2)) continue;   // warp-uniform
-                const int ch = tile_channel<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau2);
-                const float s = __ldg(iv + ch);
-                const float2 x = make_float2(v[idx].x * s, v[idx].y * s);
-                const float2* w = w0 + ch;
+                const float sc = ibuf[idx];
+                const float2 x = make_float2(v[idx].x * sc, v[idx].y * sc);
 #pragma unroll
                 for (int t = 0; t < kFwdTo; ++t)
-                    if (t < step && to0 + t < to_n) cfma(o[t], __ldg(w + (int64_t)t * tff), x);
+                    if (t < step) cfma(o[t], wbuf[t * NV + idx], x);   // masked entries carry zero weights
             }
+            ci = nxt;
+            c = cn;
         }
         __syncthreads();   // protects `red` from the previous pass / row
 #pragma unroll
@@ -242,13 +270,15 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
 template <int T, bool DW>
 __global__ void __launch_bounds__(kFwdWarps * kWarp)
 fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restrict__ SF, const float2* __restrict__ W,
-                 const float* __restrict__ inv, float2* __restrict__ O, int B) {
-    __shared__ float2 red[kFwdWarps * kFwdTo * kWarp];
+                 const float* __restrict__ inv, float2* __restrict__ O, int B, int red_to, int stage_bytes) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float2* red = reinterpret_cast<float2*>(smem_raw);
     const int l = rows[2 * blockIdx.x], mi = rows[2 * blockIdx.x + 1];
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    fwd_row<T, DW, kFwdWarps>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, kFwdTo, l, mi, g * 32 + lane, B, warp,
-                              lane);
+    unsigned char* stage = smem_raw + (size_t)kFwdWarps * red_to * 32 * sizeof(float2) + (size_t)warp * stage_bytes;
+    fwd_row<T, DW, kFwdWarps>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, stage, red_to, l, mi, g * 32 + lane, B,
+                              warp, lane);
 }
 
 // persistent blocks: block (p, g) copies group g's slab into shared memory once, then pulls rows (most expensive
@@ -257,11 +287,13 @@ template <int T, bool DW>
 __global__ void __launch_bounds__(kSlabWarps * kWarp)
 fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const float2* __restrict__ SF,
                       const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ O, int B,
-                      int* __restrict__ counters, int red_to) {
+                      int* __restrict__ counters, int red_to, int stage_bytes) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int next_row;
     float2* slab = reinterpret_cast<float2*>(smem_raw);
     float2* red = slab + (size_t)P.nSF * 32;
+    unsigned char* stage = reinterpret_cast<unsigned char*>(red + (size_t)kSlabWarps * red_to * 32) +
+                           (size_t)(threadIdx.x >> 5) * stage_bytes;
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     {
@@ -275,8 +307,8 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
         __syncthreads();
         const int r = next_row;
         if (r >= n_rows) break;
-        fwd_row<T, DW, kSlabWarps>(P, slab + lane, W, inv, O, red, red_to, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B, warp,
-                                   lane);
+        fwd_row<T, DW, kSlabWarps>(P, slab + lane, W, inv, O, red, stage, red_to, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B,
+                                   warp, lane);
     }
 }
 
@@ -287,29 +319,23 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
 // ---------------------------------------------------------------------------------------------------------------
 template <int T, int I>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
-fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ SF,
-                const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G) {
-    constexpr int NI = (T + I - 1) / I;   // t1 groups per tile
+fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
+                const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
+                int band_floats) {
+    extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
     if (task < 0) return;
-    int lo = 0, hi = P.n_triples;   // triple of this task: last k with task_begin[k] <= task
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (task_begin[mid] <= task) lo = mid; else hi = mid;
-    }
-    const TripleRec tr = P.triples[lo];
+    const GwTask tk = tasks[task];
+    const TripleRec tr = P.triples[tk.triple];
     const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int to_n = P.tO[l], tff = P.tFF[l];
-    const int no = (to_n + T - 1) / T;
-    int r = task - task_begin[lo];
-    const int qo = r % no;
-    r /= no;
-    const int q2 = r % tr.nt2;
-    r /= tr.nt2;
-    const int gi = r % NI, q1 = r / NI;
-    const int j0 = gi * I;
-    const float* C = P.cg + tr.cgoff;
+    const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
+    const int j0 = tk.gi * I;
+    float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the triple's CG band
+    for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
+    __syncwarp();
+    const float* C = band;
     int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
 #pragma unroll
     for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
@@ -386,22 +412,21 @@ fused_gw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, cons
 // weight gradient, depthwise product: warp-task = (triple, t tile, tau_out tile); FF tile generated directly.
 template <int T>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
-fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, const float2* __restrict__ SF,
-                   const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G) {
+fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
+                   const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
+                   int band_floats) {
+    extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
     if (task < 0) return;
-    int lo = 0, hi = P.n_triples;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (task_begin[mid] <= task) lo = mid; else hi = mid;
-    }
-    const TripleRec tr = P.triples[lo];
+    const GwTask tk = tasks[task];
+    const TripleRec tr = P.triples[tk.triple];
     const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int to_n = P.tO[l], tff = P.tFF[l];
-    const int no = (to_n + T - 1) / T;
-    const int r = task - task_begin[lo];
-    const int qo = r % no, q = r / no;
+    const int qo = tk.qo, q = tk.q1;
+    float* band = sband_all + (size_t)warp * band_floats;
+    for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
+    __syncwarp();
     float2 acc[T][T];
 #pragma unroll
     for (int o = 0; o < T; ++o)
@@ -413,7 +438,7 @@ fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, c
         const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l] + qo * n * T) * 32 + lane;
         for (int mi = 0; mi < n; ++mi) {
             float2 v[T];
-            gen_slab<T, true>(v, P.cg + tr.cgoff + mi * n2, f1, f2, mi - l, tr.l1, tr.l2);
+            gen_slab<T, true>(v, band + mi * n2, f1, f2, mi - l, tr.l1, tr.l2);
 #pragma unroll
             for (int o = 0; o < T; ++o) {
                 const float2 gv = go[(mi * T + o) * 32];
@@ -436,147 +461,171 @@ fused_gw_dw_kernel(PlanDev P, const int* __restrict__ task_begin, int n_tasks, c
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// input gradient.  Block = (fragment lt, kGfOut of its channels, sample group) and owns those elements of gF.  All
-// warps walk the fragment's entries (triple, role, tile of the other operand) together and split the m of the entry,
-// so the other operand's tile stays hot in L1; for its m a warp builds the gFF tile
-//     g = (1/std) sum_to conj(W[to, k]) gO[to, m]
-// in registers and contracts it with conj(other operand) and C into its private shared-memory accumulator
-// acc[channel][m_t][lane] (CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289, without the
-// trip of gFF through memory).  The warps' accumulators are added in warp order at the end.
+// input gradient.  Block = (fragment lt, one tile of its channels, sample group, part) and owns that part's
+// contribution to those elements of gF.  It walks its share of the fragment's entries (triple, role, tile of the
+// other operand); per entry the whole block
+//   stages   the other operand's tile, the CG band and conj(W)/std of the tile in shared memory,
+//   phase 1  builds the gFF tile  H[m][t1, t2] = sum_to conj(W[to, k])/std_k * gO[to, m]  for a chunk of m (warps
+//            split m) and parks it in shared memory,
+//   phase 2  lets every warp own rows m_t of the fragment and gather, in registers,
+//            x[a] = sum C * conj(other[c][.]) * H[m][a, c]  over the band, adding x once to the block's accumulator.
+// This is CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289 with gFF living only as one tile
+// in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int kGfWarps = 16;
+
 template <int T, bool DW>
-__global__ void __launch_bounds__(kGfWarpsMax * kWarp)
-fused_gf_kernel(PlanDev P, const GfEntry* __restrict__ entries, const int* __restrict__ entry_begin,
-                const int* __restrict__ block_frag, const float2* __restrict__ SF, const float2* __restrict__ SG,
-                const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ gF, int B) {
-    constexpr int OUT = kGfOut;
-    constexpr int TI = DW ? 1 : T;   // tile of the other operand
+__global__ void __launch_bounds__(kGfWarps * kWarp)
+fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
+                const int* __restrict__ blocks, const float2* __restrict__ SF, const float2* __restrict__ SG,
+                const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ out,
+                int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats) {
+    constexpr int NH = DW ? T : T * T;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int lt = block_frag[2 * blockIdx.x], t_0 = block_frag[2 * blockIdx.x + 1];
-    const int nt = 2 * lt + 1;
+    const int lt = blocks[4 * blockIdx.x], q = blocks[4 * blockIdx.x + 1];
+    const int part = blocks[4 * blockIdx.x + 2], parts = blocks[4 * blockIdx.x + 3];
+    const int nt = 2 * lt + 1, t_0 = q * T;
     const int g = blockIdx.y;
-    const int nwarps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float2* acc = reinterpret_cast<float2*>(smem_raw) + (size_t)warp * OUT * nt * 32;   // [OUT][nt][32]
-    for (int i = lane; i < OUT * nt * 32; i += 32) acc[i] = make_float2(0.f, 0.f);
-    __syncwarp();
     const int tau_t = P.tF[lt];
-    const float2* slabF = SF + (int64_t)g * P.nSF * 32 + lane;
+    float2* acc = reinterpret_cast<float2*>(smem_raw);          // [T][nt][32]
+    float2* fo = acc + (size_t)T * max_n * 32;                   // [n_o][T][32]  other operand's tile
+    float2* wt = fo + (size_t)T * max_n * 32;                    // [to_n][NH]    conj(W) / std
+    float* band = reinterpret_cast<float*>(wt + (size_t)max_to * NH);   // [n][n2]
+    float2* H = reinterpret_cast<float2*>(band + band_floats);   // [Mc][NH][32]
+    for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
+    const float2* slabF = SF + (int64_t)g * P.nSF * 32;
     const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
 
-    for (int e = entry_begin[lt]; e < entry_begin[lt + 1]; ++e) {
-        const GfEntry en = entries[e];
-        const TripleRec tr = P.triples[en.triple];
-        const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
-        if (warp >= n) continue;
-        const int to_n = P.tO[l], tff = P.tFF[l];
-        const float* C = P.cg + tr.cgoff;
-        const float2* go = slabG + P.cumSO[l] * 32;
-        const float2* Wl = W + P.cumW[l] + tr.toff;
+    const int e_end = entry_begin[lt + 1];
+    int e = entry_begin[lt] + part;
+    GfInfo en;
+    if (e < e_end) en = entries[e];
+    while (e < e_end) {
+        GfInfo nxt;
+        if (e + parts < e_end) nxt = entries[e + parts];   // in flight while this entry is computed
+        const int l = en.l, n = 2 * l + 1, n1 = 2 * en.l1 + 1, n2 = 2 * en.l2 + 1;
+        const int to_n = en.to_n, tff = en.tff;
         const bool first = en.role == 0;   // the owned fragment is the first operand of this triple
-        const int in0 = DW ? (t_0 / T) * T : en.in0;   // first channel of the other operand's tile
-        const int lo_ = first ? tr.l2 : tr.l1, no_ = first ? n2 : n1;
-        const float2* fo = slabF + (P.cumSF[lo_] + (in0 / T) * no_ * T) * 32;
-        const int tau_o = first ? tr.tau2 : tr.tau1;
-        // depthwise: the other operand's channel equals the owned channel; its element for m index 0, per owned channel
-        const float2* fdw[OUT];
-#pragma unroll
-        for (int a = 0; a < OUT; ++a) {
-            const int t = min(t_0 + a, max(tau_t - 1, 0));
-            fdw[a] = slabF + (P.cumSF[lo_] + ((t / T) * no_) * T + t % T) * 32;
-        }
-        // mid channel and norm factor of every tile entry (owned channel a, other channel c)
-        int ch[OUT][TI];
-        float sc[OUT][TI];
-#pragma unroll
-        for (int a = 0; a < OUT; ++a)
-#pragma unroll
-            for (int c = 0; c < TI; ++c) {
-                const bool ok = (t_0 + a < tau_t) && (DW || in0 + c < tau_o);
+        const int in0 = DW ? 0 : en.in0;
+        const int n_o = first ? n2 : n1;
+        __syncthreads();   // the previous entry's readers are done with the staging buffers
+        {
+            const float4* src = reinterpret_cast<const float4*>(slabF + ((int64_t)en.fo_off + (DW ? q * n_o * T : 0)) * 32);
+            float4* dst = reinterpret_cast<float4*>(fo);
+            for (int i = threadIdx.x; i < n_o * T * 16; i += blockDim.x) dst[i] = src[i];
+            for (int i = threadIdx.x; i < n * n2; i += blockDim.x) band[i] = __ldg(P.cg + en.cgoff + i);
+            for (int i = threadIdx.x; i < to_n * NH; i += blockDim.x) {
+                const int t = i / NH, idx = i - t * NH;
+                const int i1 = DW ? idx : idx / T, j1 = DW ? idx : idx % T;
+                const int a = first ? i1 : j1, c = first ? j1 : i1;   // owned / other channel inside their tiles
+                const bool ok = (t_0 + a < tau_t) && (DW || in0 + c < en.tau_o);
                 const int t1 = first ? t_0 + a : in0 + c, t2 = first ? in0 + c : t_0 + a;
-                ch[a][c] = ok ? (DW ? t_0 + a : t1 * tr.tau2 + t2) : -1;
-                sc[a][c] = ok ? inv[tr.kglob + ch[a][c]] : 0.f;
-            }
-        for (int mi = warp; mi < n; mi += nwarps) {
-            const int m = mi - l;
-            float2 gt[OUT][TI];
-#pragma unroll
-            for (int a = 0; a < OUT; ++a)
-#pragma unroll
-                for (int c = 0; c < TI; ++c) gt[a][c] = make_float2(0.f, 0.f);
-            for (int to = 0; to < to_n; ++to) {
-                const float2 gv = go[(((to / T) * n + mi) * T + to % T) * 32];
-                const float2* w = Wl + (int64_t)to * tff;
-#pragma unroll
-                for (int a = 0; a < OUT; ++a)
-#pragma unroll
-                    for (int c = 0; c < TI; ++c)
-                        if (ch[a][c] >= 0) cfma_conj(gt[a][c], __ldg(w + ch[a][c]), gv);
-            }
-#pragma unroll
-            for (int a = 0; a < OUT; ++a)
-#pragma unroll
-                for (int c = 0; c < TI; ++c) {
-                    gt[a][c].x *= sc[a][c];
-                    gt[a][c].y *= sc[a][c];
+                const int ch = DW ? t_0 + a : t1 * en.tau2 + t2;
+                float2 w = make_float2(0.f, 0.f);
+                if (ok) {
+                    w = __ldg(W + en.woff + (int64_t)t * tff + ch);
+                    const float sc = __ldg(inv + en.kglob + ch);
+                    w = make_float2(w.x * sc, -w.y * sc);
                 }
-            const int lo = max(-tr.l2, m - tr.l1), hi = min(tr.l2, m + tr.l1);
-            const float* pc = C + mi * n2 + lo + tr.l2;
-            // the other operand's m index runs up (its own m2) when the owned fragment is first, down otherwise;
-            // the owned element's m index runs the other way
-            const int dir = first ? 1 : -1;
-            const float2* po = fo + (first ? lo + tr.l2 : m - lo + tr.l1) * (T * 32);
-            float2* pa = acc + (first ? m - lo + tr.l1 : lo + tr.l2) * 32 + lane;
-            for (int k = hi - lo; k >= 0; --k) {
-                const float cg = *pc++;
-                float2 x[OUT];
+                wt[i] = w;
+            }
+        }
+        const float2* go = slabG + (int64_t)en.go_off * 32;
+        for (int mc0 = 0; mc0 < n; mc0 += Mc) {
+            const int mcn = min(Mc, n - mc0);
+            __syncthreads();   // staging visible; the previous chunk's readers are done with H
+            for (int mi = mc0 + warp; mi < mc0 + mcn; mi += kGfWarps) {
+                float2 gt[NH];
 #pragma unroll
-                for (int a = 0; a < OUT; ++a) x[a] = make_float2(0.f, 0.f);
-                if constexpr (DW) {
-                    // depthwise: the other operand's channel is the owned channel itself
+                for (int k = 0; k < NH; ++k) gt[k] = make_float2(0.f, 0.f);
+                for (int to = 0; to < to_n; ++to) {
+                    const float2 gv = go[(((to / T) * n + mi) * T + to % T) * 32];
+                    const float2* w = wt + to * NH;
 #pragma unroll
-                    for (int a = 0; a < OUT; ++a)
-                        if (ch[a][0] >= 0) {
-                            const float2 f = fdw[a][(po - fo)];
-                            cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), gt[a][0]);
+                    for (int k = 0; k < NH; ++k) cfma(gt[k], w[k], gv);
+                }
+                float2* h = H + (size_t)(mi - mc0) * NH * 32 + lane;
+#pragma unroll
+                for (int k = 0; k < NH; ++k) h[k * 32] = gt[k];
+            }
+            __syncthreads();
+            for (int r = warp; r < nt; r += kGfWarps) {
+                const int mt = r - lt;   // m of the owned element
+                float2 x[T];
+#pragma unroll
+                for (int a = 0; a < T; ++a) x[a] = make_float2(0.f, 0.f);
+                // u = m of the other operand's element; m = mt + u must lie in [-l, l] and inside the chunk
+                const int lo_ = first ? en.l2 : en.l1;
+                const int ulo = max(-lo_, max(-l, mc0 - l) - mt), uhi = min(lo_, min(l, mc0 + mcn - 1 - l) - mt);
+                if (ulo <= uhi) {
+                    // band entry [m + l][m2 + l2]: m2 = u (first) or mt (second)
+                    const float* pc = band + (mt + ulo + l) * n2 + (first ? ulo + en.l2 : mt + en.l2);
+                    const int cstep = first ? n2 + 1 : n2;
+                    const float2* pf = fo + (size_t)(ulo + lo_) * T * 32 + lane;
+                    const float2* ph = H + (size_t)(mt + ulo + l - mc0) * NH * 32 + lane;
+                    for (int k = uhi - ulo; k >= 0; --k) {
+                        const float cg = *pc;
+                        if constexpr (DW) {
+#pragma unroll
+                            for (int a = 0; a < T; ++a) {
+                                const float2 f = pf[a * 32];
+                                cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), ph[a * 32]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < T; ++c) {
+                                float2 f = pf[c * 32];
+                                f.x *= cg;
+                                f.y *= cg;
+#pragma unroll
+                                for (int a = 0; a < T; ++a) cfma_conj(x[a], f, ph[(first ? a * T + c : c * T + a) * 32]);
+                            }
                         }
-                } else {
+                        pc += cstep;
+                        pf += T * 32;
+                        ph += NH * 32;
+                    }
 #pragma unroll
-                    for (int c = 0; c < TI; ++c) {
-                        float2 f = po[c * 32];
-                        f.x *= cg;
-                        f.y *= cg;
-#pragma unroll
-                        for (int a = 0; a < OUT; ++a)
-                            if (ch[a][c] >= 0) cfma_conj(x[a], f, gt[a][c]);
+                    for (int a = 0; a < T; ++a) {
+                        float2* pa = acc + ((size_t)a * nt + r) * 32 + lane;
+                        float2 cur = *pa;
+                        cur.x += x[a].x;
+                        cur.y += x[a].y;
+                        *pa = cur;
                     }
                 }
-#pragma unroll
-                for (int a = 0; a < OUT; ++a) {
-                    float2* p = pa + a * nt * 32;
-                    float2 cur = *p;
-                    cur.x += x[a].x;
-                    cur.y += x[a].y;
-                    *p = cur;
-                }
-                po += dir * (T * 32);
-                pa -= dir * 32;
             }
         }
+        en = nxt;
+        e += parts;
     }
     __syncthreads();
-    const float2* all = reinterpret_cast<const float2*>(smem_raw);
-    for (int i = threadIdx.x; i < OUT * nt * 32; i += blockDim.x) {
+    float2* dst = out + (int64_t)part * part_stride;
+    for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) {
         const int ln = i & 31, rest = i >> 5;
-        const int a = rest / nt, mt = rest - a * nt;
-        float2 s = make_float2(0.f, 0.f);
-        for (int w = 0; w < nwarps; ++w) {
-            const float2 v = all[(size_t)w * OUT * nt * 32 + i];
+        const int a = rest / nt, r = rest - a * nt;
+        const int b = g * 32 + ln;
+        if (b < B && t_0 + a < tau_t) dst[(int64_t)b * P.n_F + P.cumF[lt] + (int64_t)(t_0 + a) * nt + r] = acc[i];
+    }
+}
+
+// gF[b][e] = sum over the parts of e's fragment, in part order
+__global__ void __launch_bounds__(256)
+gf_reduce_kernel(PlanDev P, const int* __restrict__ parts, const float2* __restrict__ partial, int64_t part_stride,
+                 float2* __restrict__ gF, int B) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= P.n_F) return;
+    const int np = parts[find_degree(P.cumF, P.lmax + 1, e)];
+    for (int b = blockIdx.y; b < B; b += gridDim.y) {
+        const float2* src = partial + (int64_t)b * P.n_F + e;
+        float2 s = src[0];
+        for (int k = 1; k < np; ++k) {
+            const float2 v = src[(int64_t)k * part_stride];
             s.x += v.x;
             s.y += v.y;
         }
-        const int b = g * 32 + ln;
-        if (b < B && t_0 + a < tau_t) gF[(int64_t)b * P.n_F + P.cumF[lt] + (int64_t)(t_0 + a) * nt + mt] = s;
+        gF[(int64_t)b * P.n_F + e] = s;
     }
 }
 
@@ -591,8 +640,17 @@ struct Workspace {
     float2* SG;     // slab of gO in the backward
     float* inv;
     int* counters;  // one row counter per sample group
+    float2* gf_part; // partial input gradients, [parts][B][n_F], when the input-gradient blocks are split
+    int gf_level;
     int64_t bytes;
 };
+
+// Splitting level of the input-gradient kernel: the coarsest one that gives every SM about two blocks.
+int gf_level(const cgb200_plan* p, int64_t G) {
+    for (int lv = 0; lv < cgb200_plan::kGfLevels; ++lv)
+        if ((int64_t)(p->gf2_blocks[lv].size() / 4) * G >= 2 * (int64_t)p->num_sms) return lv;
+    return cgb200_plan::kGfLevels - 1;
+}
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
@@ -609,6 +667,10 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
     off += align256(std::max<int64_t>(p->d.sum_tff, 1) * (int64_t)sizeof(float));
     w.counters = (int*)(c + off);
     off += align256(G * (int64_t)sizeof(int));
+    w.gf_level = gf_level(p, G);
+    w.gf_part = (float2*)(c + off);
+    if (p->gf2_max_parts[w.gf_level] > 1)
+        off += align256((int64_t)p->gf2_max_parts[w.gf_level] * B * std::max<int64_t>(p->d.n_F, 1) * (int64_t)sizeof(float2));
     w.bytes = off;
     return w;
 }
@@ -688,32 +750,48 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     if ((rc = launch_prep(p, jf, none, 1, (int)B, G, fn ? stds : nullptr, eps, update ? nullptr : ws.inv, ws.counters, st)))
         return rc;
     if (update && p->d.n_cells > 0) {
+        const size_t band = p->gen_band_bytes;
         launch_begin(K_STATS, st);
-        CGB_DISPATCH_TILE(T, p->d.depthwise,
-                          (fused_stats_kernel<TT, DD><<<p->d.n_cells, 256, 0, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G)));
+        CGB_DISPATCH_TILE(T, p->d.depthwise, {
+            auto kern = fused_stats_kernel<TT, DD>;
+            if (band > 40 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band));
+            kern<<<p->d.n_cells, 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G);
+        });
         launch_end(K_STATS, st);
         CGB_CUDA(cudaGetLastError());
     }
     const int n_rows = (int)p->fwd_rows.size() / 2;
     if (n_rows == 0) return CGB200_OK;
-    // persistent shared-memory variant when one group's slab (plus the reduction buffer) fits in an SM
+    // persistent shared-memory variant when one group's slab (plus reduction buffer and staging areas) fits in an SM
+    const int NVh = p->d.depthwise ? T : T * T;
     const int red_to = std::min(kFwdTo, std::max(p->max_tau_out, 1));
+    const int stage_bytes = fwd_stage_bytes(red_to, NVh, p->max_n);
     const size_t slab_bytes = (size_t)p->d.nSF * 32 * sizeof(float2);
-    const size_t smem = slab_bytes + (size_t)kSlabWarps * red_to * 32 * sizeof(float2);
+    const size_t smem_slab = slab_bytes + (size_t)kSlabWarps * (red_to * 32 * sizeof(float2) + stage_bytes);
+    const size_t smem_rows = (size_t)kFwdWarps * (red_to * 32 * sizeof(float2) + stage_bytes);
     const char* force = getenv("CGB200_FWD");
-    const bool use_slab = force ? (force[0] == 's') : (smem <= 200 * 1024 && G <= p->num_sms);
+    const bool fits = smem_slab <= 227 * 1024 && G <= p->num_sms;
+    const bool use_slab = fits && (force ? force[0] == 's' : true);
+    if (smem_rows > 227 * 1024) {
+        set_error("lmax too large for the fused forward kernel");
+        return CGB200_ERR_UNSUPPORTED;
+    }
     launch_begin(K_FWD, st);
-    if (use_slab && smem <= 227 * 1024) {
+    if (use_slab) {
         const int per_group = std::max(1, std::min(n_rows, p->num_sms / G));
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = fused_fwd_slab_kernel<TT, DD>;
-            CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<dim3(per_group, G), kSlabWarps * kWarp, smem, st>>>(p->d, p->d_fwd_rows, n_rows, ws.SF, (const float2*)W, ws.inv,
-                                                                    (float2*)O, (int)B, ws.counters, red_to);
+            CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_slab));
+            kern<<<dim3(per_group, G), kSlabWarps * kWarp, smem_slab, st>>>(p->d, p->d_fwd_rows, n_rows, ws.SF, (const float2*)W,
+                                                                         ws.inv, (float2*)O, (int)B, ws.counters, red_to, stage_bytes);
         });
     } else {
-        CGB_DISPATCH_TILE(T, p->d.depthwise,
-                          (fused_fwd_kernel<TT, DD><<<dim3(n_rows, G), kFwdWarps * kWarp, 0, st>>>(p->d, p->d_fwd_rows, ws.SF, (const float2*)W, ws.inv, (float2*)O, (int)B)));
+        CGB_DISPATCH_TILE(T, p->d.depthwise, {
+            auto kern = fused_fwd_kernel<TT, DD>;
+            if (smem_rows > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows));
+            kern<<<dim3(n_rows, G), kFwdWarps * kWarp, smem_rows, st>>>(p->d, p->d_fwd_rows, ws.SF, (const float2*)W, ws.inv, (float2*)O,
+                                                                     (int)B, red_to, stage_bytes);
+        });
     }
     launch_end(K_FWD, st);
     CGB_CUDA(cudaGetLastError());
@@ -750,13 +828,25 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
     if (n_tasks > 0) {
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
+        const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
+        const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;
+        if (smem > 227 * 1024) {
+            set_error("lmax too large for the fused weight-gradient kernel");
+            return CGB200_ERR_UNSUPPORTED;
+        }
         launch_begin(K_GW, st);
         if (p->d.depthwise) {
-            CGB_DISPATCH_TILE(T, false,
-                              (fused_gw_dw_kernel<TT><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G)));
+            CGB_DISPATCH_TILE(T, false, {
+                auto kern = fused_gw_dw_kernel<TT>;
+                if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                kern<<<blocks, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
+            });
         } else {
-            CGB_DISPATCH_TILE(T, false,
-                              (fused_gw_kernel<TT, GwI<TT>::value><<<blocks, kGwWarps * kWarp, 0, st>>>(p->d, p->d_gw_begin, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G)));
+            CGB_DISPATCH_TILE(T, false, {
+                auto kern = fused_gw_kernel<TT, GwI<TT>::value>;
+                if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                kern<<<blocks, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
+            });
         }
         launch_end(K_GW, st);
         CGB_CUDA(cudaGetLastError());
@@ -764,20 +854,34 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
 
     // input gradient
     if (p->d.n_F > 0) {
-        const int nblk = (int)p->gf_blocks.size() / 2;
-        const size_t per_warp = (size_t)kGfOut * p->max_n * 32 * sizeof(float2);
-        int nwarps = (int)std::min<size_t>(kGfWarpsMax, (200 * 1024) / per_warp);
-        if (nwarps < 1) {
-            set_error("lmax too large for the fused input-gradient kernel");
+        const int lv = ws.gf_level;
+        const int nblk = (int)p->gf2_blocks[lv].size() / 4;
+        const bool split = p->gf2_max_parts[lv] > 1;
+        const int NHh = p->d.depthwise ? T : T * T;
+        const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
+        const int max_to = std::max(p->max_tau_out, 1);
+        const size_t fixed = (size_t)2 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * NHh * sizeof(float2) + p->gen_band_bytes;
+        const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
+        if (fixed + per_m > 227 * 1024) {
+            set_error("lmax or tau_out too large for the fused input-gradient kernel");
             return CGB200_ERR_UNSUPPORTED;
         }
-        const size_t smem = per_warp * nwarps;
+        const int Mc = (int)std::min<size_t>(p->max_n, (227 * 1024 - fixed) / per_m);
+        const size_t smem = fixed + (size_t)Mc * per_m;
+        const int64_t part_stride = split ? (int64_t)B * p->d.n_F : 0;
         launch_begin(K_GF, st);
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = fused_gf_kernel<TT, DD>;
             if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_entries, p->d_gf_begin, p->d_gf_blocks, ws.SF, ws.SG, (const float2*)W, ws.inv, (float2*)gF, (int)B);
+            kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
         });
+        if (split) {
+            launch_end(K_GF, st);
+            CGB_CUDA(cudaGetLastError());
+            const int gx = (int)((p->d.n_F + 255) / 256);
+            launch_begin(K_GF, st);
+            gf_reduce_kernel<<<dim3(gx, (unsigned)std::min<int64_t>(B, 65535)), 256, 0, st>>>(p->d, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF, (int)B);
+        }
         launch_end(K_GF, st);
         CGB_CUDA(cudaGetLastError());
     }

@@ -368,6 +368,22 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         p->cumSO[l + 1] = (int)b;
         p->max_tau_out = std::max(p->max_tau_out, p->tO[l]);
     }
+    for (const CellRec& c : p->cells) {
+        const TripleRec& t = p->triples[c.triple];
+        CellInfo ci;
+        ci.cgoff = t.cgoff;
+        ci.o1 = p->cumSF[t.l1] + (c.t1_0 / T) * (2 * t.l1 + 1) * T;
+        ci.o2 = p->cumSF[t.l2] + (c.t2_0 / T) * (2 * t.l2 + 1) * T;
+        const int ch0 = dw ? c.t1_0 : c.t1_0 * t.tau2 + c.t2_0;
+        ci.wch0 = t.toff + ch0;
+        ci.kch0 = t.kglob + ch0;
+        ci.tau2 = t.tau2;
+        ci.l1 = (short)t.l1;
+        ci.l2 = (short)t.l2;
+        ci.v1 = (short)std::min(T, t.tau1 - c.t1_0);
+        ci.v2 = (short)std::min(T, t.tau2 - c.t2_0);
+        p->cell_info.push_back(ci);
+    }
     {
         std::vector<std::pair<double, int>> rows;   // (cost, l*(2*lmax+1)+mi)
         for (int l = 0; l < L1; ++l) {
@@ -416,6 +432,7 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     d.sum_tff = p->cumT[L1];
     if ((rc = upload(p, p->triples, &d.triples))) return rc;
     if ((rc = upload(p, p->cells, &d.cells))) return rc;
+    if ((rc = upload(p, p->cell_info, &d.cell_info))) return rc;
     if ((rc = upload(p, p->cell_begin, &d.cell_begin))) return rc;
     if ((rc = upload(p, p->triple_begin, &d.triple_begin))) return rc;
     if ((rc = upload(p, p->tF, &d.tF))) return rc;
@@ -459,10 +476,18 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         // t1 groups never straddle a channel tile: ceil(T / I) groups per tile
         const int64_t ni = dw ? t.nt1 : (int64_t)t.nt1 * ((T + p->gw_i - 1) / p->gw_i);
         const int64_t cnt = dw ? ni * no : ni * t.nt2 * no;
-        CGB_REQUIRE(p->gw_begin[k] + cnt < (1ll << 31), "too many weight-gradient tasks");
+        CGB_REQUIRE(p->gw_begin[k] + cnt < (1ll << 26), "too many weight-gradient tasks");
         p->gw_begin[k + 1] = p->gw_begin[k] + (int)cnt;
+        const int groups = dw ? 1 : (T + p->gw_i - 1) / p->gw_i;
+        for (int q1 = 0; q1 < t.nt1; ++q1)
+            for (int gi = 0; gi < groups; ++gi)
+                for (int q2 = 0; q2 < (dw ? 1 : t.nt2); ++q2)
+                    for (int qo = 0; qo < (int)no; ++qo)
+                        p->gw_tasks.push_back({k, (short)q1, (short)gi, (short)q2, (short)qo});
+        CGB_REQUIRE((int)p->gw_tasks.size() == p->gw_begin[k + 1], "internal: weight-gradient task count");
     }
     if ((rc = upload(p, p->gw_begin, &p->d_gw_begin))) return rc;
+    if ((rc = upload(p, p->gw_tasks, &p->d_gw_tasks))) return rc;
     // entries of the fused input-gradient kernel, per fragment
     p->gf_begin.assign(L1 + 1, 0);
     for (int l = 0; l < L1; ++l) {
@@ -474,6 +499,62 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
                 for (int i = 0; i < (dw ? 1 : t.nt1); ++i) p->gf_entries.push_back({k, 1, (short)(i * T)});
         }
         p->gf_begin[l + 1] = (int)p->gf_entries.size();
+    }
+    for (const GfEntry& en : p->gf_entries) {
+        const TripleRec& t = p->triples[en.triple];
+        GfInfo gi;
+        const bool first = en.role == 0;
+        const int lo_ = first ? t.l2 : t.l1;
+        gi.cgoff = t.cgoff;
+        gi.go_off = p->cumSO[t.l];
+        gi.fo_off = p->cumSF[lo_] + (dw ? 0 : (en.in0 / T) * (2 * lo_ + 1) * T);
+        gi.kglob = t.kglob;
+        gi.tau2 = t.tau2;
+        gi.tff = p->tFF[t.l];
+        gi.to_n = p->tO[t.l];
+        gi.tau_o = first ? t.tau2 : t.tau1;
+        gi.l = (short)t.l;
+        gi.l1 = (short)t.l1;
+        gi.l2 = (short)t.l2;
+        gi.role = en.role;
+        gi.in0 = en.in0;
+        gi.pad_ = 0;
+        gi.woff = t.woff;
+        p->gf_info.push_back(gi);
+    }
+    if ((rc = upload(p, p->gf_info, &p->d_gf_info))) return rc;
+    {
+        // cost of a fragment's entry list ~ sum over entries of (2l+1)*tau_out*T^2 (gFF tile) + band*T^2 (contraction)
+        std::vector<double> cost(L1, 0.0);
+        double cmax = 0.0;
+        for (int l = 0; l < L1; ++l) {
+            for (int e = p->gf_begin[l]; e < p->gf_begin[l + 1]; ++e) {
+                const TripleRec& t = p->triples[p->gf_entries[e].triple];
+                cost[l] += (double)(2 * t.l + 1) * (p->tO[t.l] + 2.0 * (2 * t.l2 + 1)) * (dw ? T : T * T);
+            }
+            cmax = std::max(cmax, cost[l]);
+        }
+        for (int lv = 0; lv < cgb200_plan::kGfLevels; ++lv) {
+            const int sfac = 1 << lv;
+            p->gf2_parts[lv].assign(L1, 1);
+            for (int l = L1 - 1; l >= 0; --l) {   // high degrees first: they are the expensive ones
+                const int n_entries = p->gf_begin[l + 1] - p->gf_begin[l];
+                int parts = cmax > 0 ? (int)(sfac * cost[l] / cmax + 0.5) : 1;
+                parts = std::max(1, std::min(parts, std::max(n_entries, 1)));
+                p->gf2_parts[lv][l] = parts;
+                p->gf2_max_parts[lv] = std::max(p->gf2_max_parts[lv], parts);
+                const int ntile = (p->tF[l] + T - 1) / T;
+                for (int q = 0; q < ntile; ++q)
+                    for (int part = 0; part < parts; ++part) {
+                        p->gf2_blocks[lv].push_back(l);
+                        p->gf2_blocks[lv].push_back(q);
+                        p->gf2_blocks[lv].push_back(part);
+                        p->gf2_blocks[lv].push_back(parts);
+                    }
+            }
+            if ((rc = upload(p, p->gf2_blocks[lv], &p->d_gf2_blocks[lv]))) return rc;
+            if ((rc = upload(p, p->gf2_parts[lv], &p->d_gf2_parts[lv]))) return rc;
+        }
     }
     if ((rc = upload(p, p->gf_entries, &p->d_gf_entries))) return rc;
     if ((rc = upload(p, p->gf_begin, &p->d_gf_begin))) return rc;
