@@ -32,6 +32,7 @@ SIGNATURES = {
     "cgb200_layer_fwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_int, vp, vp, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
+    "cgb200_layer_fwd_static": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp]),
     "cgb200_launch_count": (ctypes.c_int64, [ctypes.c_int]),
     "cgb200_kernel_count": (ctypes.c_int, []),
     "cgb200_kernel_name": (ctypes.c_char_p, [ctypes.c_int]),

@@ -888,4 +888,53 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     return CGB200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Forward pass for callers that cannot allocate device memory.
+//
+// cgb200_layer_fwd takes its scratch (the rearranged activations, the per-channel norm factors and the row counters
+// of the persistent forward kernel) from the caller.  Some hosts have no allocator to ask: a plugin entered from
+// inside another framework's stream callback or graph-replay path, a process that handed all device memory to an
+// arena it does not own, or an embedding where cudaMalloc is forbidden after start-up because it synchronises the
+// device.  For them the scratch lives in the fixed array below, which every GPU that loads this library holds from
+// module load until the process exits.
+//
+// The array's name is only a host-side handle: passing `g_static_scratch` itself to a kernel would hand it a host
+// address.  Its device address is looked up once per device with cudaGetSymbolAddress, with that device current, on the
+// first call made for that device; do that first call before starting any stream capture.
+// ---------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[CGB200_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};   // device address of g_static_scratch, per device ordinal
+}  // namespace
+
+int cgb200_layer_fwd_static(const cgb200_plan* p, const float* F, const float* W, float* stds, float cnt, float eps,
+                            int flags, float* O, int64_t B, void* stream) {
+    CGB_REQUIRE(p != nullptr, "plan is null");
+    CGB_REQUIRE(B >= 0, "negative batch size");
+    const int64_t need = cgb200_layer_workspace_bytes(p, B);
+    if (need < 0) return CGB200_ERR_ARGUMENT;
+    if (need > (int64_t)CGB200_STATIC_SCRATCH_BYTES) {
+        set_error("cgb200_layer_fwd_static: this plan and batch need " + std::to_string(need) +
+                  " bytes of scratch, the built-in array holds " + std::to_string((int64_t)CGB200_STATIC_SCRATCH_BYTES) +
+                  "; use a smaller batch or cgb200_layer_fwd with a caller-provided workspace");
+        return CGB200_ERR_WORKSPACE;
+    }
+    int dev = -1;
+    CGB_CUDA(cudaGetDevice(&dev));
+    CGB_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal out of range for the built-in scratch table");
+    CGB_REQUIRE(dev == p->device, "the plan belongs to another CUDA device than the current one");
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        CGB_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        CGB_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    // Nothing in the array has to survive from one call to the next and nothing is assumed to be zero: the prep
+    // kernel rewrites the slab (padding channels included), the norm factors and the row counters on every call.
+    return cgb200_layer_fwd(p, F, W, stds, cnt, eps, flags, O, B, g_static_scratch_ptr[dev],
+                            (int64_t)CGB200_STATIC_SCRATCH_BYTES, stream);
+}
+
 }  // extern "C"

@@ -139,6 +139,26 @@ int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, co
 /* Scratch bytes the two fused calls need for a batch of B samples (the larger of the two). */
 int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
 
+/*
+ * cgb200_layer_fwd for callers that cannot allocate device memory (no counterpart in the reference, whose Python
+ * layer always allocates through torch).  Same arguments and results, minus the workspace: the scratch is a fixed
+ * array of CGB200_STATIC_SCRATCH_BYTES inside the library, resident on every GPU that loads it for the life of the
+ * process.  Meant for hosts where an allocation is impossible or forbidden at call time: a plugin running inside
+ * another runtime's callback, a process whose device memory belongs to a foreign arena, a service that bans
+ * cudaMalloc after start-up because it stalls the device.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Returns CGB200_ERR_WORKSPACE, with the needed and available byte counts in cgb200_last_error(), when
+ *     cgb200_layer_workspace_bytes(plan, B) exceeds the array.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the last call left in it.  The call itself
+ *     rewrites everything it reads (nothing needs to be zeroed by the caller), but two calls whose kernels overlap on
+ *     the GPU - different streams, or different threads - race on it: serialise them on one stream.
+ */
+#define CGB200_STATIC_SCRATCH_BYTES (8u << 20)
+int cgb200_layer_fwd_static(const cgb200_plan* plan, const float* F, const float* W, float* stds, float cnt, float eps,
+                            int flags, float* O, int64_t B, void* stream);
+
 /* Number of kernels this library launched in this process since the last reset (bench accounting). */
 int64_t cgb200_launch_count(int reset);
 
