@@ -1,0 +1,158 @@
+"""Our kernels against the reference project's own CUDA kernels on the same GPU and the same seeded inputs.
+
+The reference extension `CG_cuda_ops` (CGNet/cudaCG, unmodified sources) is compiled for sm_100a by
+`python oracle/build_ref_cuda.py` into oracle/_ref/cuda_build/ (git-ignored, shipped with the tree).  Its six functions
+are called directly with index tensors laid out as CGNet/CG_layers.py builds them (:244-250, :104-108); the reference's
+Python files are not needed.  Skipped when the extension has not been built.  Tolerance: relative Frobenius error per
+fragment < 1e-4 (fp32 on both sides)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cg_oracle as o
+from helpers import assert_fragments_close, assert_weights_close, make_case
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "cuda_build", "CG_cuda_ops.so")
+
+
+@pytest.fixture(scope="module")
+def ref_ops():
+    if not os.path.exists(REF_SO):
+        pytest.skip("reference CUDA extension not built (python oracle/build_ref_cuda.py)")
+    spec = importlib.util.spec_from_file_location("CG_cuda_ops", REF_SO)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def it(x):
+    return torch.tensor(np.asarray(x, dtype=np.int64), dtype=torch.int, device=dev())
+
+
+class RefLayer:
+    """The index tensors of CG_woFilter_cuda / MyBatchNormWeightMM_cuda and thin calls into the reference kernels."""
+
+    def __init__(self, ops, case):
+        self.ops, self.c = ops, case
+        L, taus, tau_out, llls = case["lmax"], case["taus"], case["tau_out"], case["llls"]
+        self.L = L
+        ltuples = [[] for _ in range(L + 1)]
+        for l, l1, l2 in o.decode_triples(L, llls):
+            ltuples[l].append((l1, l2))
+        _, table = o.encode_sorted(ltuples)
+        t_ff, t_off = o.tau_ff_and_offsets(L, taus, llls)
+        self.t_ff = t_ff
+        self.d_t_F, self.d_cum_F = it(taus), it(o.cumulative_tm(taus))
+        self.d_t_FF, self.d_cum_FF = it(t_ff), it(o.cumulative_tm(t_ff))
+        self.d_t_O, self.d_cum_O = it(tau_out), it(o.cumulative_tm(tau_out))
+        self.d_cum_W = it(np.concatenate([[0], np.cumsum(t_ff * np.asarray(tau_out))]))
+        self.d_llls, self.d_table = it(llls), it(table)
+        self.d_t_off = it(list(t_off) + [2 ** 30])   # one spare entry: the kernel may peek one past the last triple
+        offs = o.cg_offsets(L, llls)
+        self.d_cg_off = it(offs)
+        self.CG = torch.zeros(offs[-1], dtype=torch.float, device=dev())
+        ops.sparse_precomputeCG(self.CG, L, self.d_llls, self.d_cg_off)
+        self.n_FF, self.n_O = int(o.cumulative_tm(t_ff)[-1]), int(o.cumulative_tm(tau_out)[-1])
+        self.w_len, self.sum_tff = int((t_ff * np.asarray(tau_out)).sum()), int(t_ff.sum())
+
+    def product_fwd(self, F):
+        FF = torch.zeros(F.shape[0], self.n_FF, 2, device=dev())
+        self.ops.sparse_forward(F, FF, self.L, F.shape[0], self.d_t_F, self.d_cum_F, self.d_t_FF, self.d_cum_FF, self.d_llls,
+                                self.d_table, self.d_t_off, self.CG, self.d_cg_off)
+        return FF
+
+    def product_bwd(self, F, gFF):
+        gF = torch.zeros_like(F)
+        self.ops.sparse_backward(F, gF, gFF, self.L, F.shape[0], self.d_t_F, self.d_cum_F, self.d_t_FF, self.d_cum_FF, self.d_llls,
+                                 self.d_t_off, self.CG, self.d_cg_off)
+        return gF
+
+    def mix_fwd(self, FF, W, stds, cnt, eps, flags):
+        O = torch.zeros(FF.shape[0], self.n_O, 2, device=dev())
+        self.ops.FN_WMM_forward(FF, O, W, self.L, FF.shape[0], self.sum_tff, self.n_O, self.d_t_FF, self.d_cum_FF, self.d_cum_O,
+                                self.d_cum_W, stds if stds is not None else torch.full((1,), eps, device=dev()), cnt, eps, flags)
+        return O
+
+    def mix_bwd(self, gO, FF, W, stds, cnt, eps, flags):
+        gFF, gW = torch.zeros_like(FF), torch.zeros_like(W)
+        self.ops.FN_WMM_backward(gO, gFF, gW, FF, W, self.L, FF.shape[0], self.n_FF, self.w_len, self.d_t_FF, self.d_cum_FF,
+                                 self.d_t_O, self.d_cum_O, self.d_cum_W,
+                                 stds if stds is not None else torch.full((1,), eps, device=dev()), cnt, eps, flags)
+        return gFF, gW
+
+
+CASES = [
+    ([2, 1], [2, 1], 2, "mst"),
+    ([3, 2, 1, 1, 1], [3, 2, 1, 1, 1], 1, "default"),
+    ([4] * 6, [4] * 6, 3, "default"),
+    ([3, 1, 4, 1, 5, 2, 2], [2, 3, 1, 4, 1, 2, 3], 2, "mst"),
+    ([8] * 6, [8] * 6, 32, "default"),          # BASELINE config 1 shape
+    ([5] * 11, [5] * 11, 20, "default"),        # one layer of BASELINE config 2 at a fifth of its batch
+    ([1] * 11, [5] * 11, 20, "default"),        # its first layer
+    ([4] * 11, [3] * 11, 5, "mst"),
+]
+
+
+@pytest.mark.parametrize("taus,tau_out,B,mode", CASES)
+def test_cg_table_and_product_match_reference_kernels(ref_ops, taus, tau_out, B, mode):
+    from cgnet_b200 import get_plan
+    case = make_case(taus, tau_out, B, mode, seed=41)
+    ref = RefLayer(ref_ops, case)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], dev())
+    from cgnet_b200.cg_layers import _precomputeCG_cuda
+    ours_cg, _ = _precomputeCG_cuda(case["lmax"], case["llls"], dev())
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(ours_cg.cpu().numpy(), ref.CG.cpu().numpy(), atol=3e-7, rtol=0)
+    F = torch.tensor(case["F"], device=dev())
+    gFF = torch.tensor(case["gFF"], device=dev())
+    assert_fragments_close(plan.cg_product_fwd(F).cpu().numpy(), ref.product_fwd(F).cpu().numpy(), ref.t_ff, "FF vs reference kernel")
+    assert_fragments_close(plan.cg_product_bwd(F, gFF).cpu().numpy(), ref.product_bwd(F, gFF).cpu().numpy(), taus,
+                           "product gF vs reference kernel")
+
+
+@pytest.mark.parametrize("bn,training", [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("taus,tau_out,B,mode", CASES)
+def test_layer_matches_reference_kernels(ref_ops, taus, tau_out, B, mode, bn, training):
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, mode, seed=42)
+    ref = RefLayer(ref_ops, case)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], dev())
+    F = torch.tensor(case["F"], device=dev())
+    W = torch.tensor(case["W"], device=dev())
+    gO = torch.tensor(case["gO"], device=dev())
+    flags = (1 if bn else 0) | (2 if training else 0)
+    cnt, eps = 2.0, 1e-5
+
+    r_stds = torch.tensor(case["stds"], device=dev()) if bn else None
+    r_FF = ref.product_fwd(F)
+    r_O = ref.mix_fwd(r_FF, W, r_stds, cnt, eps, flags)
+    r_gFF, r_gW = ref.mix_bwd(gO, r_FF, W, r_stds, cnt, eps, flags)
+    r_gF = ref.product_bwd(F, r_gFF)
+    torch.cuda.synchronize()
+
+    for fused in (False, True):
+        stds = torch.tensor(case["stds"], device=dev()) if bn else None
+        if fused:
+            O = plan.layer_fwd(F, W, stds, cnt, eps, flags)
+            gF, gW = plan.layer_bwd(F, W, stds, eps, flags & _lib.FN_PRESENT, gO)
+        else:
+            FF = plan.cg_product_fwd(F)
+            O = plan.fn_wmm_fwd(FF, W, stds, cnt, eps, flags)
+            gFF, gW = plan.fn_wmm_bwd(gO, FF, W, stds, eps, flags & _lib.FN_PRESENT)
+            gF = plan.cg_product_bwd(F, gFF)
+        tag = "fused" if fused else "two-pass"
+        assert_fragments_close(O.cpu().numpy(), r_O.cpu().numpy(), tau_out, f"O ({tag}) vs reference kernels")
+        assert_weights_close(gW.cpu().numpy(), r_gW.cpu().numpy(), ref.t_ff, tau_out, f"gW ({tag}) vs reference kernels")
+        assert_fragments_close(gF.cpu().numpy(), r_gF.cpu().numpy(), taus, f"gF ({tag}) vs reference kernels")
+        if training:
+            np.testing.assert_allclose(stds.cpu().numpy(), r_stds.cpu().numpy(), rtol=2e-5, atol=1e-7)
