@@ -195,25 +195,25 @@ __host__ __device__ inline int fwd_stage_bytes(int step, int nv, int max_n) {
     return ((step * nv * 8 + nv * 4 + max_n * 4) + 15) & ~15;
 }
 
-template <int T, bool DW, int NW>
+template <int T, bool DW, int NW, int NTO>
 __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restrict__ slab, const float2* __restrict__ W,
                                         const float* __restrict__ inv, float2* __restrict__ O, float2* __restrict__ red,
-                                        unsigned char* __restrict__ stage, int red_to, int l, int mi, int b, int B, int warp,
-                                        int lane) {
+                                        unsigned char* __restrict__ stage, int l, int mi, int b, int B, int warp, int lane) {
     constexpr int NV = TileShape<T, DW>::NV;
     const int n = 2 * l + 1;
     const int to_n = P.tO[l];
     const int tff = P.tFF[l];
     const int c_begin = P.cell_begin[l], c_end = P.cell_begin[l + 1];
     const float2* Wl = W + P.cumW[l];
-    const int step = min(kFwdTo, red_to);
+    constexpr int step = NTO;   // output channels per pass, a compile-time constant so that no issue slot is wasted
+    constexpr int red_to = NTO;
     float2* wbuf = reinterpret_cast<float2*>(stage);          // [step][NV]
     float* ibuf = reinterpret_cast<float*>(wbuf + step * NV);  // [NV]
     float* cbuf = ibuf + NV;                                   // [2*l2+1]
     for (int to0 = 0; to0 < to_n; to0 += step) {
-        float2 o[kFwdTo];
+        float2 o[NTO];
 #pragma unroll
-        for (int t = 0; t < kFwdTo; ++t) o[t] = make_float2(0.f, 0.f);
+        for (int t = 0; t < NTO; ++t) o[t] = make_float2(0.f, 0.f);
         int c = c_begin + warp;
         CellInfo ci;
         if (c < c_end) ci = P.cell_info[c];
@@ -243,16 +243,14 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
                 const float sc = ibuf[idx];
                 const float2 x = make_float2(v[idx].x * sc, v[idx].y * sc);
 #pragma unroll
-                for (int t = 0; t < kFwdTo; ++t)
-                    if (t < step) cfma(o[t], wbuf[t * NV + idx], x);   // masked entries carry zero weights
+                for (int t = 0; t < NTO; ++t) cfma(o[t], wbuf[t * NV + idx], x);   // masked entries carry zero weights
             }
             ci = nxt;
             c = cn;
         }
         __syncthreads();   // protects `red` from the previous pass / row
 #pragma unroll
-        for (int t = 0; t < kFwdTo; ++t)
-            if (t < step) red[(warp * red_to + t) * 32 + lane] = o[t];
+        for (int t = 0; t < NTO; ++t) red[(warp * red_to + t) * 32 + lane] = o[t];
         __syncthreads();
         for (int t = warp; t < step && to0 + t < to_n; t += NW) {
             float2 s = red[t * 32 + lane];
@@ -267,27 +265,29 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
 }
 
 // rows as independent blocks; the slab is read through L1.  grid = (rows, groups)
-template <int T, bool DW>
+template <int T, bool DW, int NTO>
 __global__ void __launch_bounds__(kFwdWarps * kWarp)
 fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restrict__ SF, const float2* __restrict__ W,
-                 const float* __restrict__ inv, float2* __restrict__ O, int B, int red_to, int stage_bytes) {
+                 const float* __restrict__ inv, float2* __restrict__ O, int B, int stage_bytes) {
+    constexpr int red_to = NTO;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* red = reinterpret_cast<float2*>(smem_raw);
     const int l = rows[2 * blockIdx.x], mi = rows[2 * blockIdx.x + 1];
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* stage = smem_raw + (size_t)kFwdWarps * red_to * 32 * sizeof(float2) + (size_t)warp * stage_bytes;
-    fwd_row<T, DW, kFwdWarps>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, stage, red_to, l, mi, g * 32 + lane, B,
-                              warp, lane);
+    fwd_row<T, DW, kFwdWarps, NTO>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, stage, l, mi, g * 32 + lane, B, warp,
+                                   lane);
 }
 
 // persistent blocks: block (p, g) copies group g's slab into shared memory once, then pulls rows (most expensive
 // first) from the group's counter until none is left.  grid = (blocks per group, groups)
-template <int T, bool DW>
+template <int T, bool DW, int NTO>
 __global__ void __launch_bounds__(kSlabWarps * kWarp)
 fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const float2* __restrict__ SF,
                       const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ O, int B,
-                      int* __restrict__ counters, int red_to, int stage_bytes) {
+                      int* __restrict__ counters, int stage_bytes) {
+    constexpr int red_to = NTO;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int next_row;
     float2* slab = reinterpret_cast<float2*>(smem_raw);
@@ -307,32 +307,33 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
         __syncthreads();
         const int r = next_row;
         if (r >= n_rows) break;
-        fwd_row<T, DW, kSlabWarps>(P, slab + lane, W, inv, O, red, stage, red_to, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B,
-                                   warp, lane);
+        fwd_row<T, DW, kSlabWarps, NTO>(P, slab + lane, W, inv, O, red, stage, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B, warp,
+                                        lane);
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
 // weight gradient, full product.  Warp-task = (triple, I consecutive t1 inside one tile, one t2 tile, one tau_out
 // tile).  A lane keeps acc[o][i][j] for its own sample; the sample groups are visited in order and the lanes summed at
-// the end.  Tasks are taken from the end of the list first: the high degrees have the long bands.
+// the end.  The task list is sorted by cost, most expensive first, so the blocks that start first carry the long bands
+// and the cheap tasks fill the tail.
 // ---------------------------------------------------------------------------------------------------------------
 template <int T, int I>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
-                int band_floats) {
+                int band_floats, int* __restrict__ queue) {
     extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
-    if (task < 0) return;
+    float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the current triple's CG band
+    for (int task = blockIdx.x * kGwWarps + warp; task < n_tasks; task += gridDim.x * kGwWarps) {
     const GwTask tk = tasks[task];
     const TripleRec tr = P.triples[tk.triple];
     const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int to_n = P.tO[l], tff = P.tFF[l];
     const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
     const int j0 = tk.gi * I;
-    float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the triple's CG band
+    __syncwarp();   // the previous task's readers are done with the band
     for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
     __syncwarp();
     const float* C = band;
@@ -407,6 +408,7 @@ fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const 
                     gW[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
                 }
             }
+    }
 }
 
 // weight gradient, depthwise product: warp-task = (triple, t tile, tau_out tile); FF tile generated directly.
@@ -417,8 +419,8 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
                    int band_floats) {
     extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int task = n_tasks - 1 - (blockIdx.x * kGwWarps + warp);
-    if (task < 0) return;
+    const int task = blockIdx.x * kGwWarps + warp;   // the task list is sorted, most expensive first
+    if (task >= n_tasks) return;
     const GwTask tk = tasks[task];
     const TripleRec tr = P.triples[tk.triple];
     const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
@@ -472,10 +474,10 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
 // This is CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289 with gFF living only as one tile
 // in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kGfWarps = 16;
+constexpr int kGfWarpsMax = 16;
 
 template <int T, bool DW>
-__global__ void __launch_bounds__(kGfWarps * kWarp)
+__global__ void __launch_bounds__(kGfWarpsMax * kWarp)
 fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
                 const int* __restrict__ blocks, const float2* __restrict__ SF, const float2* __restrict__ SG,
                 const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ out,
@@ -487,6 +489,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     const int nt = 2 * lt + 1, t_0 = q * T;
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
     const int tau_t = P.tF[lt];
     float2* acc = reinterpret_cast<float2*>(smem_raw);          // [T][nt][32]
     float2* fo = acc + (size_t)T * max_n * 32;                   // [n_o][T][32]  other operand's tile
@@ -535,7 +538,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
         for (int mc0 = 0; mc0 < n; mc0 += Mc) {
             const int mcn = min(Mc, n - mc0);
             __syncthreads();   // staging visible; the previous chunk's readers are done with H
-            for (int mi = mc0 + warp; mi < mc0 + mcn; mi += kGfWarps) {
+            for (int mi = mc0 + warp; mi < mc0 + mcn; mi += nwarps) {
                 float2 gt[NH];
 #pragma unroll
                 for (int k = 0; k < NH; ++k) gt[k] = make_float2(0.f, 0.f);
@@ -550,7 +553,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
                 for (int k = 0; k < NH; ++k) h[k * 32] = gt[k];
             }
             __syncthreads();
-            for (int r = warp; r < nt; r += kGfWarps) {
+            for (int r = warp; r < nt; r += nwarps) {
                 const int mt = r - lt;   // m of the owned element
                 float2 x[T];
 #pragma unroll
@@ -715,6 +718,15 @@ int launch_prep(const cgb200_plan* p, const PrepJob& a, const PrepJob& b, int nj
 
 }  // namespace
 
+// Run a statement with NN bound to the forward kernels' output-channel width as a compile-time constant.
+#define CGB_DISPATCH_NTO(N_, ...)                                         \
+    switch (N_) {                                                         \
+        case 4: { constexpr int NN = 4; __VA_ARGS__; break; }             \
+        case 5: { constexpr int NN = 5; __VA_ARGS__; break; }             \
+        case 8: { constexpr int NN = 8; __VA_ARGS__; break; }             \
+        default: { constexpr int NN = 16; __VA_ARGS__; break; }           \
+    }
+
 template <int T>
 struct GwI {
     static constexpr int value = T == 1 ? 4 : T == 2 ? 4 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1;
@@ -764,7 +776,9 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     if (n_rows == 0) return CGB200_OK;
     // persistent shared-memory variant when one group's slab (plus reduction buffer and staging areas) fits in an SM
     const int NVh = p->d.depthwise ? T : T * T;
-    const int red_to = std::min(kFwdTo, std::max(p->max_tau_out, 1));
+    // output channels per pass: the smallest instantiated width that covers the widest degree (at most kFwdTo)
+    const int want_to = std::min(kFwdTo, std::max(p->max_tau_out, 1));
+    const int red_to = want_to <= 4 ? 4 : want_to == 5 ? 5 : want_to <= 8 ? 8 : 16;
     const int stage_bytes = fwd_stage_bytes(red_to, NVh, p->max_n);
     const size_t slab_bytes = (size_t)p->d.nSF * 32 * sizeof(float2);
     const size_t smem_slab = slab_bytes + (size_t)kSlabWarps * (red_to * 32 * sizeof(float2) + stage_bytes);
@@ -779,19 +793,19 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     launch_begin(K_FWD, st);
     if (use_slab) {
         const int per_group = std::max(1, std::min(n_rows, p->num_sms / G));
-        CGB_DISPATCH_TILE(T, p->d.depthwise, {
-            auto kern = fused_fwd_slab_kernel<TT, DD>;
+        CGB_DISPATCH_TILE(T, p->d.depthwise, CGB_DISPATCH_NTO(red_to, {
+            auto kern = fused_fwd_slab_kernel<TT, DD, NN>;
             CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_slab));
             kern<<<dim3(per_group, G), kSlabWarps * kWarp, smem_slab, st>>>(p->d, p->d_fwd_rows, n_rows, ws.SF, (const float2*)W,
-                                                                         ws.inv, (float2*)O, (int)B, ws.counters, red_to, stage_bytes);
-        });
+                                                                         ws.inv, (float2*)O, (int)B, ws.counters, stage_bytes);
+        }));
     } else {
-        CGB_DISPATCH_TILE(T, p->d.depthwise, {
-            auto kern = fused_fwd_kernel<TT, DD>;
+        CGB_DISPATCH_TILE(T, p->d.depthwise, CGB_DISPATCH_NTO(red_to, {
+            auto kern = fused_fwd_kernel<TT, DD, NN>;
             if (smem_rows > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows));
             kern<<<dim3(n_rows, G), kFwdWarps * kWarp, smem_rows, st>>>(p->d, p->d_fwd_rows, ws.SF, (const float2*)W, ws.inv, (float2*)O,
-                                                                     (int)B, red_to, stage_bytes);
-        });
+                                                                     (int)B, stage_bytes);
+        }));
     }
     launch_end(K_FWD, st);
     CGB_CUDA(cudaGetLastError());
@@ -845,7 +859,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             CGB_DISPATCH_TILE(T, false, {
                 auto kern = fused_gw_kernel<TT, GwI<TT>::value>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<blocks, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
+                const int grid = blocks;
+                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats, ws.counters);
             });
         }
         launch_end(K_GW, st);
@@ -873,7 +888,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = fused_gf_kernel<TT, DD>;
             if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+            const int nwarps = kGfWarpsMax;
+            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
         });
         if (split) {
             launch_end(K_GF, st);

@@ -486,6 +486,22 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
                         p->gw_tasks.push_back({k, (short)q1, (short)gi, (short)q2, (short)qo});
         CGB_REQUIRE((int)p->gw_tasks.size() == p->gw_begin[k + 1], "internal: weight-gradient task count");
     }
+    {   // the warps of the weight-gradient kernel pull tasks from a queue: most expensive first
+        auto cost = [&](const GwTask& tk) {
+            const TripleRec& t = p->triples[tk.triple];
+            double nnz = 0;
+            for (int m = -t.l; m <= t.l; ++m) nnz += std::min(t.l2, m + t.l1) - std::max(-t.l2, m - t.l1) + 1;
+            return nnz + 6.0 * (2 * t.l2 + 1);
+        };
+        std::vector<std::pair<double, int>> order;
+        order.reserve(p->gw_tasks.size());
+        for (size_t i = 0; i < p->gw_tasks.size(); ++i) order.push_back({cost(p->gw_tasks[i]), (int)i});
+        std::stable_sort(order.begin(), order.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+        std::vector<GwTask> sorted;
+        sorted.reserve(order.size());
+        for (auto& o : order) sorted.push_back(p->gw_tasks[o.second]);
+        p->gw_tasks.swap(sorted);
+    }
     if ((rc = upload(p, p->gw_begin, &p->d_gw_begin))) return rc;
     if ((rc = upload(p, p->gw_tasks, &p->d_gw_tasks))) return rc;
     // entries of the fused input-gradient kernel, per fragment
