@@ -895,7 +895,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());
             const int gx = (int)((p->d.n_F + 255) / 256);
-            launch_begin(K_GF, st);
+            launch_begin(K_GF_REDUCE, st);
             gf_reduce_kernel<<<dim3(gx, (unsigned)std::min<int64_t>(B, 65535)), 256, 0, st>>>(p->d, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF, (int)B);
         }
         launch_end(K_GF, st);
