@@ -137,8 +137,8 @@ class Plan:
                                                     _ptr(ws), n, _stream_ptr(self.device)), "cgb200_layer_fwd")
         return O
 
-    def layer_bwd(self, F, W, stds, eps, flags, gO):
-        gF = torch.empty_like(F)
+    def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True):
+        gF = torch.empty_like(F) if need_gF else None
         gW = torch.empty_like(W)
         ws, n = self._workspace(F.shape[0])
         with torch.cuda.device(self.device):
@@ -260,7 +260,8 @@ class _CGBN_fused(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         Fs, W, stds = ctx.saved_tensors
-        gF, gW = ctx.plan.layer_bwd(Fs, W, stds, ctx.eps, ctx.flags, _check_cuda_f32(grad_output, "grad_output"))
+        gF, gW = ctx.plan.layer_bwd(Fs, W, stds, ctx.eps, ctx.flags, _check_cuda_f32(grad_output, "grad_output"),
+                                    need_gF=ctx.needs_input_grad[0])
         return gF, gW, None, None, None, None, None
 
 

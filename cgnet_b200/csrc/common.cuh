@@ -196,6 +196,7 @@ struct cgb200_plan {
     std::vector<int> gw_begin;        // [n_triples+1] warp-tasks of the fused weight-gradient kernel per triple
     const int* d_gw_begin = nullptr;
     int gw_i = 1;                     // t1 channels per weight-gradient task
+    int gw_to = 1;                    // output channels per weight-gradient task
     std::vector<cgb200::GfEntry> gf_entries;
     std::vector<int> gf_begin;        // [lmax+2] entries of fragment l
     const cgb200::GfEntry* d_gf_entries = nullptr;

@@ -318,96 +318,102 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
 // the end.  The task list is sorted by cost, most expensive first, so the blocks that start first carry the long bands
 // and the cheap tasks fill the tail.
 // ---------------------------------------------------------------------------------------------------------------
-template <int T, int I>
+template <int T, int I, int TO>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
-                int band_floats, int* __restrict__ queue) {
+                int band_floats) {
     extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the current triple's CG band
     for (int task = blockIdx.x * kGwWarps + warp; task < n_tasks; task += gridDim.x * kGwWarps) {
-    const GwTask tk = tasks[task];
-    const TripleRec tr = P.triples[tk.triple];
-    const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
-    const int to_n = P.tO[l], tff = P.tFF[l];
-    const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
-    const int j0 = tk.gi * I;
-    __syncwarp();   // the previous task's readers are done with the band
-    for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
-    __syncwarp();
-    const float* C = band;
-    int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
+        const GwTask tk = tasks[task];
+        const TripleRec tr = P.triples[tk.triple];
+        const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
+        const int to_n = P.tO[l], tff = P.tFF[l];
+        const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
+        const int j0 = tk.gi * I;
+        __syncwarp();   // the previous task's readers are done with the band
+        for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
+        __syncwarp();
+        const float* C = band;
+        int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
 #pragma unroll
-    for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
-
-    float2 acc[T][I][T];
+        for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
+        int goff[TO];  // slab offset of output channel qo*TO+o at m index 0 (clamped to the last channel, masked at the end)
 #pragma unroll
-    for (int o = 0; o < T; ++o)
-#pragma unroll
-        for (int i = 0; i < I; ++i)
-#pragma unroll
-            for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
-
-    for (int g = 0; g < G; ++g) {
-        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
-        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
-        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l] + qo * n * T) * 32 + lane;
-        for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
-            float2 Y[T][I];
-#pragma unroll
-            for (int o = 0; o < T; ++o)
-#pragma unroll
-                for (int i = 0; i < I; ++i) Y[o][i] = make_float2(0.f, 0.f);
-            const int mlo = max(-l, m2 - tr.l1), mhi = min(l, m2 + tr.l1);
-            const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
-            const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
-            const float2* pg = go + (mlo + l) * (T * 32);
-            for (int k = mhi - mlo; k >= 0; --k) {
-                const float c = *pc;
-                float2 a[I];
-#pragma unroll
-                for (int i = 0; i < I; ++i) {
-                    a[i] = p1[jrow[i] * 32];
-                    a[i].x *= c;
-                    a[i].y *= c;
-                }
-#pragma unroll
-                for (int o = 0; o < T; ++o) {
-                    const float2 gv = pg[o * 32];
-#pragma unroll
-                    for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
-                }
-                pc += n2;
-                p1 += T * 32;
-                pg += T * 32;
-            }
-            const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
-            float2 bj[T];
-#pragma unroll
-            for (int j = 0; j < T; ++j) bj[j] = p2[j * 32];
-#pragma unroll
-            for (int o = 0; o < T; ++o)
-#pragma unroll
-                for (int i = 0; i < I; ++i)
-#pragma unroll
-                    for (int j = 0; j < T; ++j) cfma_conj(acc[o][i][j], bj[j], Y[o][i]);
+        for (int o = 0; o < TO; ++o) {
+            const int to = min(qo * TO + o, to_n - 1);
+            goff[o] = ((to / T) * n * T + to % T) * 32;
         }
-    }
+
+        float2 acc[TO][I][T];
 #pragma unroll
-    for (int o = 0; o < T; ++o)
+        for (int o = 0; o < TO; ++o)
 #pragma unroll
-        for (int i = 0; i < I; ++i)
+            for (int i = 0; i < I; ++i)
 #pragma unroll
-            for (int j = 0; j < T; ++j) {
-                const float sx = warp_sum(acc[o][i][j].x), sy = warp_sum(acc[o][i][j].y);
-                const int t1 = q1 * T + j0 + i, t2 = q2 * T + j, to = qo * T + o;
-                if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
-                    const int ch = t1 * tr.tau2 + t2;
-                    const float s = inv[tr.kglob + ch];
-                    gW[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
+                for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
+
+        for (int g = 0; g < G; ++g) {
+            const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
+            const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
+            const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
+            for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
+                float2 Y[TO][I];
+#pragma unroll
+                for (int o = 0; o < TO; ++o)
+#pragma unroll
+                    for (int i = 0; i < I; ++i) Y[o][i] = make_float2(0.f, 0.f);
+                const int mlo = max(-l, m2 - tr.l1), mhi = min(l, m2 + tr.l1);
+                const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
+                const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
+                const float2* pg = go + (mlo + l) * (T * 32);
+                for (int k = mhi - mlo; k >= 0; --k) {
+                    const float c = *pc;
+                    float2 a[I];
+#pragma unroll
+                    for (int i = 0; i < I; ++i) {
+                        a[i] = p1[jrow[i] * 32];
+                        a[i].x *= c;
+                        a[i].y *= c;
+                    }
+#pragma unroll
+                    for (int o = 0; o < TO; ++o) {
+                        const float2 gv = pg[goff[o]];
+#pragma unroll
+                        for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
+                    }
+                    pc += n2;
+                    p1 += T * 32;
+                    pg += T * 32;
                 }
+                const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
+                float2 bj[T];
+#pragma unroll
+                for (int j = 0; j < T; ++j) bj[j] = p2[j * 32];
+#pragma unroll
+                for (int o = 0; o < TO; ++o)
+#pragma unroll
+                    for (int i = 0; i < I; ++i)
+#pragma unroll
+                        for (int j = 0; j < T; ++j) cfma_conj(acc[o][i][j], bj[j], Y[o][i]);
             }
+        }
+#pragma unroll
+        for (int o = 0; o < TO; ++o)
+#pragma unroll
+            for (int i = 0; i < I; ++i)
+#pragma unroll
+                for (int j = 0; j < T; ++j) {
+                    const float sx = warp_sum(acc[o][i][j].x), sy = warp_sum(acc[o][i][j].y);
+                    const int t1 = q1 * T + j0 + i, t2 = q2 * T + j, to = qo * TO + o;
+                    if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
+                        const int ch = t1 * tr.tau2 + t2;
+                        const float s = inv[tr.kglob + ch];
+                        gW[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
+                    }
+                }
     }
 }
 
@@ -728,8 +734,9 @@ int launch_prep(const cgb200_plan* p, const PrepJob& a, const PrepJob& b, int nj
     }
 
 template <int T>
-struct GwI {
-    static constexpr int value = T == 1 ? 4 : T == 2 ? 4 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1;
+struct GwShape {   // must match kGwI / kGwTo of the plan
+    static constexpr int I = T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1;
+    static constexpr int TO = T == 1 ? 8 : T == 2 ? 8 : T == 3 ? 4 : T == 4 ? 4 : T == 5 ? 5 : 6;
 };
 
 extern "C" {
@@ -828,7 +835,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         }
         return CGB200_OK;
     }
-    CGB_REQUIRE(F != nullptr && gF != nullptr && (gO != nullptr || p->d.n_O == 0), "null buffer");
+    CGB_REQUIRE(F != nullptr && (gO != nullptr || p->d.n_O == 0), "null buffer");
     CGB_REQUIRE(p->d.w_len == 0 || (W != nullptr && gW != nullptr), "W or gW is null");
     const int G = (int)((B + 31) / 32);
     Workspace ws = carve(p, B, workspace);
@@ -857,18 +864,18 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             });
         } else {
             CGB_DISPATCH_TILE(T, false, {
-                auto kern = fused_gw_kernel<TT, GwI<TT>::value>;
+                auto kern = fused_gw_kernel<TT, GwShape<TT>::I, GwShape<TT>::TO>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                 const int grid = blocks;
-                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats, ws.counters);
+                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
             });
         }
         launch_end(K_GW, st);
         CGB_CUDA(cudaGetLastError());
     }
 
-    // input gradient
-    if (p->d.n_F > 0) {
+    // input gradient (skipped when the caller passes no buffer: the first layer of a network needs none)
+    if (p->d.n_F > 0 && gF != nullptr) {
         const int lv = ws.gf_level;
         const int nblk = (int)p->gf2_blocks[lv].size() / 4;
         const bool split = p->gf2_max_parts[lv] > 1;

@@ -467,12 +467,15 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     if ((rc = upload(p, p->gen_items, &p->d_gen_items))) return rc;
 
     // warp-tasks of the fused weight-gradient kernel: (t1 group, t2 tile, tau_out tile) per triple
-    static const int kGwI[kMaxTile + 1] = {0, 4, 4, 3, 2, 2, 1};
+    // rows of t1 and output channels per task, by tile edge: about 32..50 complex accumulators per lane
+    static const int kGwI[kMaxTile + 1] = {0, 1, 2, 3, 2, 2, 1};
+    static const int kGwTo[kMaxTile + 1] = {0, 8, 8, 4, 4, 5, 6};
     p->gw_i = dw ? T : kGwI[T];
+    p->gw_to = dw ? T : kGwTo[T];
     p->gw_begin.assign(n + 1, 0);
     for (int k = 0; k < n; ++k) {
         const TripleRec& t = p->triples[k];
-        const int64_t no = (p->tO[t.l] + T - 1) / T;
+        const int64_t no = (p->tO[t.l] + p->gw_to - 1) / p->gw_to;
         // t1 groups never straddle a channel tile: ceil(T / I) groups per tile
         const int64_t ni = dw ? t.nt1 : (int64_t)t.nt1 * ((T + p->gw_i - 1) / p->gw_i);
         const int64_t cnt = dw ? ni * no : ni * t.nt2 * no;

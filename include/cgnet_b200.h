@@ -130,7 +130,8 @@ int cgb200_layer_fwd(const cgb200_plan* plan, const float* F, const float* W, fl
 /*
  * Gradients of the whole layer, (F, W, stds, gO) -> (gF, gW), regenerating FF on the fly.
  * Replaces `FN_WMM_backward` + `sparse_backward` issued by autograd (CGNet/CG_layers.py:54-72, 194-203).
- * `stds` must be the values the forward used (i.e. after its update).
+ * `stds` must be the values the forward used (i.e. after its update).  gF may be NULL when the gradient with respect
+ * to the input is not wanted (the first layer of a network): that part of the work is then skipped.
  */
 int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, const float* stds, float eps, int flags,
                      const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,

@@ -234,3 +234,20 @@ def test_empty_batch_and_bad_arguments():
     rc = lib.cgb200_layer_fwd(plan.handle, t(one["F"]).data_ptr(), t(one["W"]).data_ptr(), None, 1.0, 1e-5, 0, Od.data_ptr(), 4,
                               ws.data_ptr(), 256, None)
     assert rc == 4 and b"workspace" in lib.cgb200_last_error()
+
+
+def test_input_gradient_is_optional():
+    """A layer whose input needs no gradient (the first layer of a network) skips that part of the backward."""
+    from cgnet_b200 import CGBN_cuda, _lib
+    case = make_case([1] * 5, [4] * 5, 9, "default", seed=17)
+    plan = plan_for(case)
+    F, W, gO = t(case["F"]), t(case["W"]), t(case["gO"])
+    gF_full, gW_full = plan.layer_bwd(F, W, None, 1e-5, 0, gO)
+    gF_none, gW_only = plan.layer_bwd(F, W, None, 1e-5, 0, gO, need_gF=False)
+    assert gF_none is None and torch.equal(gW_full, gW_only)
+    layer = CGBN_cuda(4, [1] * 5, [4] * 5, batchnorm=False, device=dev())
+    with torch.no_grad():
+        layer.bnWMM.W.copy_(W)
+    O = layer(F, straight_output=True)          # F does not require grad
+    (O * gO).sum().backward()
+    assert torch.equal(layer.bnWMM.W.grad, gW_full)
