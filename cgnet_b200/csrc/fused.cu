@@ -322,11 +322,15 @@ template <int T, int I, int TO>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
-                int band_floats) {
+                int band_floats, int slices, int64_t slice_stride) {
     extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the current triple's CG band
-    for (int task = blockIdx.x * kGwWarps + warp; task < n_tasks; task += gridDim.x * kGwWarps) {
+    // unit = (task, slice): slice s sums the sample groups s, s + slices, ...; with more than one slice the partial
+    // sums go to gW + s * slice_stride and gw_reduce_kernel adds them in slice order
+    for (int unit = blockIdx.x * kGwWarps + warp; unit < n_tasks * slices; unit += gridDim.x * kGwWarps) {
+        const int task = unit / slices, slice = unit - task * slices;
+        float2* __restrict__ out = gW + (int64_t)slice * slice_stride;
         const GwTask tk = tasks[task];
         const TripleRec tr = P.triples[tk.triple];
         const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
@@ -355,7 +359,7 @@ fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const 
 #pragma unroll
                 for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
 
-        for (int g = 0; g < G; ++g) {
+        for (int g = slice; g < G; g += slices) {
             const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
             const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
             const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
@@ -411,9 +415,23 @@ fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const 
                     if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
                         const int ch = t1 * tr.tau2 + t2;
                         const float s = inv[tr.kglob + ch];
-                        gW[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
+                        out[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
                     }
                 }
+    }
+}
+
+// gW[i] = sum over the slices, in slice order
+__global__ void __launch_bounds__(256)
+gw_reduce_kernel(const float2* __restrict__ partial, int slices, int64_t slice_stride, float2* __restrict__ gW, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float2 s = partial[i];
+        for (int k = 1; k < slices; ++k) {
+            const float2 v = partial[(int64_t)k * slice_stride + i];
+            s.x += v.x;
+            s.y += v.y;
+        }
+        gW[i] = s;
     }
 }
 
@@ -651,8 +669,22 @@ struct Workspace {
     int* counters;  // one row counter per sample group
     float2* gf_part; // partial input gradients, [parts][B][n_F], when the input-gradient blocks are split
     int gf_level;
+    float2* gw_part; // partial weight gradients, [slices][w_len], when the sample groups are split over warps
+    int gw_slices;
     int64_t bytes;
 };
+
+// Slices of the sample groups in the weight-gradient kernel: a task walks all groups of its slice in sequence, so with
+// few tasks the longest one sets the kernel's duration; slicing shortens it and multiplies the number of warps.
+int gw_slices(const cgb200_plan* p, int64_t G) {
+    if (p->d.depthwise) return 1;
+    const int64_t n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
+    if (n_tasks == 0) return 1;
+    int64_t s = (24 * (int64_t)p->num_sms + n_tasks - 1) / n_tasks;
+    s = std::min<int64_t>(s, G);
+    while (s > 1 && s * p->d.w_len * (int64_t)sizeof(float2) > (256ll << 20)) --s;
+    return (int)std::max<int64_t>(s, 1);
+}
 
 // Splitting level of the input-gradient kernel: the coarsest one that gives every SM about two blocks.
 int gf_level(const cgb200_plan* p, int64_t G) {
@@ -680,6 +712,9 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
     w.gf_part = (float2*)(c + off);
     if (p->gf2_max_parts[w.gf_level] > 1)
         off += align256((int64_t)p->gf2_max_parts[w.gf_level] * B * std::max<int64_t>(p->d.n_F, 1) * (int64_t)sizeof(float2));
+    w.gw_slices = gw_slices(p, G);
+    w.gw_part = (float2*)(c + off);
+    if (w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
     w.bytes = off;
     return w;
 }
@@ -866,9 +901,18 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             CGB_DISPATCH_TILE(T, false, {
                 auto kern = fused_gw_kernel<TT, GwShape<TT>::I, GwShape<TT>::TO>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                const int grid = blocks;
-                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
+                const int slices = ws.gw_slices;
+                const int grid = (int)(((int64_t)n_tasks * slices + kGwWarps - 1) / kGwWarps);
+                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv,
+                                                           slices > 1 ? ws.gw_part : (float2*)gW, G, band_floats, slices, p->d.w_len);
             });
+            if (ws.gw_slices > 1) {
+                launch_end(K_GW, st);
+                CGB_CUDA(cudaGetLastError());
+                launch_begin(K_GW_REDUCE, st);
+                const int gx = (int)std::min<int64_t>((p->d.w_len + 255) / 256, 4 * p->num_sms);
+                gw_reduce_kernel<<<gx, 256, 0, st>>>(ws.gw_part, ws.gw_slices, p->d.w_len, (float2*)gW, p->d.w_len);
+            }
         }
         launch_end(K_GW, st);
         CGB_CUDA(cudaGetLastError());
