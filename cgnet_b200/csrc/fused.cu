@@ -499,6 +499,8 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
 // in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kGfWarpsMax = 16;
+constexpr int kGfRows = 1;   // rows of the owned fragment a warp gathers together in phase 2 (measured: 1 beats 3, the
+                             // phase is bound by its longest warp, not by shared-memory traffic)
 
 template <int T, bool DW>
 __global__ void __launch_bounds__(kGfWarpsMax * kWarp)
@@ -577,51 +579,62 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
                 for (int k = 0; k < NH; ++k) h[k * 32] = gt[k];
             }
             __syncthreads();
-            for (int r = warp; r < nt; r += nwarps) {
-                const int mt = r - lt;   // m of the owned element
-                float2 x[T];
+            // rows of the owned fragment in groups of kGfRows: the rows of a group need the same H[m] tiles, which
+            // are loaded into registers once per m and used for every row of the group (shared-memory traffic / kGfRows)
+            const int lo_ = first ? en.l2 : en.l1;
+            for (int r0 = warp * kGfRows; r0 < nt; r0 += nwarps * kGfRows) {
+                float2 x[kGfRows][T];
 #pragma unroll
-                for (int a = 0; a < T; ++a) x[a] = make_float2(0.f, 0.f);
-                // u = m of the other operand's element; m = mt + u must lie in [-l, l] and inside the chunk
-                const int lo_ = first ? en.l2 : en.l1;
-                const int ulo = max(-lo_, max(-l, mc0 - l) - mt), uhi = min(lo_, min(l, mc0 + mcn - 1 - l) - mt);
-                if (ulo <= uhi) {
-                    // band entry [m + l][m2 + l2]: m2 = u (first) or mt (second)
-                    const float* pc = band + (mt + ulo + l) * n2 + (first ? ulo + en.l2 : mt + en.l2);
-                    const int cstep = first ? n2 + 1 : n2;
-                    const float2* pf = fo + (size_t)(ulo + lo_) * T * 32 + lane;
-                    const float2* ph = H + (size_t)(mt + ulo + l - mc0) * NH * 32 + lane;
-                    for (int k = uhi - ulo; k >= 0; --k) {
-                        const float cg = *pc;
-                        if constexpr (DW) {
+                for (int rr = 0; rr < kGfRows; ++rr)
 #pragma unroll
-                            for (int a = 0; a < T; ++a) {
-                                const float2 f = pf[a * 32];
-                                cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), ph[a * 32]);
-                            }
-                        } else {
+                    for (int a = 0; a < T; ++a) x[rr][a] = make_float2(0.f, 0.f);
+                const int mt0 = r0 - lt;   // m of the group's first row; row rr has m_t = mt0 + rr
+                const int rows = min(kGfRows, nt - r0);
+                // m = m_t + u with u = m of the other operand's element, |u| <= lo_, m inside [-l, l] and the chunk
+                const int mlo = max(max(-l, mc0 - l), mt0 - lo_), mhi = min(min(l, mc0 + mcn - 1 - l), mt0 + rows - 1 + lo_);
+                for (int m = mlo; m <= mhi; ++m) {
+                    float2 h[NH];
+                    const float2* ph = H + (size_t)(m + l - mc0) * NH * 32 + lane;
 #pragma unroll
-                            for (int c = 0; c < T; ++c) {
-                                float2 f = pf[c * 32];
-                                f.x *= cg;
-                                f.y *= cg;
+                    for (int k = 0; k < NH; ++k) h[k] = ph[k * 32];
 #pragma unroll
-                                for (int a = 0; a < T; ++a) cfma_conj(x[a], f, ph[(first ? a * T + c : c * T + a) * 32]);
+                    for (int rr = 0; rr < kGfRows; ++rr) {
+                        const int u = m - (mt0 + rr);
+                        if (rr < rows && u >= -lo_ && u <= lo_) {   // warp-uniform
+                            // band entry [m + l][m2 + l2]: m2 = u (first) or m_t (second)
+                            const float cg = band[(m + l) * n2 + (first ? u : mt0 + rr) + en.l2];
+                            const float2* pf = fo + (size_t)(u + lo_) * T * 32 + lane;
+                            if constexpr (DW) {
+#pragma unroll
+                                for (int a = 0; a < T; ++a) {
+                                    const float2 f = pf[a * 32];
+                                    cfma_conj(x[rr][a], make_float2(f.x * cg, f.y * cg), h[a]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < T; ++c) {
+                                    float2 f = pf[c * 32];
+                                    f.x *= cg;
+                                    f.y *= cg;
+#pragma unroll
+                                    for (int a = 0; a < T; ++a) cfma_conj(x[rr][a], f, first ? h[a * T + c] : h[c * T + a]);
+                                }
                             }
                         }
-                        pc += cstep;
-                        pf += T * 32;
-                        ph += NH * 32;
-                    }
-#pragma unroll
-                    for (int a = 0; a < T; ++a) {
-                        float2* pa = acc + ((size_t)a * nt + r) * 32 + lane;
-                        float2 cur = *pa;
-                        cur.x += x[a].x;
-                        cur.y += x[a].y;
-                        *pa = cur;
                     }
                 }
+#pragma unroll
+                for (int rr = 0; rr < kGfRows; ++rr)
+                    if (rr < rows) {
+#pragma unroll
+                        for (int a = 0; a < T; ++a) {
+                            float2* pa = acc + ((size_t)a * nt + r0 + rr) * 32 + lane;
+                            float2 cur = *pa;
+                            cur.x += x[rr][a].x;
+                            cur.y += x[rr][a].y;
+                            *pa = cur;
+                        }
+                    }
             }
         }
         en = nxt;
@@ -932,7 +945,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             set_error("lmax or tau_out too large for the fused input-gradient kernel");
             return CGB200_ERR_UNSUPPORTED;
         }
-        const int Mc = (int)std::min<size_t>(p->max_n, (227 * 1024 - fixed) / per_m);
+        const size_t budget = 227 * 1024;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
+        const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
         const size_t smem = fixed + (size_t)Mc * per_m;
         const int64_t part_stride = split ? (int64_t)B * p->d.n_F : 0;
         launch_begin(K_GF, st);
