@@ -105,9 +105,10 @@ class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
 
     def __init__(self, index):
-        self.rows = []
+        self.rows = []          # (host time when the line arrived, fields)
         self.proc = None
         self.index = index
+        self.window = None      # (t0, t1) of the timed region on the host clock
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -115,26 +116,30 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        rows = [r for t, r in self.rows if self.window is None or self.window[0] <= t <= self.window[1] + 0.06]
+        scope = "timed region"
+        if not rows:   # the timed region was shorter than the sampling period: use the samples of the whole loaded run
+            rows, scope = [r for _, r in self.rows], "warm-up + timed region"
+        sm = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 4 + i and r[4 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 4 + i and r[4 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "scope": scope}
 
 
 def run_ours(args, wl_name, wl):
@@ -206,17 +211,19 @@ def run_ours(args, wl_name, wl):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for i in range(max(args.warmup, 3)):
         step(*dev_batches[i % n_batches])
     barrier()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    t_begin = time.time()
     lib.cgb200_launch_count(1)
     total_ms = timed(args.steps, e2e=False)
     launches = int(lib.cgb200_launch_count(0))
     e2e_ms = timed(args.steps, e2e=True)
+    sampler.window = (t_begin, time.time())
     clocks = sampler.stop() if rank == 0 else None
 
     # per-kernel device time, separate instrumented pass over the same steps (events around every launch)
@@ -386,9 +393,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    # stdout carries exactly one JSON line: anything a library prints there meanwhile (NCCL's version banner, ...) is
+    # sent to stderr
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     out = run_reference(args, args.workload, wl) if args.impl == "reference" else run_ours(args, args.workload, wl)
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     if out is not None:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":
