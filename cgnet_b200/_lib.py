@@ -24,6 +24,7 @@ SIGNATURES = {
     "cgb200_plan_destroy": (None, [vp]),
     "cgb200_plan_query": (ctypes.c_int, [vp, ctypes.c_int, c_i64p]),
     "cgb200_plan_t_ff": (ctypes.c_int, [vp, c_i32p]),
+    "cgb200_plan_status": (ctypes.c_int, [vp, c_i32p]),
     "cgb200_plan_cg_table": (vp, [vp]),
     "cgb200_cg_product_fwd": (ctypes.c_int, [vp, vp, vp, ctypes.c_int64, vp]),
     "cgb200_cg_product_bwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, vp]),

@@ -129,7 +129,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // Kernel identifiers for launch accounting and the optional per-kernel CUDA-event timing (cgb200_timing_*).
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
-    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_COUNT
+    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.
@@ -169,6 +169,15 @@ void launch_end(int kid, cudaStream_t st);
         case 13: { constexpr int TT = 6; constexpr bool DD = true; (void)TT; (void)DD; __VA_ARGS__; break; }   \
         default: cgb200::set_error("internal: tile edge out of range"); return CGB200_ERR_UNSUPPORTED;  \
     }
+
+// tensor-core forward (fused_tc.cu)
+struct cgb200_plan;
+namespace cgb200 {
+bool tc_wanted(const cgb200_plan* p);
+int64_t tc_pack_floats(const cgb200_plan* p);
+int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
+                  cudaStream_t st);
+}  // namespace cgb200
 
 // The opaque handle of the C ABI.
 struct cgb200_plan {
@@ -211,6 +220,16 @@ struct cgb200_plan {
     std::vector<int> gf2_parts[kGfLevels];            // [lmax+1] parts per fragment
     const int* d_gf2_parts[kGfLevels] = {nullptr};
     int gf2_max_parts[kGfLevels] = {0};
+    // tensor-core forward (tile edge 2 or 4, full product): per degree the padded GEMM width N' = 2*tau_out rounded
+    // up to 16, the offset (in floats) of the degree's packed weights, and the list of row tiles (l, first m index)
+    bool tc_ok = false;
+    std::vector<int> tc_npad;
+    std::vector<int64_t> tc_pack_off;   // [lmax+2]
+    std::vector<int> tc_tiles;          // (l, m0) pairs, longest K first
+    const int* d_tc_npad = nullptr;
+    const int64_t* d_tc_pack_off = nullptr;
+    const int* d_tc_tiles = nullptr;
+    int* d_status = nullptr;          // set to 1 by a kernel whose bounded wait ran out (cgb200_plan_status)
     std::vector<int> fwd_rows;        // (l, m+l) rows of the output, most expensive first (dynamic scheduling order)
     const int* d_fwd_rows = nullptr;
     int max_tau_out = 0;

@@ -682,6 +682,7 @@ struct Workspace {
     int* counters;  // one row counter per sample group
     float2* gf_part; // partial input gradients, [parts][B][n_F], when the input-gradient blocks are split
     int gf_level;
+    float* tc_pack;  // packed TF32 weights of the tensor-core forward
     float2* gw_part; // partial weight gradients, [slices][w_len], when the sample groups are split over warps
     int gw_slices;
     int64_t bytes;
@@ -725,6 +726,8 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
     w.gf_part = (float2*)(c + off);
     if (p->gf2_max_parts[w.gf_level] > 1)
         off += align256((int64_t)p->gf2_max_parts[w.gf_level] * B * std::max<int64_t>(p->d.n_F, 1) * (int64_t)sizeof(float2));
+    w.tc_pack = (float*)(c + off);
+    if (tc_wanted(p)) off += align256(tc_pack_floats(p) * (int64_t)sizeof(float));
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
     if (w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
@@ -829,6 +832,7 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     }
     const int n_rows = (int)p->fwd_rows.size() / 2;
     if (n_rows == 0) return CGB200_OK;
+    if (tc_wanted(p)) return launch_fwd_tc(p, ws.SF, (const float2*)W, ws.inv, ws.tc_pack, (float2*)O, (int)B, G, st);
     // persistent shared-memory variant when one group's slab (plus reduction buffer and staging areas) fits in an SM
     const int NVh = p->d.depthwise ? T : T * T;
     // output channels per pass: the smallest instantiated width that covers the widest degree (at most kFwdTo)

@@ -1,0 +1,363 @@
+// Tensor-core variant of the fused forward: CG product generated on the CUDA cores straight into shared memory as the
+// A operand of a tcgen05 (5th-generation tensor core) GEMM whose accumulator lives in tensor memory; the mixing weights,
+// pre-scaled by 1/std, split into TF32 high/low parts and packed in the MMA's shared-memory order, arrive by bulk
+// asynchronous copy (the TMA engine's 1-D mode).  The quadratic mid activation FF exists only as one 128 x 2T^2 tile
+// per pipeline stage.
+//
+//   O_l[(m, b), (to, re|im)] = sum_k  FF_l[(m, b), (k, re|im)] * Wr_l[(k, re|im), (to, re|im)]
+//
+// The complex product is run as a real GEMM of doubled dimensions: a row of A holds (re, im) of every mid channel, the
+// columns of B hold, for output (to, re): (Wr, -Wi) and for (to, im): (Wi, Wr).  3xTF32: A = Ah + Al, B = Bh + Bl with
+// Ah, Bh rounded to TF32; D += Ah*Bh + Al*Bh + Ah*Bl, accumulated in fp32 by the tensor core (the dropped Al*Bl term
+// is ~2^-22 relative).
+//
+// Block = one row tile: degree l, four consecutive m, one group of 32 samples (row r = 32*(m - m0) + sample, the same
+// one-sample-per-lane scheme as the other fused kernels, so the generator is gen_slab unchanged).  Warps:
+//   generator groups 0..kTcStages-1, four warps each: group s produces the cells k = s, s + kTcStages, ... of the
+//     degree into pipeline stage s (A tile written with st.shared, then fence.proxy.async + mbarrier arrive); its first
+//     lane also starts the bulk copy of the cell's packed weights into the stage;
+//   one MMA warp: a single lane waits for each stage, issues the 3 x (2T^2/8) tcgen05.mma of the cell and commits them
+//     to the stage's "empty" barrier; after the last cell it commits to the "done" barrier;
+//   epilogue: group 0 reads the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 = its own m) and
+//     writes O.
+// Every wait is bounded: a wait that runs out sets a flag in shared memory and a status word in global memory, all
+// roles then skip to the end, tensor memory is released and the kernel returns.
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace cgb200 {
+
+constexpr int kTcStages = 3;
+constexpr int kTcGenWarps = 4 * kTcStages;
+constexpr int kTcThreads = 32 * (kTcGenWarps + 1);
+constexpr uint32_t kTcSpinLimit = 4000000;   // polls of mbarrier.try_wait before a wait gives up
+
+// ---- thin PTX wrappers --------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out or another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kTcSpinLimit; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((spin & 1023) == 1023 && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier (addresses and size multiples of 16)
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], TF32 inputs, fp32 accumulate; one thread issues for the whole block
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` = byte distance between
+// the two core matrices an MMA reads along K, `sbo` = byte distance between consecutive 8-row groups.  Field layout:
+// [0,14) start address >> 4, [16,30) lbo >> 4, [32,46) sbo >> 4, [46,48) version = 1 on this architecture,
+// [61,64) swizzle mode = 0.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+           ((uint64_t)1 << 46);
+}
+// Instruction descriptor of kind::tf32: fp32 accumulator ([4,6) = 1), A and B formats TF32 ([7,10) = [10,13) = 2), both
+// K-major ([15], [16] = 0), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ inline uint32_t tc_idesc(int M, int N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Weight packing.  One block per cell: the T*T mid channels of the cell against all output channels of its degree,
+// scaled by 1/max(eps, std), expanded to the real form, split into TF32 high and low parts and stored in the order
+// the MMA descriptor expects (element (n', kk) at (n'/8)*(Kc/4)*32 + (kk/4)*32 + (n'%8)*4 + kk%4 floats), high part
+// first.  One contiguous block per cell, so a stage's weights are a single bulk copy.
+// ---------------------------------------------------------------------------------------------------------------
+template <int T>
+__global__ void __launch_bounds__(256)
+tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restrict__ pack_off, const float2* __restrict__ W,
+               const float* __restrict__ inv, float* __restrict__ pack) {
+    constexpr int Kc = 2 * T * T;
+    const int c = blockIdx.x;
+    const CellInfo ci = P.cell_info[c];
+    const int l = P.triples[P.cells[c].triple].l;
+    const int N = npad[l];
+    if (N == 0) return;
+    const int to_n = P.tO[l], tff = P.tFF[l];
+    float* hi = pack + pack_off[l] + (int64_t)(c - P.cell_begin[l]) * 2 * N * Kc;
+    float* lo = hi + N * Kc;
+    const float2* Wl = W + P.cumW[l];
+    for (int e = threadIdx.x; e < N * Kc; e += blockDim.x) {
+        const int np = e / Kc, kk = e - np * Kc;
+        const int to = np >> 1, co = np & 1, idx = kk >> 1, cin = kk & 1;
+        const int i = idx / T, j = idx - i * T;
+        float v = 0.f;
+        if (to < to_n && i < ci.v1 && j < ci.v2) {
+            const int ch = i * ci.tau2 + j;
+            const float2 w = __ldg(Wl + (int64_t)to * tff + ci.wch0 + ch);
+            const float sc = __ldg(inv + ci.kch0 + ch);
+            v = (co == 0 ? (cin == 0 ? w.x : -w.y) : (cin == 0 ? w.y : w.x)) * sc;
+        }
+        const float h = to_tf32(v);
+        const int off = (np >> 3) * (Kc / 4) * 32 + (kk >> 2) * 32 + (np & 7) * 4 + (kk & 3);
+        hi[off] = h;
+        lo[off] = v - h;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The fused forward on the tensor cores.  grid = (row tiles, sample groups), kTcThreads threads.
+// Dynamic shared memory: kTcStages x { A high [128 x Kc], A low [128 x Kc], B high+low [2 x n_max x Kc] } floats,
+// then one CG band row per generator warp.
+// ---------------------------------------------------------------------------------------------------------------
+template <int T>
+__global__ void __launch_bounds__(kTcThreads)
+fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
+                    const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O, int B, int n_max,
+                    int max_n, int* __restrict__ status) {
+    constexpr int Kc = 2 * T * T;            // real K extent of one cell
+    constexpr int NV = T * T;
+    constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kTcStages], empty_bar[kTcStages], done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed_flag;
+
+    const int l = tiles[2 * blockIdx.x], m0 = tiles[2 * blockIdx.x + 1];
+    const int g = blockIdx.y;
+    const int n = 2 * l + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
+    const int N = npad[l];
+    const int to_n = P.tO[l];
+    const uint32_t tmem_cols = N <= 32 ? 32u : N <= 64 ? 64u : 128u;
+    const size_t stage_floats = (size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc;
+    float* stages = reinterpret_cast<float*>(smem_raw);
+    float* cbuf = stages + kTcStages * stage_floats + (size_t)warp * max_n;
+    volatile int* failed = &failed_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&full_bar[s], 128);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        failed_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp < kTcGenWarps) {
+        // ---------------- generators ----------------
+        const int s = warp >> 2, wq = warp & 3;
+        const int mi = m0 + wq;
+        const bool live_m = mi < n;
+        const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
+        float* a_hi = stages + s * stage_floats;
+        float* a_lo = a_hi + 128 * Kc;
+        float* b_st = a_lo + 128 * Kc;
+        const int r = wq * 32 + lane;
+        float4* row_hi = reinterpret_cast<float4*>(a_hi) + (size_t)(r >> 3) * (Kc / 4) * 8 + (r & 7);
+        float4* row_lo = reinterpret_cast<float4*>(a_lo) + (size_t)(r >> 3) * (Kc / 4) * 8 + (r & 7);
+        const uint32_t b_bytes = (uint32_t)(2 * N * Kc * sizeof(float));
+        bool ok = true;
+        for (int k = s, u = 0; k < ncell && ok; k += kTcStages, ++u) {
+            if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
+            if (!ok) break;
+            if (wq == 0 && lane == 0) {
+                mbar_expect_tx(&full_bar[s], b_bytes);
+                bulk_g2s(b_st, pack + pack_off[l] + (int64_t)k * 2 * N * Kc, b_bytes, &full_bar[s]);
+            }
+            float2 v[NV];
+            if (live_m) {
+                const CellInfo ci = P.cell_info[c_begin + k];
+                const int n2 = 2 * ci.l2 + 1;
+                __syncwarp();
+                for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
+                __syncwarp();
+                gen_slab<T, false>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = make_float2(0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 0; q < Kc / 4; ++q) {
+                const float2 x0 = v[2 * q], x1 = v[2 * q + 1];
+                float4 h, w;
+                h.x = to_tf32(x0.x); h.y = to_tf32(x0.y); h.z = to_tf32(x1.x); h.w = to_tf32(x1.y);
+                w.x = x0.x - h.x; w.y = x0.y - h.y; w.z = x1.x - h.z; w.w = x1.y - h.w;
+                row_hi[q * 8] = h;
+                row_lo[q * 8] = w;
+            }
+            fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
+            mbar_arrive(&full_bar[s]);
+        }
+        // ---------------- epilogue (first generator group) ----------------
+        if (s == 0) {
+            const int b = g * 32 + lane;
+            float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
+            if (ncell > 0) ok = ok && mbar_wait(&done_bar, 0u, failed);
+            tc_fence_after();
+            for (int col0 = 0; col0 < N; col0 += 16) {
+                uint32_t rr[16];
+                if (ncell > 0 && ok) {
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) rr[j] = 0u;
+                }
+                if (live_m && b < B) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int to = (col0 >> 1) + j;
+                        if (to < to_n) out[(int64_t)to * n] = make_float2(__uint_as_float(rr[2 * j]), __uint_as_float(rr[2 * j + 1]));
+                    }
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = tc_idesc(128, N);
+        bool ok = true;
+        for (int k = 0; k < ncell && ok; ++k) {
+            const int s = k % kTcStages, u = k / kTcStages;
+            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(stages + s * stage_floats);
+            const uint32_t a_lo = a_hi + 128 * Kc * 4;
+            const uint32_t b_hi = a_lo + 128 * Kc * 4;
+            const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
+#pragma unroll
+            for (int ks = 0; ks < Kc / 8; ++ks) {
+                const uint64_t dah = smem_desc(a_hi + ks * 256, 128, kSbo), dal = smem_desc(a_lo + ks * 256, 128, kSbo);
+                const uint64_t dbh = smem_desc(b_hi + ks * 256, 128, kSbo), dbl = smem_desc(b_lo + ks * 256, 128, kSbo);
+                tc_mma_tf32(tmem_base, dah, dbh, idesc, (k > 0 || ks > 0) ? 1u : 0u);
+                tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
+                tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+            }
+            tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+        }
+        if (ok && ncell > 0) tc_commit(&done_bar);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tmem_cols);
+    if (threadIdx.x == 0 && failed_flag) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------
+// Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
+// when the mixing dominates, i.e. from about 8 output channels; CGB200_TC=0 / 1 overrides the default.
+bool tc_wanted(const cgb200_plan* p) {
+    if (!p->tc_ok) return false;
+    if (const char* env = getenv("CGB200_TC")) return env[0] == '1';
+    return p->max_tau_out >= 8;
+}
+
+int64_t tc_pack_floats(const cgb200_plan* p) { return p->tc_ok ? p->tc_pack_off.back() : 0; }
+
+template <int T>
+static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B,
+                     int G, cudaStream_t st) {
+    constexpr int Kc = 2 * T * T;
+    int n_max = 16;
+    for (int v : p->tc_npad) n_max = std::max(n_max, v);
+    const int n_tiles = (int)p->tc_tiles.size() / 2;
+    if (n_tiles == 0) return CGB200_OK;
+    launch_begin(K_TC_PACK, st);
+    if (p->d.n_cells > 0)
+        tc_pack_kernel<T><<<p->d.n_cells, 256, 0, st>>>(p->d, p->d_tc_npad, p->d_tc_pack_off, W, inv, pack);
+    launch_end(K_TC_PACK, st);
+    CGB_CUDA(cudaGetLastError());
+    const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
+    const size_t smem = kTcStages * stage_bytes + (size_t)(kTcGenWarps + 1) * p->max_n * sizeof(float);
+    if (smem > 227 * 1024) {
+        set_error("tensor-core forward: pipeline stages do not fit in shared memory");
+        return CGB200_ERR_UNSUPPORTED;
+    }
+    auto kern = fused_fwd_tc_kernel<T>;
+    CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_begin(K_FWD_TC, st);
+    kern<<<dim3(n_tiles, G), kTcThreads, smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B, n_max,
+                                                     p->max_n, p->d_status);
+    launch_end(K_FWD_TC, st);
+    CGB_CUDA(cudaGetLastError());
+    return CGB200_OK;
+}
+
+int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
+                  cudaStream_t st) {
+    if (p->d.tile == 4) return launch_tc<4>(p, SF, W, inv, pack, O, B, G, st);
+    if (p->d.tile == 2) return launch_tc<2>(p, SF, W, inv, pack, O, B, G, st);
+    set_error("internal: tensor-core forward asked for an unsupported tile edge");
+    return CGB200_ERR_UNSUPPORTED;
+}
+
+}  // namespace cgb200

@@ -30,7 +30,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_product_bwd", "fn_stats", "wmm_fwd",
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
-                                            "fused_grad_w_reduce"};
+                                            "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;
@@ -408,6 +408,30 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         }
     }
 
+    // tensor-core forward tables
+    p->tc_ok = !dw && has_out && (T == 2 || T == 4) && p->max_tau_out >= 4 && p->max_tau_out <= 64 && 2 * lmax + 1 <= 128;
+    if (p->tc_ok) {
+        const int Kc = 2 * T * T;
+        p->tc_npad.assign(L1, 0);
+        p->tc_pack_off.assign(L1 + 1, 0);
+        std::vector<std::pair<int, int>> order;   // (cells, l)
+        for (int l = 0; l < L1; ++l) {
+            p->tc_npad[l] = p->tO[l] > 0 ? ((2 * p->tO[l] + 15) / 16) * 16 : 0;
+            const int64_t ncell = p->cell_begin[l + 1] - p->cell_begin[l];
+            p->tc_pack_off[l + 1] = p->tc_pack_off[l] + ncell * 2 * p->tc_npad[l] * Kc;
+            if (p->tO[l] > 0) order.push_back({(int)ncell, l});
+        }
+        std::stable_sort(order.begin(), order.end(), [](const std::pair<int, int>& a, const std::pair<int, int>& b) { return a.first > b.first; });
+        for (auto& o : order)
+            for (int m0 = 0; m0 < 2 * o.second + 1; m0 += 4) {
+                p->tc_tiles.push_back(o.second);
+                p->tc_tiles.push_back(m0);
+            }
+        if ((rc = upload(p, p->tc_npad, &p->d_tc_npad))) return rc;
+        if ((rc = upload(p, p->tc_pack_off, &p->d_tc_pack_off))) return rc;
+        if ((rc = upload(p, p->tc_tiles, &p->d_tc_tiles))) return rc;
+    }
+
     // which triples use fragment l as first / second operand (for the gather-style input gradient)
     std::vector<int> r1b(L1 + 1, 0), r2b(L1 + 1, 0), r1l, r2l;
     for (int l = 0; l < L1; ++l) {
@@ -585,6 +609,10 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         }
     if ((rc = upload(p, p->gf_blocks, &p->d_gf_blocks))) return rc;
 
+    CGB_CUDA(cudaMalloc(&p->d_status, sizeof(int)));
+    p->allocations.push_back(p->d_status);
+    CGB_CUDA(cudaMemset(p->d_status, 0, sizeof(int)));
+
     float* cg = nullptr;
     CGB_CUDA(cudaMalloc(&cg, std::max<int64_t>(cgoff, 1) * sizeof(float)));
     p->allocations.push_back(cg);
@@ -616,6 +644,15 @@ int cgb200_plan_query(const cgb200_plan* p, int what, int64_t* v) {
         case CGB200_Q_TILE: *v = p->d.tile; break;
         default: set_error("unknown query"); return CGB200_ERR_ARGUMENT;
     }
+    return CGB200_OK;
+}
+
+int cgb200_plan_status(const cgb200_plan* p, int32_t* out) {
+    CGB_REQUIRE(p != nullptr && out != nullptr, "null argument");
+    int v = 0;
+    CGB_CUDA(cudaMemcpy(&v, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) CGB_CUDA(cudaMemset(p->d_status, 0, sizeof(int)));
+    *out = v;
     return CGB200_OK;
 }
 

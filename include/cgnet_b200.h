@@ -80,6 +80,12 @@ void cgb200_plan_destroy(cgb200_plan* plan);
 #define CGB200_Q_N_TRIPLES  6
 #define CGB200_Q_TILE       7   /* channel-tile edge chosen for the register-tiled kernels    */
 int cgb200_plan_query(const cgb200_plan* plan, int what, int64_t* value);
+/*
+ * Device-side status of the plan's kernels (no reference counterpart).  The tensor-core forward waits on hardware
+ * barriers with an iteration limit; a wait that runs out makes the kernel return early and sets this word.  The call
+ * synchronises the device, returns the word in *status (0 = fine) and clears it.
+ */
+int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 /* Per-degree mid-channel counts t_FF[0..lmax] (CGNet/CG_layers.py:253-262), for cross-checking the host's own. */
 int cgb200_plan_t_ff(const cgb200_plan* plan, int32_t* t_ff_host);
 /* Device address of the plan's CG table (float[CGB200_Q_CG_LEN]); valid until the plan is destroyed. */
