@@ -33,11 +33,21 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
+METRIC_TRAIN = "CG-net samples/sec (training step, forward+backward)"
+METRIC_INFER = "fused CG layer samples/sec (inference forward)"
+
 WORKLOADS = {
     "cgnet5_lmax10": dict(lmax=10, tau_in=1, tau=5, layers=5, batch=100, hidden=256, classes=10,
                           describe="5-layer CGNet lmax=10 tau=5 batch=100 fwd+bwd (BASELINE configs[1])"),
     "layer_lmax5": dict(lmax=5, tau_in=8, tau=8, layers=1, batch=32, hidden=256, classes=10,
                         describe="single CG layer lmax=5 tau=8 batch=32 fwd+bwd (BASELINE configs[0] shape)"),
+    # single fused layer, inference forward only (BASELINE configs[4], the sweep's points that fit a quick run)
+    "fused_layer_lmax10_tau16": dict(kind="layer_infer", lmax=10, tau_in=16, tau=16, layers=1, batch=256, classes=10, hidden=0,
+                                     describe="one fused CG layer lmax=10 tau=16 batch=256, inference forward (BASELINE configs[4])"),
+    "fused_layer_lmax10_tau32": dict(kind="layer_infer", lmax=10, tau_in=32, tau=32, layers=1, batch=128, classes=10, hidden=0,
+                                     describe="one fused CG layer lmax=10 tau=32 batch=128, inference forward (BASELINE configs[4])"),
+    "fused_layer_lmax10_tau64": dict(kind="layer_infer", lmax=10, tau_in=64, tau=64, layers=1, batch=64, classes=10, hidden=0,
+                                     describe="one fused CG layer lmax=10 tau=64 batch=64, inference forward (BASELINE configs[4])"),
 }
 
 
@@ -160,8 +170,15 @@ def run_ours(args, wl_name, wl):
 
     torch.manual_seed(1234)
     np.random.seed(1234)
-    net = Net(wl, dev)
-    net.train()
+    infer = wl.get("kind") == "layer_infer"
+    if infer:
+        from cgnet_b200 import CGBN_cuda
+        L1 = wl["lmax"] + 1
+        net = CGBN_cuda(wl["lmax"], [wl["tau_in"]] * L1, [wl["tau"]] * L1, batchnorm=True, device=dev)
+        net.eval()
+    else:
+        net = Net(wl, dev)
+        net.train()
     if world > 1:
         broadcast_parameters(net)
     params = [p for p in net.parameters() if p.requires_grad]
@@ -174,6 +191,9 @@ def run_ours(args, wl_name, wl):
     loss_fn = torch.nn.NLLLoss()
 
     def step(x, y):
+        if infer:
+            with torch.no_grad():
+                return net(x, straight_output=True)[:, :8].sum()   # a small read-back value for the end-to-end pass
         for p in params:
             p.grad = None
         loss = loss_fn(net(x), y)
@@ -264,7 +284,7 @@ def run_ours(args, wl_name, wl):
     roof = None
     if top is not None:
         # every fused kernel launches once per layer per step; average the per-layer work over the layers
-        if top == "fused_fwd":
+        if top in ("fused_fwd", "fused_fwd_tensor"):
             flops = [w["cg_flops"] + w["mix_flops"] for w in works]
         elif top == "fused_stats":
             flops = [w["cg_flops"] for w in works]
@@ -287,17 +307,19 @@ def run_ours(args, wl_name, wl):
                 "hbm_frac_of_algorithmic_bytes": round(sum(byts) / len(works) / dur_s / 1e9 / hbm_peak, 5) if dur_s > 0 else None,
                 "cuda_core_fp32": {"achieved": round(achieved_tf, 3), "peak": round(simt_peak_tf, 1), "unit": "TFLOP/s",
                                    "frac": round(achieved_tf / simt_peak_tf, 4),
-                                   "note": "this kernel runs on the fp32 CUDA cores; peak = 148 SMs x 128 lanes x 2 x sampled SM clock"}}
+                                   "note": "CG-product generation runs on the fp32 CUDA cores in every kernel (the tensor-core forward "
+                                           "moves only the mixing to tcgen05); peak = 148 SMs x 128 lanes x 2 x sampled SM clock"}}
 
     cpu = None if args.no_cpu_baseline else cpu_baseline(wl, sample=4, repeats=1)
     ms_step = total_ms / args.steps
     out = {
-        "metric": "CG-net samples/sec (training step, forward+backward)", "value": round(world * B / (ms_step / 1e3), 1),
+        "metric": METRIC_INFER if infer else METRIC_TRAIN, "value": round(world * B / (ms_step / 1e3), 1),
         "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": wl_name, "describe": wl["describe"], "per_gpu_batch": B, "global_batch": B * world,
                    "l2": "flushed between timed steps (256 MB write, outside the timed intervals)",
-                   "parallelism": f"dp{world}", "fragment_norm": "training mode (statistics updated every step)"},
+                   "parallelism": f"dp{world}",
+                   "fragment_norm": "inference (stored statistics)" if infer else "training mode (statistics updated every step)"},
         "e2e": {"value": round(world * B / (e2e_ms / args.steps / 1e3), 1), "unit": "samples/s",
                 "h2d_bytes_per_step": int(pinned[0][0].numel() * 4 + pinned[0][1].numel() * 8), "d2h_bytes_per_step": 4,
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
@@ -320,6 +342,10 @@ def cpu_step(wl, x, y, weights, stds_list):
     taus = layer_taus(wl)
     llls, _ = o.encode_sorted(o.default_ltuples(lmax))
     B = x.shape[0]
+    if wl.get("kind") == "layer_infer":
+        with torch.no_grad():
+            out = o.twin_forward(o.split_fragments(x, taus[0]), taus[0], taus[1], lmax, llls, weights[0], stds=stds_list[0])
+        return float(out[0].sum().item())
     Ws = [w.clone().requires_grad_(True) for w in weights]
     fs = o.split_fragments(x, taus[0])
     emb = [fs[0].reshape(B, -1)]
@@ -371,7 +397,7 @@ def run_reference(args, wl_name, wl):
     steps = max(1, min(args.steps, 3))
     cpu = cpu_baseline(wl, sample=sample, repeats=steps)
     return {
-        "impl": "reference", "metric": "CG-net samples/sec (training step, forward+backward)", "value": cpu["value"],
+        "impl": "reference", "metric": METRIC_INFER if wl.get("kind") == "layer_infer" else METRIC_TRAIN, "value": cpu["value"],
         "unit": "samples/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": 1,
         "ms_per_step": round(1e3 * cpu["seconds_per_step"], 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",

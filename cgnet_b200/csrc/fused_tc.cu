@@ -13,7 +13,7 @@
 //
 // Block = one row tile: degree l, four consecutive m, one group of 32 samples (row r = 32*(m - m0) + sample, the same
 // one-sample-per-lane scheme as the other fused kernels, so the generator is gen_slab unchanged).  Warps:
-//   generator groups 0..kTcStages-1, four warps each: group s produces the cells k = s, s + kTcStages, ... of the
+//   generator groups 0..S-1 (S pipeline stages), four warps each: group s produces the cells k = s, s + S, ... of the
 //     degree into pipeline stage s (A tile written with st.shared, then fence.proxy.async + mbarrier arrive); its first
 //     lane also starts the bulk copy of the cell's packed weights into the stage;
 //   one MMA warp: a single lane waits for each stage, issues the 3 x (2T^2/8) tcgen05.mma of the cell and commits them
@@ -30,9 +30,8 @@
 
 namespace cgb200 {
 
-constexpr int kTcStages = 3;
-constexpr int kTcGenWarps = 4 * kTcStages;
-constexpr int kTcThreads = 32 * (kTcGenWarps + 1);
+constexpr int kTcMaxStages = 5;   // pipeline stages = generator groups; the launch picks as many as shared memory holds
+constexpr int kTcMaxThreads = 32 * (4 * kTcMaxStages + 1);
 constexpr uint32_t kTcSpinLimit = 4000000;   // polls of mbarrier.try_wait before a wait gives up
 
 // ---- thin PTX wrappers --------------------------------------------------------------------------------------------
@@ -166,20 +165,20 @@ tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restric
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// The fused forward on the tensor cores.  grid = (row tiles, sample groups), kTcThreads threads.
-// Dynamic shared memory: kTcStages x { A high [128 x Kc], A low [128 x Kc], B high+low [2 x n_max x Kc] } floats,
+// The fused forward on the tensor cores.  grid = (row tiles, sample groups), 32 * (4 S + 1) threads.
+// Dynamic shared memory: S x { A high [128 x Kc], A low [128 x Kc], B high+low [2 x n_max x Kc] } floats,
 // then one CG band row per generator warp.
 // ---------------------------------------------------------------------------------------------------------------
 template <int T>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
                     const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O, int B, int n_max,
-                    int max_n, int* __restrict__ status) {
+                    int max_n, int* __restrict__ status, int n_stages) {
     constexpr int Kc = 2 * T * T;            // real K extent of one cell
     constexpr int NV = T * T;
     constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kTcStages], empty_bar[kTcStages], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
@@ -193,11 +192,12 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     const uint32_t tmem_cols = N <= 32 ? 32u : N <= 64 ? 64u : 128u;
     const size_t stage_floats = (size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc;
     float* stages = reinterpret_cast<float*>(smem_raw);
-    float* cbuf = stages + kTcStages * stage_floats + (size_t)warp * max_n;
+    float* cbuf = stages + n_stages * stage_floats + (size_t)warp * max_n;
+    const int gen_warps = 4 * n_stages;
     volatile int* failed = &failed_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTcStages; ++s) {
+        for (int s = 0; s < n_stages; ++s) {
             mbar_init(&full_bar[s], 128);
             mbar_init(&empty_bar[s], 1);
         }
@@ -211,7 +211,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp < kTcGenWarps) {
+    if (warp < gen_warps) {
         // ---------------- generators ----------------
         const int s = warp >> 2, wq = warp & 3;
         const int mi = m0 + wq;
@@ -225,7 +225,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
         float4* row_lo = reinterpret_cast<float4*>(a_lo) + (size_t)(r >> 3) * (Kc / 4) * 8 + (r & 7);
         const uint32_t b_bytes = (uint32_t)(2 * N * Kc * sizeof(float));
         bool ok = true;
-        for (int k = s, u = 0; k < ncell && ok; k += kTcStages, ++u) {
+        for (int k = s, u = 0; k < ncell && ok; k += n_stages, ++u) {
             if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
             if (!ok) break;
             if (wq == 0 && lane == 0) {
@@ -284,7 +284,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
         const uint32_t idesc = tc_idesc(128, N);
         bool ok = true;
         for (int k = 0; k < ncell && ok; ++k) {
-            const int s = k % kTcStages, u = k / kTcStages;
+            const int s = k % n_stages, u = k / n_stages;
             ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed);
             if (!ok) break;
             tc_fence_after();
@@ -314,11 +314,12 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 // Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
-// when the mixing dominates, i.e. from about 8 output channels; CGB200_TC=0 / 1 overrides the default.
+// when the mixing dominates: measured on B200, 1.2x faster than the CUDA-core forward at 16 output channels, 2.2-2.7x at
+// 32 and 64, slower below 16.  CGB200_TC=0 / 1 overrides the default.
 bool tc_wanted(const cgb200_plan* p) {
     if (!p->tc_ok) return false;
     if (const char* env = getenv("CGB200_TC")) return env[0] == '1';
-    return p->max_tau_out >= 8;
+    return p->max_tau_out >= 16;
 }
 
 int64_t tc_pack_floats(const cgb200_plan* p) { return p->tc_ok ? p->tc_pack_off.back() : 0; }
@@ -337,16 +338,19 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     launch_end(K_TC_PACK, st);
     CGB_CUDA(cudaGetLastError());
     const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
-    const size_t smem = kTcStages * stage_bytes + (size_t)(kTcGenWarps + 1) * p->max_n * sizeof(float);
-    if (smem > 227 * 1024) {
+    const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
+    int n_stages = (int)std::min<size_t>(kTcMaxStages, (220 * 1024 - cbuf_bytes) / stage_bytes);
+    if (const char* env = getenv("CGB200_TC_STAGES")) n_stages = std::min(n_stages, std::max(1, atoi(env)));
+    const size_t smem = n_stages * stage_bytes + cbuf_bytes;
+    if (n_stages < 2) {
         set_error("tensor-core forward: pipeline stages do not fit in shared memory");
         return CGB200_ERR_UNSUPPORTED;
     }
     auto kern = fused_fwd_tc_kernel<T>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
-    kern<<<dim3(n_tiles, G), kTcThreads, smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B, n_max,
-                                                     p->max_n, p->d_status);
+    kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
+                                                                  n_max, p->max_n, p->d_status, n_stages);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;
