@@ -70,7 +70,7 @@ class SphericalCNN_fast(SphericalCNN):
         self.num_channels_input = int(num_channels_input)
         idx = np.concatenate([c * (lmax + 1) ** 2 + np.arange(l * l, (l + 1) ** 2)
                               for l in range(lmax + 1) for c in range(self.num_channels_input)])
-        self.register_buffer("_gather", torch.as_tensor(idx, dtype=torch.long), persistent=False)
+        self.register_buffer("_gather", torch.as_tensor(idx, dtype=torch.long, device=device), persistent=False)
 
     def pack(self, coeffs):
         """``(B, C, (lmax+1)^2)`` complex -> flat ``(B, sum_l C(2l+1), 2)`` float32 on the module's device."""
