@@ -155,7 +155,7 @@ class ClockSampler:
 def run_ours(args, wl_name, wl):
     import torch.distributed as dist
     from cgnet_b200 import _lib
-    from cgnet_b200.dp import allreduce_gradients, broadcast_parameters
+    from cgnet_b200.dp import GradientAverager, broadcast_parameters
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -182,6 +182,10 @@ def run_ours(args, wl_name, wl):
     if world > 1:
         broadcast_parameters(net)
     params = [p for p in net.parameters() if p.requires_grad]
+    # the network's gradients are 1.5 MB: one bucket, one all-reduce on the compute stream after the backward pass
+    # (measured on two GPUs: +0.035 ms per step; per-layer buckets started inside the backward pass cost +0.10 ms,
+    # because each collective takes SMs from the persistent backward kernels)
+    averager = GradientAverager(params, average=True, bucket_bytes=64 << 20, overlap=False) if world > 1 and not infer else None
     B = wl["batch"]
     n_batches = 4
     host = [synth_batch(wl, 100 + rank * n_batches + i) for i in range(n_batches)]
@@ -198,8 +202,8 @@ def run_ours(args, wl_name, wl):
             p.grad = None
         loss = loss_fn(net(x), y)
         loss.backward()
-        if world > 1:
-            allreduce_gradients(params, average=True)
+        if averager is not None:
+            averager.finish()
         return loss
 
     def barrier():

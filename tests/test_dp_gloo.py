@@ -64,9 +64,64 @@ def test_gradient_allreduce_world2_gloo(bucket_bytes):
     assert out[0][3] == (0, 5) and out[1][3] == (5, 10)
 
 
+def _averager_worker(rank, world, port, bucket_bytes, overlap, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cgnet_b200.dp import GradientAverager, broadcast_parameters, shard_batch
+        torch.manual_seed(5)
+        net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+        unused = torch.nn.Parameter(torch.ones(4))         # never receives a gradient: its bucket must still close
+        broadcast_parameters(net, src=0)
+        params = list(net.parameters()) + [unused]
+        avg = GradientAverager(params, average=True, bucket_bytes=bucket_bytes, overlap=overlap)
+        net2 = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+        net2.load_state_dict(net.state_dict())
+        ok, counts = True, []
+        for step in range(3):                              # several steps: the countdown state must reset
+            torch.manual_seed(20 + step)
+            X = torch.randn(10, 6)
+            sl = shard_batch(10, rank, world)
+            for p in params:
+                p.grad = None
+            net(X[sl]).pow(2).sum().backward()
+            counts.append(avg.finish())
+            for p in net2.parameters():
+                p.grad = None
+            (net2(X).pow(2).sum() / world).backward()      # mean over ranks of per-rank sums
+            ok = ok and all(torch.allclose(p.grad, q.grad, rtol=1e-5, atol=1e-6)
+                            for p, q in zip(net.parameters(), net2.parameters()))
+            ok = ok and unused.grad is None
+        avg.remove()
+        for p in params:
+            p.grad = None
+        net(X[sl]).pow(2).sum().backward()
+        results[rank] = (ok, counts, avg.finish())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("bucket_bytes,overlap", [(1 << 20, True), (64, True), (64, False)])
+def test_gradient_averager_world2_gloo(bucket_bytes, overlap):
+    world = 2
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_averager_worker, args=(world, _free_port(), bucket_bytes, overlap, results), nprocs=world, join=True)
+        out = dict(results)
+    assert set(out) == {0, 1}
+    for rank in range(world):
+        ok, counts, after_remove = out[rank]
+        assert ok, "averaged gradients differ from the single-process gradients of the whole batch"
+        assert counts == [1 if bucket_bytes > 1024 else 4] * 3
+        assert after_remove == 0
+
+
 def test_single_process_is_a_noop():
     from cgnet_b200.dp import allreduce_gradients, shard_batch
     p = torch.nn.Parameter(torch.ones(3))
     p.grad = torch.full((3,), 2.0)
     assert allreduce_gradients([p]) == 0 and torch.equal(p.grad, torch.full((3,), 2.0))
     assert [shard_batch(10, r, 3) for r in range(3)] == [slice(0, 4), slice(4, 7), slice(7, 10)]
+    from cgnet_b200.dp import GradientAverager
+    avg = GradientAverager([p])
+    assert not avg.active and avg.finish() == 0
