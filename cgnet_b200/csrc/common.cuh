@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <mutex>
 #include <vector>
 
 #include "../../include/cgnet_b200.h"
@@ -135,6 +136,7 @@ enum KernelId {
 // the launching stream before and after it.
 void launch_begin(int kid, cudaStream_t st);
 void launch_end(int kid, cudaStream_t st);
+bool timing_active();   // per-kernel event timing is on (cgb200_timing_enable)
 
 #define CGB_CUDA(call)                                         \
     do {                                                       \
@@ -234,6 +236,13 @@ struct cgb200_plan {
     const int* d_fwd_rows = nullptr;
     int max_tau_out = 0;
     std::vector<void*> allocations;   // every cudaMalloc of the plan, freed on destroy
+
+    // cgb200_layer_bwd runs the weight gradient beside the input gradient: a second stream forked from and joined
+    // back to the caller's stream with these two events (created on first use; the mutex keeps one call's
+    // fork ... join enqueue sequence from interleaving with another thread's on the same plan)
+    mutable cudaStream_t side_stream = nullptr;
+    mutable cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    mutable std::mutex side_mutex;
 };
 
 #ifdef __CUDACC__

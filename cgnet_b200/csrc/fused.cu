@@ -897,9 +897,14 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     PrepJob jg{(const float2*)gO, ws.SG, p->d.n_O, p->d.cumO, p->d.cumSO, p->d.tO, p->d.nSO, has_pad(p->tO, T) ? 1 : 0};
     if ((rc = launch_prep(p, jf, jg, p->d.n_O > 0 ? 2 : 1, (int)B, G, fn ? stds : nullptr, eps, ws.inv, ws.counters, st))) return rc;
 
-    // weight gradient: every (to, k) of every degree with both output and mid channels belongs to exactly one task
+    // The weight gradient and the input gradient are independent given gO.  Each leaves SMs idle towards its end
+    // (few long blocks), so the weight gradient goes to a second stream forked from the caller's: its blocks fill the
+    // SMs that the input gradient's last wave leaves free.  With per-kernel timing on, or when only one of the two
+    // runs, everything stays on the caller's stream.
+    const bool want_gf = p->d.n_F > 0 && gF != nullptr;
+    // weight gradient (enqueued on stream gs): every (to, k) of every degree with both output and mid channels belongs to exactly one task
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
-    if (n_tasks > 0) {
+    auto enqueue_gw = [&](cudaStream_t gs) -> int {
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;
@@ -907,12 +912,12 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             set_error("lmax too large for the fused weight-gradient kernel");
             return CGB200_ERR_UNSUPPORTED;
         }
-        launch_begin(K_GW, st);
+        launch_begin(K_GW, gs);
         if (p->d.depthwise) {
             CGB_DISPATCH_TILE(T, false, {
                 auto kern = fused_gw_dw_kernel<TT>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<blocks, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
+                kern<<<blocks, kGwWarps * kWarp, smem, gs>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv, (float2*)gW, G, band_floats);
             });
         } else {
             CGB_DISPATCH_TILE(T, false, {
@@ -920,23 +925,24 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                 const int slices = ws.gw_slices;
                 const int grid = (int)(((int64_t)n_tasks * slices + kGwWarps - 1) / kGwWarps);
-                kern<<<grid, kGwWarps * kWarp, smem, st>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv,
+                kern<<<grid, kGwWarps * kWarp, smem, gs>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv,
                                                            slices > 1 ? ws.gw_part : (float2*)gW, G, band_floats, slices, p->d.w_len);
             });
             if (ws.gw_slices > 1) {
-                launch_end(K_GW, st);
+                launch_end(K_GW, gs);
                 CGB_CUDA(cudaGetLastError());
-                launch_begin(K_GW_REDUCE, st);
+                launch_begin(K_GW_REDUCE, gs);
                 const int gx = (int)std::min<int64_t>((p->d.w_len + 255) / 256, 4 * p->num_sms);
-                gw_reduce_kernel<<<gx, 256, 0, st>>>(ws.gw_part, ws.gw_slices, p->d.w_len, (float2*)gW, p->d.w_len);
+                gw_reduce_kernel<<<gx, 256, 0, gs>>>(ws.gw_part, ws.gw_slices, p->d.w_len, (float2*)gW, p->d.w_len);
             }
         }
-        launch_end(K_GW, st);
+        launch_end(K_GW, gs);
         CGB_CUDA(cudaGetLastError());
-    }
+        return CGB200_OK;
+    };
 
     // input gradient (skipped when the caller passes no buffer: the first layer of a network needs none)
-    if (p->d.n_F > 0 && gF != nullptr) {
+    auto enqueue_gf = [&]() -> int {
         const int lv = ws.gf_level;
         const int nblk = (int)p->gf2_blocks[lv].size() / 4;
         const bool split = p->gf2_max_parts[lv] > 1;
@@ -969,8 +975,33 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         }
         launch_end(K_GF, st);
         CGB_CUDA(cudaGetLastError());
+        return CGB200_OK;
+    };
+
+    const bool want_gw = n_tasks > 0;
+    static const bool serial_env = [] { const char* e = getenv("CGB200_BWD_SERIAL"); return e && atoi(e) != 0; }();
+    if (!(want_gw && want_gf) || timing_active() || serial_env) {
+        if (want_gw && (rc = enqueue_gw(st))) return rc;
+        if (want_gf && (rc = enqueue_gf())) return rc;
+        return CGB200_OK;
     }
-    return CGB200_OK;
+    std::lock_guard<std::mutex> side_lock(p->side_mutex);
+    if (!p->side_stream) {
+        CGB_CUDA(cudaStreamCreateWithFlags(&p->side_stream, cudaStreamNonBlocking));
+        CGB_CUDA(cudaEventCreateWithFlags(&p->ev_fork, cudaEventDisableTiming));
+        CGB_CUDA(cudaEventCreateWithFlags(&p->ev_join, cudaEventDisableTiming));
+    }
+    CGB_CUDA(cudaEventRecord(p->ev_fork, st));
+    CGB_CUDA(cudaStreamWaitEvent(p->side_stream, p->ev_fork, 0));
+    // from here on the join is enqueued whatever the launches return (a capturing stream must be joined)
+    static const bool gw_first = [] { const char* e = getenv("CGB200_BWD_ORDER"); return e && e[0] == 'w'; }();
+    int rc_w = CGB200_OK, rc_f = CGB200_OK;
+    if (gw_first) rc_w = enqueue_gw(p->side_stream);
+    rc_f = enqueue_gf();
+    if (!gw_first) rc_w = enqueue_gw(p->side_stream);
+    CGB_CUDA(cudaEventRecord(p->ev_join, p->side_stream));
+    CGB_CUDA(cudaStreamWaitEvent(st, p->ev_join, 0));
+    return rc_f ? rc_f : rc_w;
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -60,6 +60,7 @@ void launch_begin(int kid, cudaStream_t st) {
         g_timed.push_back(t);
     }
 }
+bool timing_active() { return g_timing.load(std::memory_order_relaxed); }
 void launch_end(int kid, cudaStream_t st) {
     (void)kid;
     if (g_timing.load(std::memory_order_relaxed)) {
@@ -628,6 +629,9 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
 void cgb200_plan_destroy(cgb200_plan* p) {
     if (!p) return;
     for (void* a : p->allocations) cudaFree(a);
+    if (p->side_stream) cudaStreamDestroy(p->side_stream);
+    if (p->ev_fork) cudaEventDestroy(p->ev_fork);
+    if (p->ev_join) cudaEventDestroy(p->ev_join);
     delete p;
 }
 
