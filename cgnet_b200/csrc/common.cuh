@@ -78,6 +78,7 @@ struct GenItem {
     int ncell;
 };
 constexpr int kGenThreads = 256;
+constexpr int kGfWarps = 16;   // warps of an input-gradient block (the plan's phase-2 unit assignment is made for this count)
 
 // Work entry of the fused input-gradient kernel: one triple in which a given fragment takes part, the role it plays
 // there (0: first operand, 1: second operand) and the first channel of the tile of the *other* operand.
@@ -219,6 +220,8 @@ struct cgb200_plan {
     static constexpr int kGfLevels = 6;               // s = 1, 2, 4, 8, 16, 32
     std::vector<int> gf2_blocks[kGfLevels];           // (fragment, owned tile, part, parts) per block
     const int* d_gf2_blocks[kGfLevels] = {nullptr};
+    std::vector<unsigned char> gf_owner;   // warp of every phase-2 unit of the input-gradient kernel, [2 l^2 + u]
+    const unsigned char* d_gf_owner = nullptr;
     std::vector<int> gf2_parts[kGfLevels];            // [lmax+1] parts per fragment
     const int* d_gf2_parts[kGfLevels] = {nullptr};
     int gf2_max_parts[kGfLevels] = {0};

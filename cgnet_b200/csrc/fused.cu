@@ -17,6 +17,7 @@
 //   grad_w        gW_l[to, (t1,t2)] = (1/std) sum_{b, m2} conj(F2[t2, m2]) * sum_m C[m, m2] conj(F1[t1, m-m2]) gO[to, m]
 //   grad_f        gF via gFF tiles built from gO and W in registers, contracted with conj(F) and C into per-warp
 //                 shared-memory accumulators that one block owns
+#include <cuda_pipeline.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -498,17 +499,110 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
 // This is CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289 with gFF living only as one tile
 // in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kGfWarpsMax = 16;
-constexpr int kGfRows = 1;   // rows of the owned fragment a warp gathers together in phase 2 (measured: 1 beats 3, the
-                             // phase is bound by its longest warp, not by shared-memory traffic)
+
+// Work split inside a block.  A phase ends at a barrier, so it lasts as long as its busiest warp.  With 2l+1 = 21 m's or
+// rows on 16 warps whole units would leave a third of the warp-time idle; both phases therefore use half units:
+//   phase 1  unit = (m, half of the tile's NH entries), all of about equal cost, dealt round-robin;
+//   phase 2  unit = (row, first ceil(T/2) or last floor(T/2) owned channels); their cost follows the row's band
+//            length, and the plan holds a longest-processing-time assignment of the 2(2l+1) units of every owned
+//            degree to the 16 warps (PlanDev-independent table `owner`, 2 l^2 + u for unit u of degree l).
+template <int T, bool DW>
+struct GfShape {
+    static constexpr int NH = DW ? T : T * T;
+    static constexpr int NHP = (NH + 1) & ~1;                   // row pitch of the staged weights: 16-byte rows
+    static constexpr int KA = NH >= 4 ? ((NH / 2) & ~1) : 0;    // entries of phase 1's first half (even), 0: no split
+    static constexpr int AH = (T + 1) / 2;                      // owned channels of phase 2's heavy unit
+    static constexpr int AL = T - AH;                           // ... of its light unit (0 for T = 1: no split)
+};
+
+// phase 1 unit: H[m][K0 .. K0+KN) = sum_to wt[to][k] * gO[to, m]
+template <int T, int NH, int NHP, int K0, int KN>
+__device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const float2* __restrict__ wt, float2* __restrict__ h,
+                                          int to_n, int n, int mi) {
+    static_assert(K0 % 2 == 0, "16-byte loads of the staged weights need an even first entry");
+    float2 gt[KN];
+#pragma unroll
+    for (int k = 0; k < KN; ++k) gt[k] = make_float2(0.f, 0.f);
+    constexpr int kPre = 8;   // output-gradient values fetched together: their global-load latencies overlap
+    for (int to0 = 0; to0 < to_n; to0 += kPre) {
+        float2 gvs[kPre];
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) {
+            const int to = to0 + j;
+            gvs[j] = to < to_n ? go[(((to / T) * n + mi) * T + to % T) * 32] : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) {
+            const int to = to0 + j;
+            if (to < to_n) {   // warp-uniform
+                const float2 gv = gvs[j];
+                const float4* w4 = reinterpret_cast<const float4*>(wt + to * NHP + K0);
+#pragma unroll
+                for (int k = 0; k < KN / 2; ++k) {
+                    const float4 w = w4[k];
+                    cfma(gt[2 * k], make_float2(w.x, w.y), gv);
+                    cfma(gt[2 * k + 1], make_float2(w.z, w.w), gv);
+                }
+                if constexpr (KN % 2 == 1) cfma(gt[KN - 1], wt[to * NHP + K0 + KN - 1], gv);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < KN; ++k) h[(K0 + k) * 32] = gt[k];
+}
+
+// phase 2 unit: owned channels A0 .. A0+AN of row r gather their band from the H tiles of the chunk
+template <int T, bool DW, bool FIRST, int A0, int AN>
+__device__ __forceinline__ void gf_row_unit(const float2* __restrict__ H, const float2* __restrict__ fo,
+                                            const float* __restrict__ band, float2* __restrict__ acc, int r, int lt, int nt,
+                                            int l, int lo_, int l2, int n2, int mc0, int mcn, int lane) {
+    constexpr int NH = DW ? T : T * T;
+    float2 x[AN];
+#pragma unroll
+    for (int a = 0; a < AN; ++a) x[a] = make_float2(0.f, 0.f);
+    const int mt = r - lt;
+    // m = m_t + u with u = m of the other operand's element, |u| <= lo_, m inside [-l, l] and inside the chunk
+    const int mlo = max(max(-l, mc0 - l), mt - lo_), mhi = min(min(l, mc0 + mcn - 1 - l), mt + lo_);
+    for (int m = mlo; m <= mhi; ++m) {
+        const int u = m - mt;
+        const float cg = band[(m + l) * n2 + (FIRST ? u : mt) + l2];   // band entry [m + l][m2 + l2]
+        const float2* ph = H + (size_t)(m + l - mc0) * NH * 32 + lane;
+        const float2* pf = fo + (size_t)(u + lo_) * T * 32 + lane;
+        if constexpr (DW) {
+#pragma unroll
+            for (int a = 0; a < AN; ++a) {
+                const float2 f = pf[(A0 + a) * 32];
+                cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), ph[(A0 + a) * 32]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < T; ++c) {
+                float2 f = pf[c * 32];
+                f.x *= cg;
+                f.y *= cg;
+#pragma unroll
+                for (int a = 0; a < AN; ++a) cfma_conj(x[a], f, ph[(FIRST ? (A0 + a) * T + c : c * T + A0 + a) * 32]);
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < AN; ++a) {
+        float2* pa = acc + ((size_t)(A0 + a) * nt + r) * 32 + lane;
+        float2 cur = *pa;
+        cur.x += x[a].x;
+        cur.y += x[a].y;
+        *pa = cur;
+    }
+}
 
 template <int T, bool DW>
-__global__ void __launch_bounds__(kGfWarpsMax * kWarp)
+__global__ void __launch_bounds__(kGfWarps * kWarp)
 fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
-                const int* __restrict__ blocks, const float2* __restrict__ SF, const float2* __restrict__ SG,
-                const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ out,
-                int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats) {
-    constexpr int NH = DW ? T : T * T;
+                const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
+                const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
+                float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats) {
+    using S = GfShape<T, DW>;
+    constexpr int NH = S::NH, NHP = S::NHP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lt = blocks[4 * blockIdx.x], q = blocks[4 * blockIdx.x + 1];
     const int part = blocks[4 * blockIdx.x + 2], parts = blocks[4 * blockIdx.x + 3];
@@ -518,127 +612,122 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     const int nwarps = blockDim.x >> 5;
     const int tau_t = P.tF[lt];
     float2* acc = reinterpret_cast<float2*>(smem_raw);          // [T][nt][32]
-    float2* fo = acc + (size_t)T * max_n * 32;                   // [n_o][T][32]  other operand's tile
-    float2* wt = fo + (size_t)T * max_n * 32;                    // [to_n][NH]    conj(W) / std
-    float* band = reinterpret_cast<float*>(wt + (size_t)max_to * NH);   // [n][n2]
-    float2* H = reinterpret_cast<float2*>(band + band_floats);   // [Mc][NH][32]
+    float2* fo2 = acc + (size_t)T * max_n * 32;                  // 2 x [n_o][T][32]  other operand's tile, two entries
+    float2* wt = fo2 + (size_t)2 * T * max_n * 32;               // [to_n][NHP]   conj(W) / std
+    float* band2 = reinterpret_cast<float*>(wt + (size_t)max_to * NHP);   // 2 x [n][n2]
+    unsigned char* owner = reinterpret_cast<unsigned char*>(band2 + 2 * band_floats);   // [2 nt] warp of every phase-2 unit
+    float2* H = reinterpret_cast<float2*>(owner + ((2 * max_n + 15) & ~15));      // [Mc][NH][32]
     for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
+    for (int i = threadIdx.x; i < 2 * nt; i += blockDim.x) owner[i] = owner_tab[2 * lt * lt + i];
     const float2* slabF = SF + (int64_t)g * P.nSF * 32;
     const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
+
+    // Staging of an entry runs one entry ahead of its use: the other operand's tile and the CG band go to the idle
+    // half of their double buffers by asynchronous copies issued when the previous entry starts; the tile of
+    // conj(W)/std is fetched into registers before the previous entry's phase 2 (which does not read `wt`) and stored
+    // after it.  No warp then waits at a barrier for another warp's global loads.
+    auto stage_async = [&](const GfInfo& x, int buf) {
+        const bool fst = x.role == 0;
+        const int xn = 2 * x.l + 1, xn2 = 2 * x.l2 + 1, xno = fst ? xn2 : 2 * x.l1 + 1;
+        const float4* src = reinterpret_cast<const float4*>(slabF + ((int64_t)x.fo_off + (DW ? q * xno * T : 0)) * 32);
+        float4* dstf = reinterpret_cast<float4*>(fo2 + (size_t)buf * T * max_n * 32);
+        for (int i = threadIdx.x; i < xno * T * 16; i += blockDim.x) __pipeline_memcpy_async(dstf + i, src + i, 16);
+        float* dstb = band2 + buf * band_floats;
+        for (int i = threadIdx.x; i < xn * xn2; i += blockDim.x) __pipeline_memcpy_async(dstb + i, P.cg + x.cgoff + i, 4);
+        __pipeline_commit();
+    };
+    constexpr int kWtRegs = 2;   // staged weights a thread carries in registers across phase 2
+    auto wt_load = [&](const GfInfo& x, int i) -> float2 {
+        const bool fst = x.role == 0;
+        const int xin0 = DW ? 0 : x.in0;
+        const int t = i / NH, idx = i - t * NH;
+        const int i1 = DW ? idx : idx / T, j1 = DW ? idx : idx % T;
+        const int a = fst ? i1 : j1, c = fst ? j1 : i1;   // owned / other channel inside their tiles
+        const bool ok = (t_0 + a < tau_t) && (DW || xin0 + c < x.tau_o);
+        const int t1 = fst ? t_0 + a : xin0 + c, t2 = fst ? xin0 + c : t_0 + a;
+        const int ch = DW ? t_0 + a : t1 * x.tau2 + t2;
+        float2 w = make_float2(0.f, 0.f);
+        if (ok) {
+            w = __ldg(W + x.woff + (int64_t)t * x.tff + ch);
+            const float sc = __ldg(inv + x.kglob + ch);
+            w = make_float2(w.x * sc, -w.y * sc);
+        }
+        return w;
+    };
+    auto wt_prefetch = [&](const GfInfo& x, float2 (&reg)[kWtRegs]) {
+#pragma unroll
+        for (int j = 0; j < kWtRegs; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < x.to_n * NH) reg[j] = wt_load(x, i);
+        }
+    };
+    auto wt_store = [&](const GfInfo& x, const float2 (&reg)[kWtRegs]) {
+#pragma unroll
+        for (int j = 0; j < kWtRegs; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < x.to_n * NH) wt[(i / NH) * NHP + i % NH] = reg[j];
+        }
+        for (int i = threadIdx.x + kWtRegs * blockDim.x; i < x.to_n * NH; i += blockDim.x)   // beyond the registers
+            wt[(i / NH) * NHP + i % NH] = wt_load(x, i);
+    };
 
     const int e_end = entry_begin[lt + 1];
     int e = entry_begin[lt] + part;
     GfInfo en;
-    if (e < e_end) en = entries[e];
+    float2 wreg[kWtRegs];
+    int buf = 0;
+    if (e < e_end) {
+        en = entries[e];
+        stage_async(en, 0);
+        wt_prefetch(en, wreg);
+    }
     while (e < e_end) {
+        const bool has_next = e + parts < e_end;
         GfInfo nxt;
-        if (e + parts < e_end) nxt = entries[e + parts];   // in flight while this entry is computed
-        const int l = en.l, n = 2 * l + 1, n1 = 2 * en.l1 + 1, n2 = 2 * en.l2 + 1;
-        const int to_n = en.to_n, tff = en.tff;
+        if (has_next) nxt = entries[e + parts];
+        const int l = en.l, n = 2 * l + 1, n2 = 2 * en.l2 + 1;
+        const int to_n = en.to_n;
         const bool first = en.role == 0;   // the owned fragment is the first operand of this triple
-        const int in0 = DW ? 0 : en.in0;
-        const int n_o = first ? n2 : n1;
-        __syncthreads();   // the previous entry's readers are done with the staging buffers
-        {
-            const float4* src = reinterpret_cast<const float4*>(slabF + ((int64_t)en.fo_off + (DW ? q * n_o * T : 0)) * 32);
-            float4* dst = reinterpret_cast<float4*>(fo);
-            for (int i = threadIdx.x; i < n_o * T * 16; i += blockDim.x) dst[i] = src[i];
-            for (int i = threadIdx.x; i < n * n2; i += blockDim.x) band[i] = __ldg(P.cg + en.cgoff + i);
-            for (int i = threadIdx.x; i < to_n * NH; i += blockDim.x) {
-                const int t = i / NH, idx = i - t * NH;
-                const int i1 = DW ? idx : idx / T, j1 = DW ? idx : idx % T;
-                const int a = first ? i1 : j1, c = first ? j1 : i1;   // owned / other channel inside their tiles
-                const bool ok = (t_0 + a < tau_t) && (DW || in0 + c < en.tau_o);
-                const int t1 = first ? t_0 + a : in0 + c, t2 = first ? in0 + c : t_0 + a;
-                const int ch = DW ? t_0 + a : t1 * en.tau2 + t2;
-                float2 w = make_float2(0.f, 0.f);
-                if (ok) {
-                    w = __ldg(W + en.woff + (int64_t)t * tff + ch);
-                    const float sc = __ldg(inv + en.kglob + ch);
-                    w = make_float2(w.x * sc, -w.y * sc);
-                }
-                wt[i] = w;
-            }
-        }
+        const float2* fo = fo2 + (size_t)buf * T * max_n * 32;
+        const float* band = band2 + buf * band_floats;
+        wt_store(en, wreg);          // phase 1 of the previous entry ended before its second barrier
+        __pipeline_wait_prior(0);    // this thread's copies for this entry have landed
+        __syncthreads();             // staging visible; the previous entry's phase 2 is over: H and the other halves are free
+        if (has_next) stage_async(nxt, buf ^ 1);
         const float2* go = slabG + (int64_t)en.go_off * 32;
+        const int lo_ = first ? en.l2 : en.l1;
         for (int mc0 = 0; mc0 < n; mc0 += Mc) {
             const int mcn = min(Mc, n - mc0);
-            __syncthreads();   // staging visible; the previous chunk's readers are done with H
-            for (int mi = mc0 + warp; mi < mc0 + mcn; mi += nwarps) {
-                float2 gt[NH];
-#pragma unroll
-                for (int k = 0; k < NH; ++k) gt[k] = make_float2(0.f, 0.f);
-                for (int to = 0; to < to_n; ++to) {
-                    const float2 gv = go[(((to / T) * n + mi) * T + to % T) * 32];
-                    const float2* w = wt + to * NH;
-#pragma unroll
-                    for (int k = 0; k < NH; ++k) cfma(gt[k], w[k], gv);
+            if (mc0 > 0) __syncthreads();   // the previous chunk's readers are done with H
+            if constexpr (S::KA > 0) {
+                for (int u = warp; u < 2 * mcn; u += nwarps) {
+                    const int mi = mc0 + (u >> 1);
+                    float2* h = H + (size_t)(mi - mc0) * NH * 32 + lane;
+                    if (u & 1) gf_h_unit<T, NH, NHP, S::KA, NH - S::KA>(go, wt, h, to_n, n, mi);
+                    else gf_h_unit<T, NH, NHP, 0, S::KA>(go, wt, h, to_n, n, mi);
                 }
-                float2* h = H + (size_t)(mi - mc0) * NH * 32 + lane;
-#pragma unroll
-                for (int k = 0; k < NH; ++k) h[k * 32] = gt[k];
+            } else {
+                for (int mi = mc0 + warp; mi < mc0 + mcn; mi += nwarps)
+                    gf_h_unit<T, NH, NHP, 0, NH>(go, wt, H + (size_t)(mi - mc0) * NH * 32 + lane, to_n, n, mi);
             }
             __syncthreads();
-            // rows of the owned fragment in groups of kGfRows: the rows of a group need the same H[m] tiles, which
-            // are loaded into registers once per m and used for every row of the group (shared-memory traffic / kGfRows)
-            const int lo_ = first ? en.l2 : en.l1;
-            for (int r0 = warp * kGfRows; r0 < nt; r0 += nwarps * kGfRows) {
-                float2 x[kGfRows][T];
-#pragma unroll
-                for (int rr = 0; rr < kGfRows; ++rr)
-#pragma unroll
-                    for (int a = 0; a < T; ++a) x[rr][a] = make_float2(0.f, 0.f);
-                const int mt0 = r0 - lt;   // m of the group's first row; row rr has m_t = mt0 + rr
-                const int rows = min(kGfRows, nt - r0);
-                // m = m_t + u with u = m of the other operand's element, |u| <= lo_, m inside [-l, l] and the chunk
-                const int mlo = max(max(-l, mc0 - l), mt0 - lo_), mhi = min(min(l, mc0 + mcn - 1 - l), mt0 + rows - 1 + lo_);
-                for (int m = mlo; m <= mhi; ++m) {
-                    float2 h[NH];
-                    const float2* ph = H + (size_t)(m + l - mc0) * NH * 32 + lane;
-#pragma unroll
-                    for (int k = 0; k < NH; ++k) h[k] = ph[k * 32];
-#pragma unroll
-                    for (int rr = 0; rr < kGfRows; ++rr) {
-                        const int u = m - (mt0 + rr);
-                        if (rr < rows && u >= -lo_ && u <= lo_) {   // warp-uniform
-                            // band entry [m + l][m2 + l2]: m2 = u (first) or m_t (second)
-                            const float cg = band[(m + l) * n2 + (first ? u : mt0 + rr) + en.l2];
-                            const float2* pf = fo + (size_t)(u + lo_) * T * 32 + lane;
-                            if constexpr (DW) {
-#pragma unroll
-                                for (int a = 0; a < T; ++a) {
-                                    const float2 f = pf[a * 32];
-                                    cfma_conj(x[rr][a], make_float2(f.x * cg, f.y * cg), h[a]);
-                                }
-                            } else {
-#pragma unroll
-                                for (int c = 0; c < T; ++c) {
-                                    float2 f = pf[c * 32];
-                                    f.x *= cg;
-                                    f.y *= cg;
-#pragma unroll
-                                    for (int a = 0; a < T; ++a) cfma_conj(x[rr][a], f, first ? h[a * T + c] : h[c * T + a]);
-                                }
-                            }
-                        }
-                    }
+            if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
+            for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u) {
+                if (owner[u] != warp) continue;   // warp-uniform
+                const bool heavy = u < nt;
+                const int r = heavy ? u : u - nt;
+                if (heavy) {
+                    if (first) gf_row_unit<T, DW, true, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                    else gf_row_unit<T, DW, false, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                } else if constexpr (S::AL > 0) {
+                    if (first) gf_row_unit<T, DW, true, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                    else gf_row_unit<T, DW, false, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
                 }
-#pragma unroll
-                for (int rr = 0; rr < kGfRows; ++rr)
-                    if (rr < rows) {
-#pragma unroll
-                        for (int a = 0; a < T; ++a) {
-                            float2* pa = acc + ((size_t)a * nt + r0 + rr) * 32 + lane;
-                            float2 cur = *pa;
-                            cur.x += x[rr][a].x;
-                            cur.y += x[rr][a].y;
-                            *pa = cur;
-                        }
-                    }
             }
         }
         en = nxt;
         e += parts;
+        buf ^= 1;
     }
     __syncthreads();
     float2* dst = out + (int64_t)part * part_stride;
@@ -949,7 +1038,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         const int NHh = p->d.depthwise ? T : T * T;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const int max_to = std::max(p->max_tau_out, 1);
-        const size_t fixed = (size_t)2 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * NHh * sizeof(float2) + p->gen_band_bytes;
+        const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
+                             2 * p->gen_band_bytes + (size_t)((2 * p->max_n + 15) & ~15);
         const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
         if (fixed + per_m > 227 * 1024) {
             set_error("lmax or tau_out too large for the fused input-gradient kernel");
@@ -963,8 +1053,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = fused_gf_kernel<TT, DD>;
             if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            const int nwarps = kGfWarpsMax;
-            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+            const int nwarps = kGfWarps;
+            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
         });
         if (split) {
             launch_end(K_GF, st);

@@ -569,6 +569,42 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     }
     if ((rc = upload(p, p->gf_info, &p->d_gf_info))) return rc;
     {
+        // Phase 2 of the input-gradient kernel: rows of the owned fragment, each split into a unit for the first
+        // ceil(T/2) owned channels and one for the rest, dealt to the block's 16 warps by longest processing time first.
+        // A unit's cost is its share of the row's band length summed over the fragment's entries plus a fixed part.
+        constexpr int kWarps = kGfWarps;
+        const int ah = (T + 1) / 2, al = T - ah;
+        p->gf_owner.assign((size_t)2 * L1 * L1, 255);
+        for (int l = 0; l < L1; ++l) {
+            const int nt = 2 * l + 1;
+            std::vector<double> row(nt, 0.0);
+            for (int e = p->gf_begin[l]; e < p->gf_begin[l + 1]; ++e) {
+                const TripleRec& t = p->triples[p->gf_entries[e].triple];
+                const int lo_ = p->gf_entries[e].role == 0 ? t.l2 : t.l1;
+                for (int r = 0; r < nt; ++r) {
+                    const int mt = r - l;
+                    const int len = std::min(t.l, mt + lo_) - std::max(-t.l, mt - lo_) + 1;
+                    row[r] += std::max(len, 0) + 1.0;
+                }
+            }
+            std::vector<std::pair<double, int>> units;
+            for (int r = 0; r < nt; ++r) {
+                units.push_back({row[r] * (0.15 + ah), r});
+                if (al > 0) units.push_back({row[r] * (0.15 + al), nt + r});
+            }
+            std::stable_sort(units.begin(), units.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
+            double load[kWarps] = {0.0};
+            for (auto& u : units) {
+                int best = 0;
+                for (int w = 1; w < kWarps; ++w)
+                    if (load[w] < load[best]) best = w;
+                load[best] += u.first;
+                p->gf_owner[(size_t)2 * l * l + u.second] = (unsigned char)best;
+            }
+        }
+        if ((rc = upload(p, p->gf_owner, &p->d_gf_owner))) return rc;
+    }
+    {
         // cost of a fragment's entry list ~ sum over entries of (2l+1)*tau_out*T^2 (gFF tile) + band*T^2 (contraction)
         std::vector<double> cost(L1, 0.0);
         double cmax = 0.0;
