@@ -523,27 +523,25 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
     float2 gt[KN];
 #pragma unroll
     for (int k = 0; k < KN; ++k) gt[k] = make_float2(0.f, 0.f);
-    constexpr int kPre = 8;   // output-gradient values fetched together: their global-load latencies overlap
-    for (int to0 = 0; to0 < to_n; to0 += kPre) {
-        float2 gvs[kPre];
+    // one output tile (T channels, adjacent in the slab) per step: its T loads are issued together, so their
+    // global-load latencies overlap, and their offsets are compile-time constants
+    for (int to0 = 0; to0 < to_n; to0 += T) {
+        const float2* gp = go + ((to0 / T) * n + mi) * T * 32;
+        float2 gvs[T];
 #pragma unroll
-        for (int j = 0; j < kPre; ++j) {
-            const int to = to0 + j;
-            gvs[j] = to < to_n ? go[(((to / T) * n + mi) * T + to % T) * 32] : make_float2(0.f, 0.f);
-        }
+        for (int j = 0; j < T; ++j) gvs[j] = to0 + j < to_n ? gp[j * 32] : make_float2(0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < kPre; ++j) {
-            const int to = to0 + j;
-            if (to < to_n) {   // warp-uniform
+        for (int j = 0; j < T; ++j) {
+            if (to0 + j < to_n) {   // warp-uniform
                 const float2 gv = gvs[j];
-                const float4* w4 = reinterpret_cast<const float4*>(wt + to * NHP + K0);
+                const float4* w4 = reinterpret_cast<const float4*>(wt + (to0 + j) * NHP + K0);
 #pragma unroll
                 for (int k = 0; k < KN / 2; ++k) {
                     const float4 w = w4[k];
                     cfma(gt[2 * k], make_float2(w.x, w.y), gv);
                     cfma(gt[2 * k + 1], make_float2(w.z, w.w), gv);
                 }
-                if constexpr (KN % 2 == 1) cfma(gt[KN - 1], wt[to * NHP + K0 + KN - 1], gv);
+                if constexpr (KN % 2 == 1) cfma(gt[KN - 1], wt[(to0 + j) * NHP + K0 + KN - 1], gv);
             }
         }
     }
@@ -615,10 +613,16 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     float2* fo2 = acc + (size_t)T * max_n * 32;                  // 2 x [n_o][T][32]  other operand's tile, two entries
     float2* wt = fo2 + (size_t)2 * T * max_n * 32;               // [to_n][NHP]   conj(W) / std
     float* band2 = reinterpret_cast<float*>(wt + (size_t)max_to * NHP);   // 2 x [n][n2]
-    unsigned char* owner = reinterpret_cast<unsigned char*>(band2 + 2 * band_floats);   // [2 nt] warp of every phase-2 unit
-    float2* H = reinterpret_cast<float2*>(owner + ((2 * max_n + 15) & ~15));      // [Mc][NH][32]
+    unsigned short* ulist = reinterpret_cast<unsigned short*>(band2 + 2 * band_floats);   // [warps][2 max_n] phase-2 units of each warp
+    float2* H = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(ulist) + ((kGfWarps * 4 * max_n + 15) & ~15));   // [Mc][NH][32]
     for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
-    for (int i = threadIdx.x; i < 2 * nt; i += blockDim.x) owner[i] = owner_tab[2 * lt * lt + i];
+    int n_units = 0;   // this warp's phase-2 units, listed once per block (every lane keeps the same count)
+    for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u)
+        if (owner_tab[2 * lt * lt + u] == warp) {
+            if (lane == 0) ulist[warp * 2 * max_n + n_units] = (unsigned short)u;
+            ++n_units;
+        }
+    __syncwarp();
     const float2* slabF = SF + (int64_t)g * P.nSF * 32;
     const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
 
@@ -712,8 +716,8 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
             }
             __syncthreads();
             if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
-            for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u) {
-                if (owner[u] != warp) continue;   // warp-uniform
+            for (int k = 0; k < n_units; ++k) {
+                const int u = ulist[warp * 2 * max_n + k];
                 const bool heavy = u < nt;
                 const int r = heavy ? u : u - nt;
                 if (heavy) {
@@ -1039,7 +1043,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const int max_to = std::max(p->max_tau_out, 1);
         const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
-                             2 * p->gen_band_bytes + (size_t)((2 * p->max_n + 15) & ~15);
+                             2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
         const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
         if (fixed + per_m > 227 * 1024) {
             set_error("lmax or tau_out too large for the fused input-gradient kernel");
