@@ -156,3 +156,56 @@ def test_layer_matches_reference_kernels(ref_ops, taus, tau_out, B, mode, bn, tr
         assert_fragments_close(gF.cpu().numpy(), r_gF.cpu().numpy(), taus, f"gF ({tag}) vs reference kernels")
         if training:
             np.testing.assert_allclose(stds.cpu().numpy(), r_stds.cpu().numpy(), rtol=2e-5, atol=1e-7)
+
+
+def _time_ms(fn, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+SPEED_CASES = [
+    ("benchmark layer (lmax 10, tau 5 -> 5, batch 100)", [5] * 11, [5] * 11, 100),
+    ("benchmark first layer (lmax 10, tau 1 -> 5, batch 100)", [1] * 11, [5] * 11, 100),
+    ("single layer lmax 5, tau 8, batch 32", [8] * 6, [8] * 6, 32),
+]
+
+
+@pytest.mark.parametrize("name,taus,tau_out,B", SPEED_CASES)
+def test_layer_is_faster_than_reference_kernels(ref_ops, name, taus, tau_out, B, capsys):
+    """Forward + backward of one layer with training-mode norm: the fused path and the reference's four kernel calls
+    (product, norm + mixing, their two backward calls, with the zero-filled outputs the reference's modules allocate on
+    every call, CGNet/CG_layers.py:262-286,126-160), timed with CUDA events on the same GPU.  The results of the two paths
+    are compared by the parity tests above; this one records the ratio and fails if the fused path is not faster."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, "default", seed=43)
+    ref = RefLayer(ref_ops, case)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], dev())
+    F = torch.tensor(case["F"], device=dev())
+    W = torch.tensor(case["W"], device=dev())
+    gO = torch.tensor(case["gO"], device=dev())
+    cnt, eps, flags = 2.0, 1e-5, 3
+    r_stds = torch.tensor(case["stds"], device=dev())
+    o_stds = r_stds.clone()
+
+    def run_ref():
+        FF = ref.product_fwd(F)
+        ref.mix_fwd(FF, W, r_stds, cnt, eps, flags)
+        gFF, _ = ref.mix_bwd(gO, FF, W, r_stds, cnt, eps, flags)
+        ref.product_bwd(F, gFF)
+
+    def run_ours():
+        plan.layer_fwd(F, W, o_stds, cnt, eps, flags)
+        plan.layer_bwd(F, W, o_stds, eps, flags & _lib.FN_PRESENT, gO)
+
+    t_ref, t_ours = _time_ms(run_ref), _time_ms(run_ours)
+    with capsys.disabled():
+        print(f"\n[speed] {name}: reference kernels {t_ref:.3f} ms, fused path {t_ours:.3f} ms, ratio {t_ref / t_ours:.1f}x")
+    assert t_ours < t_ref, f"{name}: fused path {t_ours:.3f} ms is not faster than the reference kernels {t_ref:.3f} ms"
