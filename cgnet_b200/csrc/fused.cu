@@ -148,7 +148,7 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
         const int g = task / n, mi = task - g * n;
         const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
         float2 v[NV];
-        gen_slab<T, DW>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
+        gen_slab<T, DW, true>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float nrm = v[i].x * v[i].x + v[i].y * v[i].y;
