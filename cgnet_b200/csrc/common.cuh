@@ -131,7 +131,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // Kernel identifiers for launch accounting and the optional per-kernel CUDA-event timing (cgb200_timing_*).
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
-    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_COUNT
+    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.
@@ -177,6 +177,8 @@ bool timing_active();   // per-kernel event timing is on (cgb200_timing_enable)
 struct cgb200_plan;
 namespace cgb200 {
 bool tc_wanted(const cgb200_plan* p);
+bool tc_gw_wanted(const cgb200_plan* p);
+int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, int G, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
 int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
                   cudaStream_t st);
@@ -234,6 +236,8 @@ struct cgb200_plan {
     const int* d_tc_npad = nullptr;
     const int64_t* d_tc_pack_off = nullptr;
     const int* d_tc_tiles = nullptr;
+    std::vector<int> tc_gw_tiles;       // tensor-core weight gradient: (l, first cell of a block of four) pairs, longest first
+    const int* d_tc_gw_tiles = nullptr;
     int* d_status = nullptr;          // set to 1 by a kernel whose bounded wait ran out (cgb200_plan_status)
     std::vector<int> fwd_rows;        // (l, m+l) rows of the output, most expensive first (dynamic scheduling order)
     const int* d_fwd_rows = nullptr;

@@ -998,6 +998,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     // weight gradient (enqueued on stream gs): every (to, k) of every degree with both output and mid channels belongs to exactly one task
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
     auto enqueue_gw = [&](cudaStream_t gs) -> int {
+        if (tc_gw_wanted(p)) return launch_gw_tc(p, ws.SF, ws.SG, ws.inv, (float2*)gW, G, gs);
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;

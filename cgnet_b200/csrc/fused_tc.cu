@@ -311,6 +311,177 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// The weight gradient on the tensor cores.
+//
+//   gW_l[to, k] = 1/std_k * sum_{b, m} conj(FF_l[b, k, m]) * gO_l[b, to, m]
+//
+// as a real GEMM that contracts over (m, b):  D[(k, re|im), (to, re|im)] = sum A'[(k, .), (m, b)] * B'[(to, .), (m, b)],
+// from which gW.re = D[kr, tor] + D[ki, toi] and gW.im = D[kr, toi] - D[ki, tor].  Block = four cells of one degree
+// (4 x 2T^2 = 128 rows of D for T = 4 = the 128 lanes of tensor memory) against all output channels; it walks every
+// (sample group, m) of the layer, 32 samples = one K chunk = four K steps of the MMA.  Generator group s (four warps,
+// warp w <-> cell w of the block) fills pipeline stage s for the chunks s, s + S, ...: the cell's FF values of its lane's
+// sample, split into TF32 high / low parts, go to shared memory as the M x K operand (K-major: a lane owns one K
+// column), and the four warps share the chunk's gO values as the N x K operand.  The K stride between core matrices is
+// 144 bytes instead of 128, so that the eight lane quads of a warp, which write eight different core matrices of the
+// same row, fall into different banks.  MMA warp, barriers, bounded waits and 3xTF32 as in the forward kernel; the
+// accumulation order is fixed, so the result is bit-identical from run to run.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr uint32_t kGwLbo = 144;           // bytes between K-adjacent core matrices (8 rows x 16 bytes, then 16 bytes of padding)
+constexpr uint32_t kGwSbo = 8 * kGwLbo;    // bytes between 8-row groups: a K chunk of 32 samples = 8 core matrices
+
+template <int T>
+__global__ void __launch_bounds__(kTcMaxThreads)
+fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
+                   const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
+                   int max_n, int* __restrict__ status, int n_stages) {
+    constexpr int NV = T * T;
+    constexpr int MR = 2 * NV;   // real rows of D per cell
+    static_assert(4 * MR == 128, "four cells must fill the 128 rows of the accumulator");
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed_flag;
+
+    const int l = tiles[2 * blockIdx.x], cell0 = tiles[2 * blockIdx.x + 1];
+    const int n = 2 * l + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
+    const int N = npad[l];
+    const int to_n = P.tO[l], tff = P.tFF[l];
+    const uint32_t tmem_cols = N <= 32 ? 32u : N <= 64 ? 64u : 128u;
+    const uint32_t a_bytes = 16 * kGwSbo, b_bytes = (uint32_t)(n_max / 8) * kGwSbo;
+    const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    float* cbuf = reinterpret_cast<float*>(smem_raw + (size_t)n_stages * stage_bytes) + (size_t)warp * max_n;
+    const int gen_warps = 4 * n_stages;
+    const int n_chunks = n * G;
+    volatile int* failed = &failed_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(&full_bar[s], 128);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        failed_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp < gen_warps) {
+        // ---------------- generators ----------------
+        const int s = warp >> 2, wq = warp & 3;
+        const int cell = cell0 + wq;
+        const bool live = cell < ncell;
+        CellInfo ci{};
+        if (live) ci = P.cell_info[c_begin + cell];
+        const int n2 = 2 * ci.l2 + 1;
+        unsigned char* st_base = smem_raw + (size_t)s * stage_bytes;
+        // this lane's K column inside a chunk: core matrix lane/4 along K, word lane%4 inside its 16-byte row
+        const uint32_t col_off = (uint32_t)(lane >> 2) * kGwLbo + (uint32_t)(lane & 3) * 4;
+        unsigned char* a_hi = st_base + (uint32_t)(wq * (MR / 8)) * kGwSbo + col_off;   // this warp's 32 rows
+        unsigned char* a_lo = a_hi + a_bytes;
+        unsigned char* b_hi = st_base + 2 * a_bytes + col_off;
+        unsigned char* b_lo = b_hi + b_bytes;
+        const int to_per = (to_n + 3) >> 2, to_lo = wq * to_per, to_hi = min(to_n, to_lo + to_per);
+        bool ok = true;
+        for (int q = s, u = 0; q < n_chunks && ok; q += n_stages, ++u) {
+            if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
+            if (!ok) break;
+            const int g = q / n, mi = q - g * n;
+            if (live) {
+                const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
+                float2 v[NV];
+                __syncwarp();
+                for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
+                __syncwarp();
+                gen_slab<T, false>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+#pragma unroll
+                for (int kk = 0; kk < MR; ++kk) {
+                    const float x = (kk & 1) ? v[kk >> 1].y : v[kk >> 1].x;
+                    const float h = to_tf32(x);
+                    const uint32_t off = (uint32_t)(kk >> 3) * kGwSbo + (uint32_t)(kk & 7) * 16;
+                    *reinterpret_cast<float*>(a_hi + off) = h;
+                    *reinterpret_cast<float*>(a_lo + off) = x - h;
+                }
+            }
+            const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
+            for (int to = to_lo; to < to_hi; ++to) {
+                const float2 gv = go[(((to / T) * n + mi) * T + to % T) * 32];
+                const float hr = to_tf32(gv.x), hi_ = to_tf32(gv.y);
+                const int r0 = 2 * to;   // rows (to, re) and (to, im): same 8-row group, adjacent 16-byte rows
+                const uint32_t off = (uint32_t)(r0 >> 3) * kGwSbo + (uint32_t)(r0 & 7) * 16;
+                *reinterpret_cast<float*>(b_hi + off) = hr;
+                *reinterpret_cast<float*>(b_hi + off + 16) = hi_;
+                *reinterpret_cast<float*>(b_lo + off) = gv.x - hr;
+                *reinterpret_cast<float*>(b_lo + off + 16) = gv.y - hi_;
+            }
+            fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
+            mbar_arrive(&full_bar[s]);
+        }
+        // ---------------- epilogue (first generator group): warp w owns the accumulator rows of cell w ----------------
+        if (s == 0) {
+            if (n_chunks > 0) ok = ok && mbar_wait(&done_bar, 0u, failed);
+            tc_fence_after();
+            const int idx = lane >> 1, i = idx / T, j = idx - i * T;
+            const bool writer = live && (lane & 1) == 0 && i < ci.v1 && j < ci.v2;
+            const int ch = i * ci.tau2 + j;
+            const float sc = writer ? inv[ci.kch0 + ch] : 0.f;
+            float2* out = gW + P.cumW[l] + ci.wch0 + ch;
+            for (int col0 = 0; col0 < N; col0 += 16) {
+                uint32_t rr[16];
+                if (n_chunks > 0 && ok) {
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) rr[c] = 0u;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float mr = __uint_as_float(rr[2 * c]), mim = __uint_as_float(rr[2 * c + 1]);
+                    const float orr = __shfl_xor_sync(0xffffffffu, mr, 1), oim = __shfl_xor_sync(0xffffffffu, mim, 1);
+                    const int to = (col0 >> 1) + c;
+                    // even lane = row (k, re), its neighbour = row (k, im)
+                    if (writer && to < to_n) out[(int64_t)to * tff] = make_float2((mr + oim) * sc, (mim - orr) * sc);
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = tc_idesc(128, N);
+        bool ok = true;
+        for (int q = 0; q < n_chunks && ok; ++q) {
+            const int s = q % n_stages, u = q / n_stages;
+            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(smem_raw + (size_t)s * stage_bytes);
+            const uint32_t a_lo = a_hi + a_bytes;
+            const uint32_t b_hi = a_lo + a_bytes;
+            const uint32_t b_lo = b_hi + b_bytes;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {   // 32 samples = 4 K steps of 8 = 2 core matrices each
+                const uint32_t koff = ks * 2 * kGwLbo;
+                const uint64_t dah = smem_desc(a_hi + koff, kGwLbo, kGwSbo), dal = smem_desc(a_lo + koff, kGwLbo, kGwSbo);
+                const uint64_t dbh = smem_desc(b_hi + koff, kGwLbo, kGwSbo), dbl = smem_desc(b_lo + koff, kGwLbo, kGwSbo);
+                tc_mma_tf32(tmem_base, dah, dbh, idesc, (q > 0 || ks > 0) ? 1u : 0u);
+                tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
+                tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+            }
+            tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+        }
+        if (ok && n_chunks > 0) tc_commit(&done_bar);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tmem_cols);
+    if (threadIdx.x == 0 && failed_flag) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 // Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
@@ -362,6 +533,40 @@ int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const
     if (p->d.tile == 2) return launch_tc<2>(p, SF, W, inv, pack, O, B, G, st);
     set_error("internal: tensor-core forward asked for an unsupported tile edge");
     return CGB200_ERR_UNSUPPORTED;
+}
+
+
+// Weight gradient on the tensor cores: tile edge 4, full product, where the forward's tables exist.  Same default
+// threshold as the forward (16 output channels); CGB200_TC_GW=0 / 1 overrides it.
+bool tc_gw_wanted(const cgb200_plan* p) {
+    if (!p->tc_ok || p->d.tile != 4 || p->tc_gw_tiles.empty()) return false;
+    if (const char* env = getenv("CGB200_TC_GW")) return env[0] == '1';
+    return p->max_tau_out >= 16;
+}
+
+int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, int G, cudaStream_t st) {
+    constexpr int T = 4;
+    int n_max = 16;
+    for (int v : p->tc_npad) n_max = std::max(n_max, v);
+    const int n_tiles = (int)p->tc_gw_tiles.size() / 2;
+    if (n_tiles == 0) return CGB200_OK;
+    const size_t stage_bytes = (size_t)2 * 16 * kGwSbo + (size_t)2 * (n_max / 8) * kGwSbo;
+    const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
+    int n_stages = (int)std::min<size_t>(kTcMaxStages, (226 * 1024 - cbuf_bytes) / stage_bytes);
+    if (const char* env = getenv("CGB200_TC_STAGES")) n_stages = std::min(n_stages, std::max(1, atoi(env)));
+    if (n_stages < 2) {
+        set_error("tensor-core weight gradient: pipeline stages do not fit in shared memory");
+        return CGB200_ERR_UNSUPPORTED;
+    }
+    const size_t smem = n_stages * stage_bytes + cbuf_bytes;
+    auto kern = fused_gw_tc_kernel<T>;
+    CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_begin(K_GW_TC, st);
+    kern<<<n_tiles, 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv, gW, G, n_max, p->max_n,
+                                                         p->d_status, n_stages);
+    launch_end(K_GW_TC, st);
+    CGB_CUDA(cudaGetLastError());
+    return CGB200_OK;
 }
 
 }  // namespace cgb200

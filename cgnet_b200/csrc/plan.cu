@@ -30,7 +30,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_product_bwd", "fn_stats", "wmm_fwd",
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
-                                            "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor"};
+                                            "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;
@@ -431,6 +431,17 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         if ((rc = upload(p, p->tc_npad, &p->d_tc_npad))) return rc;
         if ((rc = upload(p, p->tc_pack_off, &p->d_tc_pack_off))) return rc;
         if ((rc = upload(p, p->tc_tiles, &p->d_tc_tiles))) return rc;
+        if (T == 4) {   // weight gradient: blocks of four cells, degrees with the longest contraction (2l+1) first
+            for (int l = L1 - 1; l >= 0; --l) {
+                if (p->tO[l] == 0) continue;
+                const int ncell = p->cell_begin[l + 1] - p->cell_begin[l];
+                for (int c0 = 0; c0 < ncell; c0 += 4) {
+                    p->tc_gw_tiles.push_back(l);
+                    p->tc_gw_tiles.push_back(c0);
+                }
+            }
+            if ((rc = upload(p, p->tc_gw_tiles, &p->d_tc_gw_tiles))) return rc;
+        }
     }
 
     // which triples use fragment l as first / second operand (for the gather-style input gradient)

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import assert_fragments_close, make_case, oracle_layer
+from helpers import assert_fragments_close, assert_weights_close, make_case, oracle_layer
 
 pytestmark = pytest.mark.gpu
 
@@ -65,4 +65,51 @@ def test_tensor_core_forward_is_deterministic():
     plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], torch.device("cuda", 0))
     a, _ = _forward(plan, case, True, False, tc=True)
     b, _ = _forward(plan, case, True, False, tc=True)
+    assert np.array_equal(a, b)
+
+
+def _weight_gradient(plan, case, bn, tc):
+    from cgnet_b200 import _lib
+    dev = torch.device("cuda", 0)
+    os.environ["CGB200_TC_GW"] = "1" if tc else "0"
+    try:
+        F = torch.tensor(case["F"], device=dev)
+        W = torch.tensor(case["W"], device=dev)
+        gO = torch.tensor(case["gO"], device=dev)
+        stds = torch.tensor(case["stds"], device=dev) if bn else None
+        _, gW = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT if bn else 0, gO)
+        torch.cuda.synchronize()
+        st = ctypes.c_int32(-1)
+        _lib.check(_lib.load().cgb200_plan_status(plan.handle, st), "cgb200_plan_status")
+        assert st.value == 0, "a bounded wait inside the tensor-core kernel ran out"
+        return gW.cpu().numpy()
+    finally:
+        os.environ.pop("CGB200_TC_GW", None)
+
+
+@pytest.mark.parametrize("bn", [False, True])
+@pytest.mark.parametrize("taus,tau_out,B,mode", CASES)
+def test_tensor_core_weight_gradient(taus, tau_out, B, mode, bn):
+    """gW from the tcgen05 weight-gradient kernel (3xTF32, contraction over samples and m in tensor memory) against the
+    oracle's autograd gradient and against the CUDA-core kernel."""
+    from cgnet_b200 import get_plan
+    import cg_oracle as o
+    case = make_case(taus, tau_out, B, mode, seed=53)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
+    if plan.tile != 4:
+        pytest.skip(f"tile edge {plan.tile}: the tensor-core weight gradient is built for 4")
+    t_ff, _ = o.tau_ff_and_offsets(case["lmax"], taus, case["llls"])
+    _, _, gW_want, _ = oracle_layer(case, bn, False, cnt=2.0)
+    gW_tc = _weight_gradient(plan, case, bn, tc=True)
+    assert_weights_close(gW_tc, gW_want, t_ff, tau_out, "gW (tensor-core) vs oracle")
+    gW_cc = _weight_gradient(plan, case, bn, tc=False)
+    assert_weights_close(gW_tc, gW_cc, t_ff, tau_out, "gW (tensor-core) vs CUDA-core kernel")
+
+
+def test_tensor_core_weight_gradient_is_deterministic():
+    from cgnet_b200 import get_plan
+    case = make_case([8] * 5, [16] * 5, 70, "default", seed=54)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], torch.device("cuda", 0))
+    a = _weight_gradient(plan, case, True, tc=True)
+    b = _weight_gradient(plan, case, True, tc=True)
     assert np.array_equal(a, b)
