@@ -131,7 +131,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // Kernel identifiers for launch accounting and the optional per-kernel CUDA-event timing (cgb200_timing_*).
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
-    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_COUNT
+    K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_GF_TC, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.
@@ -178,6 +178,9 @@ struct cgb200_plan;
 namespace cgb200 {
 bool tc_wanted(const cgb200_plan* p);
 bool tc_gw_wanted(const cgb200_plan* p);
+bool tc_gf_wanted(const cgb200_plan* p);
+int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* SG, const float2* W, const float* inv, float2* out,
+                 int64_t part_stride, int B, int G, cudaStream_t st);
 int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, int G, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
 int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
@@ -412,6 +415,66 @@ __device__ __forceinline__ int find_degree(const int64_t* __restrict__ cum, int 
         if (cum[mid] <= e) lo = mid; else hi = mid;
     }
     return lo;
+}
+
+// ---- pieces of the fused input-gradient kernels (CUDA-core and tensor-core variant) ----------------------------------
+// Work split inside a block.  A phase ends at a barrier, so it lasts as long as its busiest warp.  With 2l+1 = 21 m's or
+// rows on 16 warps whole units would leave a third of the warp-time idle; both phases therefore use half units:
+//   phase 1  unit = (m, half of the tile's NH entries), all of about equal cost, dealt round-robin;
+//   phase 2  unit = (row, first ceil(T/2) or last floor(T/2) owned channels); their cost follows the row's band
+//            length, and the plan holds a longest-processing-time assignment of the 2(2l+1) units of every owned
+//            degree to the 16 warps (PlanDev-independent table `owner`, 2 l^2 + u for unit u of degree l).
+template <int T, bool DW>
+struct GfShape {
+    static constexpr int NH = DW ? T : T * T;
+    static constexpr int NHP = (NH + 1) & ~1;                   // row pitch of the staged weights: 16-byte rows
+    static constexpr int KA = NH >= 4 ? ((NH / 2) & ~1) : 0;    // entries of phase 1's first half (even), 0: no split
+    static constexpr int AH = (T + 1) / 2;                      // owned channels of phase 2's heavy unit
+    static constexpr int AL = T - AH;                           // ... of its light unit (0 for T = 1: no split)
+};
+
+// phase 2 unit: owned channels A0 .. A0+AN of row r gather their band from the H tiles of the chunk
+template <int T, bool DW, bool FIRST, int A0, int AN>
+__device__ __forceinline__ void gf_row_unit(const float2* __restrict__ H, const float2* __restrict__ fo,
+                                            const float* __restrict__ band, float2* __restrict__ acc, int r, int lt, int nt,
+                                            int l, int lo_, int l2, int n2, int mc0, int mcn, int lane) {
+    constexpr int NH = DW ? T : T * T;
+    float2 x[AN];
+#pragma unroll
+    for (int a = 0; a < AN; ++a) x[a] = make_float2(0.f, 0.f);
+    const int mt = r - lt;
+    // m = m_t + u with u = m of the other operand's element, |u| <= lo_, m inside [-l, l] and inside the chunk
+    const int mlo = max(max(-l, mc0 - l), mt - lo_), mhi = min(min(l, mc0 + mcn - 1 - l), mt + lo_);
+    for (int m = mlo; m <= mhi; ++m) {
+        const int u = m - mt;
+        const float cg = band[(m + l) * n2 + (FIRST ? u : mt) + l2];   // band entry [m + l][m2 + l2]
+        const float2* ph = H + (size_t)(m + l - mc0) * NH * 32 + lane;
+        const float2* pf = fo + (size_t)(u + lo_) * T * 32 + lane;
+        if constexpr (DW) {
+#pragma unroll
+            for (int a = 0; a < AN; ++a) {
+                const float2 f = pf[(A0 + a) * 32];
+                cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), ph[(A0 + a) * 32]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < T; ++c) {
+                float2 f = pf[c * 32];
+                f.x *= cg;
+                f.y *= cg;
+#pragma unroll
+                for (int a = 0; a < AN; ++a) cfma_conj(x[a], f, ph[(FIRST ? (A0 + a) * T + c : c * T + A0 + a) * 32]);
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < AN; ++a) {
+        float2* pa = acc + ((size_t)(A0 + a) * nt + r) * 32 + lane;
+        float2 cur = *pa;
+        cur.x += x[a].x;
+        cur.y += x[a].y;
+        *pa = cur;
+    }
 }
 
 }  // namespace cgb200

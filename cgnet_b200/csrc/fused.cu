@@ -500,21 +500,6 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
 // in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
 
-// Work split inside a block.  A phase ends at a barrier, so it lasts as long as its busiest warp.  With 2l+1 = 21 m's or
-// rows on 16 warps whole units would leave a third of the warp-time idle; both phases therefore use half units:
-//   phase 1  unit = (m, half of the tile's NH entries), all of about equal cost, dealt round-robin;
-//   phase 2  unit = (row, first ceil(T/2) or last floor(T/2) owned channels); their cost follows the row's band
-//            length, and the plan holds a longest-processing-time assignment of the 2(2l+1) units of every owned
-//            degree to the 16 warps (PlanDev-independent table `owner`, 2 l^2 + u for unit u of degree l).
-template <int T, bool DW>
-struct GfShape {
-    static constexpr int NH = DW ? T : T * T;
-    static constexpr int NHP = (NH + 1) & ~1;                   // row pitch of the staged weights: 16-byte rows
-    static constexpr int KA = NH >= 4 ? ((NH / 2) & ~1) : 0;    // entries of phase 1's first half (even), 0: no split
-    static constexpr int AH = (T + 1) / 2;                      // owned channels of phase 2's heavy unit
-    static constexpr int AL = T - AH;                           // ... of its light unit (0 for T = 1: no split)
-};
-
 // phase 1 unit: H[m][K0 .. K0+KN) = sum_to wt[to][k] * gO[to, m]
 template <int T, int NH, int NHP, int K0, int KN>
 __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const float2* __restrict__ wt, float2* __restrict__ h,
@@ -547,50 +532,6 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
     }
 #pragma unroll
     for (int k = 0; k < KN; ++k) h[(K0 + k) * 32] = gt[k];
-}
-
-// phase 2 unit: owned channels A0 .. A0+AN of row r gather their band from the H tiles of the chunk
-template <int T, bool DW, bool FIRST, int A0, int AN>
-__device__ __forceinline__ void gf_row_unit(const float2* __restrict__ H, const float2* __restrict__ fo,
-                                            const float* __restrict__ band, float2* __restrict__ acc, int r, int lt, int nt,
-                                            int l, int lo_, int l2, int n2, int mc0, int mcn, int lane) {
-    constexpr int NH = DW ? T : T * T;
-    float2 x[AN];
-#pragma unroll
-    for (int a = 0; a < AN; ++a) x[a] = make_float2(0.f, 0.f);
-    const int mt = r - lt;
-    // m = m_t + u with u = m of the other operand's element, |u| <= lo_, m inside [-l, l] and inside the chunk
-    const int mlo = max(max(-l, mc0 - l), mt - lo_), mhi = min(min(l, mc0 + mcn - 1 - l), mt + lo_);
-    for (int m = mlo; m <= mhi; ++m) {
-        const int u = m - mt;
-        const float cg = band[(m + l) * n2 + (FIRST ? u : mt) + l2];   // band entry [m + l][m2 + l2]
-        const float2* ph = H + (size_t)(m + l - mc0) * NH * 32 + lane;
-        const float2* pf = fo + (size_t)(u + lo_) * T * 32 + lane;
-        if constexpr (DW) {
-#pragma unroll
-            for (int a = 0; a < AN; ++a) {
-                const float2 f = pf[(A0 + a) * 32];
-                cfma_conj(x[a], make_float2(f.x * cg, f.y * cg), ph[(A0 + a) * 32]);
-            }
-        } else {
-#pragma unroll
-            for (int c = 0; c < T; ++c) {
-                float2 f = pf[c * 32];
-                f.x *= cg;
-                f.y *= cg;
-#pragma unroll
-                for (int a = 0; a < AN; ++a) cfma_conj(x[a], f, ph[(FIRST ? (A0 + a) * T + c : c * T + A0 + a) * 32]);
-            }
-        }
-    }
-#pragma unroll
-    for (int a = 0; a < AN; ++a) {
-        float2* pa = acc + ((size_t)(A0 + a) * nt + r) * 32 + lane;
-        float2 cur = *pa;
-        cur.x += x[a].x;
-        cur.y += x[a].y;
-        *pa = cur;
-    }
 }
 
 template <int T, bool DW>
@@ -1040,36 +981,41 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         const int lv = ws.gf_level;
         const int nblk = (int)p->gf2_blocks[lv].size() / 4;
         const bool split = p->gf2_max_parts[lv] > 1;
-        const int NHh = p->d.depthwise ? T : T * T;
-        const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
-        const int max_to = std::max(p->max_tau_out, 1);
-        const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
-                             2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
-        const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
-        if (fixed + per_m > 227 * 1024) {
-            set_error("lmax or tau_out too large for the fused input-gradient kernel");
-            return CGB200_ERR_UNSUPPORTED;
-        }
-        const size_t budget = 227 * 1024;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
-        const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
-        const size_t smem = fixed + (size_t)Mc * per_m;
         const int64_t part_stride = split ? (int64_t)B * p->d.n_F : 0;
-        launch_begin(K_GF, st);
-        CGB_DISPATCH_TILE(T, p->d.depthwise, {
-            auto kern = fused_gf_kernel<TT, DD>;
-            if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            const int nwarps = kGfWarps;
-            kern<<<dim3(nblk, G), nwarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, split ? ws.gf_part : (float2*)gF, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
-        });
-        if (split) {
+        float2* gf_out = split ? ws.gf_part : (float2*)gF;
+        if (tc_gf_wanted(p)) {
+            const int rc2 = launch_gf_tc(p, lv, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, G, st);
+            if (rc2) return rc2;
+        } else {
+            const int NHh = p->d.depthwise ? T : T * T;
+            const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
+            const int max_to = std::max(p->max_tau_out, 1);
+            const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
+                                 2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
+            const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
+            if (fixed + per_m > 227 * 1024) {
+                set_error("lmax or tau_out too large for the fused input-gradient kernel");
+                return CGB200_ERR_UNSUPPORTED;
+            }
+            const size_t budget = 227 * 1024;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
+            const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
+            const size_t smem = fixed + (size_t)Mc * per_m;
+            launch_begin(K_GF, st);
+            CGB_DISPATCH_TILE(T, p->d.depthwise, {
+                auto kern = fused_gf_kernel<TT, DD>;
+                if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+            });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());
+        }
+        if (split) {
             const int gx = (int)((p->d.n_F + 255) / 256);
             launch_begin(K_GF_REDUCE, st);
             gf_reduce_kernel<<<dim3(gx, (unsigned)std::min<int64_t>(B, 65535)), 256, 0, st>>>(p->d, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF, (int)B);
+            launch_end(K_GF_REDUCE, st);
+            CGB_CUDA(cudaGetLastError());
         }
-        launch_end(K_GF, st);
-        CGB_CUDA(cudaGetLastError());
         return CGB200_OK;
     };
 

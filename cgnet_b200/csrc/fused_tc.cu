@@ -22,6 +22,7 @@
 //     writes O.
 // Every wait is bounded: a wait that runs out sets a flag in shared memory and a status word in global memory, all
 // roles then skip to the end, tensor memory is released and the kernel returns.
+#include <cuda_pipeline.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -482,6 +483,297 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// The input gradient with its first phase on the tensor cores.
+//
+// Same block structure, entry walk, staging and phase 2 as fused_gf_kernel (fused.cu); what changes is phase 1, the
+// gFF tile  H[(m, b), k] = sum_to conj(W[to, k])/std_k * gO[b, to, m]:  it is the real GEMM
+//   D[(m, b), (k, re|im)] = sum_{(to, re|im)} G[(m, b), (to, re|im)] * Bw[(k, re|im), (to, re|im)]
+// with 128 rows = four m x 32 samples per MMA tile and the 2T^2 = 32 real columns of one cell.  Per (row tile, chunk
+// of 16 output channels) the 16 warps write the gO values of their lanes' samples, split into TF32 high / low parts,
+// into one of two shared-memory A buffers (a lane owns a row: 16-byte stores, no conflicts); after a block barrier one
+// thread issues the 4 x 3 tcgen05.mma (3xTF32) of the chunk into the tile's 32 tensor-memory columns and commits them
+// to the buffer's "empty" barrier, so the next chunk is staged while this one is multiplied.  The weights of the entry
+// (real form of conj(W)/std, high / low parts) are the B operand, written once per entry.  When the entry's last MMA has
+// completed, the warps move H from tensor memory to the shared-memory transit buffer (warp w can read the rows
+// with m % 4 == w % 4) in chunks of Mc m's and run phase 2 on every chunk exactly as the CUDA-core kernel does.
+// All waits are bounded; a wait that runs out sets the plan's status word and the block finishes without hanging.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool mbar_wait_checked(uint64_t* bar, uint32_t parity, volatile int* failed) {
+    if (*failed) return false;
+    return mbar_wait(bar, parity, failed);
+}
+
+template <int T>
+__global__ void __launch_bounds__(kGfWarps * 32)
+fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
+                   const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
+                   const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
+                   float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int Kb, int band_floats,
+                   uint32_t tmem_cols, int* __restrict__ status) {
+    using S = GfShape<T, false>;
+    constexpr int NH = T * T;                       // complex entries of a tile
+    constexpr int NR = 2 * NH;                      // real columns of D = rows of the B operand
+    static_assert(NR == 32, "built for tile edge 4");
+    constexpr uint32_t kABytes = 128 * 32 * 4;      // high (or low) part of one A chunk: 128 rows x 32 floats
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t empty_bar[2], done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed_flag;
+
+    const int lt = blocks[4 * blockIdx.x], q = blocks[4 * blockIdx.x + 1];
+    const int part = blocks[4 * blockIdx.x + 2], parts = blocks[4 * blockIdx.x + 3];
+    const int nt = 2 * lt + 1, t_0 = q * T;
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tau_t = P.tF[lt];
+    // shared-memory carve: the two A buffers first (128-byte aligned), then as in the CUDA-core kernel
+    unsigned char* a_st = smem_raw;                                                   // 2 x { high, low }
+    float* b_hi = reinterpret_cast<float*>(a_st + 4 * kABytes);                       // [32][Kb] in MMA order
+    float* b_lo = b_hi + NR * Kb;
+    float2* acc = reinterpret_cast<float2*>(b_lo + NR * Kb);                          // [T][nt][32]
+    float2* fo2 = acc + (size_t)T * max_n * 32;                                       // 2 x [n_o][T][32]
+    float* band2 = reinterpret_cast<float*>(fo2 + (size_t)2 * T * max_n * 32);        // 2 x [n][n2]
+    unsigned short* ulist = reinterpret_cast<unsigned short*>(band2 + 2 * band_floats);
+    float2* H = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(ulist) + ((kGfWarps * 4 * max_n + 15) & ~15));   // [Mc][NH][32]
+    volatile int* failed = &failed_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&empty_bar[0], 1);
+        mbar_init(&empty_bar[1], 1);
+        mbar_init(&done_bar, 1);
+        failed_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_slot, tmem_cols);
+    for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
+    int n_units = 0;   // this warp's phase-2 units, listed once per block
+    for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u)
+        if (owner_tab[2 * lt * lt + u] == warp) {
+            if (lane == 0) ulist[warp * 2 * max_n + n_units] = (unsigned short)u;
+            ++n_units;
+        }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const float2* slabF = SF + (int64_t)g * P.nSF * 32;
+    const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
+
+    auto stage_async = [&](const GfInfo& x, int buf) {
+        const bool fst = x.role == 0;
+        const int xn = 2 * x.l + 1, xn2 = 2 * x.l2 + 1, xno = fst ? xn2 : 2 * x.l1 + 1;
+        const float4* src = reinterpret_cast<const float4*>(slabF + (int64_t)x.fo_off * 32);
+        float4* dstf = reinterpret_cast<float4*>(fo2 + (size_t)buf * T * max_n * 32);
+        for (int i = threadIdx.x; i < xno * T * 16; i += blockDim.x) __pipeline_memcpy_async(dstf + i, src + i, 16);
+        float* dstb = band2 + buf * band_floats;
+        for (int i = threadIdx.x; i < xn * xn2; i += blockDim.x) __pipeline_memcpy_async(dstb + i, P.cg + x.cgoff + i, 4);
+        __pipeline_commit();
+    };
+    // weights of the entry: element i = (to, tile entry) -> conj(W)/std, zero outside the tile or beyond tau_out
+    constexpr int kWtRegs = 2;
+    auto wt_load = [&](const GfInfo& x, int i) -> float2 {
+        const bool fst = x.role == 0;
+        const int t = i / NH, idx = i - t * NH;
+        const int i1 = idx / T, j1 = idx % T;
+        const int a = fst ? i1 : j1, c = fst ? j1 : i1;   // owned / other channel inside their tiles
+        const bool ok = t < x.to_n && (t_0 + a < tau_t) && (x.in0 + c < x.tau_o);
+        const int t1 = fst ? t_0 + a : x.in0 + c, t2 = fst ? x.in0 + c : t_0 + a;
+        const int ch = t1 * x.tau2 + t2;
+        float2 w = make_float2(0.f, 0.f);
+        if (ok) {
+            w = __ldg(W + x.woff + (int64_t)t * x.tff + ch);
+            const float sc = __ldg(inv + x.kglob + ch);
+            w = make_float2(w.x * sc, -w.y * sc);
+        }
+        return w;
+    };
+    const int n_wt = (Kb / 2) * NH;   // every (to < Kb/2, entry): the padding is written as zeros each time
+    auto wt_prefetch = [&](const GfInfo& x, float2 (&reg)[kWtRegs]) {
+#pragma unroll
+        for (int j = 0; j < kWtRegs; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n_wt) reg[j] = wt_load(x, i);
+        }
+    };
+    // B operand in the MMA's K-major core-matrix order: element (row n', column kk) at
+    // (n'/8)*(Kb/4)*32 + (kk/4)*32 + (n'%8)*4 + kk%4 floats; rows (k, re), (k, im), columns (to, re), (to, im)
+    auto b_put = [&](int i, float2 w) {
+        const int t = i / NH, idx = i - t * NH;
+        const int kk = 2 * t;
+        const int r0 = 2 * idx, r1 = r0 + 1;
+        const int o0 = (r0 >> 3) * (Kb / 4) * 32 + (kk >> 2) * 32 + (r0 & 7) * 4 + (kk & 3);
+        const int o1 = (r1 >> 3) * (Kb / 4) * 32 + (kk >> 2) * 32 + (r1 & 7) * 4 + (kk & 3);
+        const float hr = to_tf32(w.x), hi_ = to_tf32(w.y);
+        // H.re = sum wr*gr - wi*gi,  H.im = sum wi*gr + wr*gi
+        *reinterpret_cast<float2*>(b_hi + o0) = make_float2(hr, -hi_);
+        *reinterpret_cast<float2*>(b_hi + o1) = make_float2(hi_, hr);
+        *reinterpret_cast<float2*>(b_lo + o0) = make_float2(w.x - hr, -(w.y - hi_));
+        *reinterpret_cast<float2*>(b_lo + o1) = make_float2(w.y - hi_, w.x - hr);
+    };
+    auto wt_store = [&](const GfInfo& x, const float2 (&reg)[kWtRegs]) {
+#pragma unroll
+        for (int j = 0; j < kWtRegs; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n_wt) b_put(i, reg[j]);
+        }
+        for (int i = threadIdx.x + kWtRegs * blockDim.x; i < n_wt; i += blockDim.x) b_put(i, wt_load(x, i));
+    };
+
+    const int e_end = entry_begin[lt + 1];
+    int e = entry_begin[lt] + part;
+    GfInfo en;
+    float2 wreg[kWtRegs];
+    int buf = 0;
+    int a_step = 0;      // A-buffer uses so far (all threads count alike)
+    int n_entry = 0;     // entries whose MMAs were committed to done_bar: its phase parity
+    bool ok = true;
+    if (e < e_end) {
+        en = entries[e];
+        stage_async(en, 0);
+        wt_prefetch(en, wreg);
+    }
+    const int mq = warp & 3, tq = warp >> 2;   // staging role: m inside the row tile, quarter of the chunk's 16 channels
+    const uint32_t idesc = tc_idesc(128, NR);
+    while (e < e_end) {
+        const bool has_next = e + parts < e_end;
+        GfInfo nxt;
+        if (has_next) nxt = entries[e + parts];
+        const int l = en.l, n = 2 * l + 1, n2 = 2 * en.l2 + 1;
+        const int to_n = en.to_n;
+        const bool first = en.role == 0;
+        const float2* fo = fo2 + (size_t)buf * T * max_n * 32;
+        const float* band = band2 + buf * band_floats;
+        wt_store(en, wreg);          // the previous entry's MMAs are complete (its done barrier was waited for)
+        __pipeline_wait_prior(0);
+        __syncthreads();             // the previous entry's phase 2 is over: H and the idle staging halves are free
+        if (has_next) stage_async(nxt, buf ^ 1);
+        const float2* go = slabG + (int64_t)en.go_off * 32;
+        const int lo_ = first ? en.l2 : en.l1;
+        // ---- phase 1 on the tensor cores ----
+        const int n_tiles = (n + 3) >> 2, n_kc = (2 * to_n + 31) >> 5;
+        const int n_steps = n_tiles * n_kc;
+        // the gO values of step s + 1 are loaded before step s is staged: the global-load latency of a step would
+        // otherwise be paid once per step by all 16 warps together
+        auto load_step = [&](int s_, float2 (&gv)[4]) {
+            const int t = s_ / n_kc, kc = s_ - t * n_kc;
+            const int mi = 4 * t + mq;
+            const float2* gp = go + (((kc * 4 + tq) * n + min(mi, n - 1)) * T) * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                gv[i] = (mi < n && kc * 16 + 4 * tq + i < to_n) ? gp[i * 32] : make_float2(0.f, 0.f);
+        };
+        float2 gv[4], gv_next[4];
+        if (n_steps > 0) load_step(0, gv);
+        for (int s_ = 0; s_ < n_steps; ++s_) {
+            const int t = s_ / n_kc, kc = s_ - t * n_kc;
+            if (s_ + 1 < n_steps) load_step(s_ + 1, gv_next);
+            {
+                const int ab = a_step & 1, use = a_step >> 1;
+                if (use > 0) ok = mbar_wait_checked(&empty_bar[ab], (uint32_t)((use - 1) & 1), failed) && ok;
+                const int mi = 4 * t + mq;
+                if (mi < n) {
+                    const int r = 32 * mq + lane;
+                    float4* row_hi = reinterpret_cast<float4*>(a_st + (size_t)ab * 2 * kABytes) + (size_t)(r >> 3) * 64 + (r & 7);
+                    float4* row_lo = row_hi + kABytes / 16;
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const float2 x0 = gv[2 * h2], x1 = gv[2 * h2 + 1];
+                        float4 h, w;
+                        h.x = to_tf32(x0.x); h.y = to_tf32(x0.y); h.z = to_tf32(x1.x); h.w = to_tf32(x1.y);
+                        w.x = x0.x - h.x; w.y = x0.y - h.y; w.z = x1.x - h.z; w.w = x1.y - h.w;
+                        row_hi[(2 * tq + h2) * 8] = h;
+                        row_lo[(2 * tq + h2) * 8] = w;
+                    }
+                }
+                fence_proxy_async();   // A chunk and (first step of the entry) the B operand become visible to the MMA
+                tc_fence_before();
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    if (ok && !*failed) {
+                        tc_fence_after();
+                        const uint32_t a_hi = smem_u32(a_st + (size_t)ab * 2 * kABytes), a_lo = a_hi + kABytes;
+                        const uint32_t bh = smem_u32(b_hi) + kc * 1024, bl = smem_u32(b_lo) + kc * 1024;
+                        const uint32_t b_sbo = (uint32_t)(Kb / 4) * 128;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t dah = smem_desc(a_hi + ks * 256, 128, 1024), dal = smem_desc(a_lo + ks * 256, 128, 1024);
+                            const uint64_t dbh = smem_desc(bh + ks * 256, 128, b_sbo), dbl = smem_desc(bl + ks * 256, 128, b_sbo);
+                            const uint32_t d = tmem_base + (uint32_t)t * NR;
+                            tc_mma_tf32(d, dah, dbh, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
+                            tc_mma_tf32(d, dal, dbh, idesc, 1u);
+                            tc_mma_tf32(d, dah, dbl, idesc, 1u);
+                        }
+                    }
+                    tc_commit(&empty_bar[ab]);
+                    if (s_ == n_steps - 1) tc_commit(&done_bar);
+                }
+                ++a_step;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) gv[i] = gv_next[i];
+        }
+        if (n_tiles * n_kc > 0) {
+            ok = mbar_wait_checked(&done_bar, (uint32_t)(n_entry & 1), failed) && ok;
+            ++n_entry;   // phases of done_bar completed so far
+        }
+        tc_fence_after();
+        // ---- H from tensor memory to the transit buffer, chunk by chunk, then phase 2 on the chunk ----
+        for (int mc0 = 0; mc0 < n; mc0 += Mc) {
+            const int mcn = min(Mc, n - mc0);
+            if (mc0 > 0) __syncthreads();   // the previous chunk's readers are done with H
+            {
+                // this warp reads the rows with m % 4 == warp % 4; the four warps of a quadrant share its (m, half) pairs
+                int m_first = mc0 + ((mq - mc0) & 3);
+                int pair = 0;
+                for (int mi = m_first; mi < mc0 + mcn; mi += 4)
+                    for (int half = 0; half < 2; ++half, ++pair) {
+                        if ((pair & 3) != tq) continue;   // warp-uniform
+                        uint32_t rr[16];
+                        if (ok && n_tiles * n_kc > 0) {
+                            tmem_ld16(tmem_base + ((uint32_t)(32 * mq) << 16) + (uint32_t)((mi >> 2) * NR + half * 16), rr);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) rr[c] = 0u;
+                        }
+                        float2* h = H + ((size_t)(mi - mc0) * NH + half * 8) * 32 + lane;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) h[c * 32] = make_float2(__uint_as_float(rr[2 * c]), __uint_as_float(rr[2 * c + 1]));
+                    }
+            }
+            tc_fence_before();
+            __syncthreads();
+            if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
+            for (int k = 0; k < n_units; ++k) {
+                const int u = ulist[warp * 2 * max_n + k];
+                const bool heavy = u < nt;
+                const int r = heavy ? u : u - nt;
+                if (heavy) {
+                    if (first) gf_row_unit<T, false, true, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                    else gf_row_unit<T, false, false, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                } else if constexpr (S::AL > 0) {
+                    if (first) gf_row_unit<T, false, true, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                    else gf_row_unit<T, false, false, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
+                }
+            }
+        }
+        en = nxt;
+        e += parts;
+        buf ^= 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tmem_cols);
+    float2* dst = out + (int64_t)part * part_stride;
+    for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) {
+        const int ln = i & 31, rest = i >> 5;
+        const int a = rest / nt, r = rest - a * nt;
+        const int b = g * 32 + ln;
+        if (b < B && t_0 + a < tau_t) dst[(int64_t)b * P.n_F + P.cumF[lt] + (int64_t)(t_0 + a) * nt + r] = acc[i];
+    }
+    if (threadIdx.x == 0 && failed_flag) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 // Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
@@ -565,6 +857,47 @@ int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const
     kern<<<n_tiles, 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv, gW, G, n_max, p->max_n,
                                                          p->d_status, n_stages);
     launch_end(K_GW_TC, st);
+    CGB_CUDA(cudaGetLastError());
+    return CGB200_OK;
+}
+
+// Input gradient with phase 1 on the tensor cores: tile edge 4, full product, 2 lmax + 1 <= 64 (the gFF tile of an entry
+// must fit the 512 columns of tensor memory).  Off unless CGB200_TC_GF=1: measured on B200 it matches but does not beat
+// the CUDA-core kernel (lmax 14, 16 channels, batch 64: 8.5 against 7.5 ms; lmax 10, 64 channels: 62 against 59 ms).
+// Every (row tile, 16-channel chunk) step moves a 32 KB A chunk through one of two shared-memory buffers, so a step
+// lasts half the issue-to-completion latency of its MMAs (about 1 us per step); a deeper ring does not fit beside the
+// phase-2 buffers, and a wider N per step (several cells per MMA) needs more than the 512 columns of tensor memory.
+bool tc_gf_wanted(const cgb200_plan* p) {
+    if (!p->tc_ok || p->d.tile != 4 || p->max_n > 64) return false;
+    if (const char* env = getenv("CGB200_TC_GF")) return env[0] == '1';
+    return false;
+}
+
+int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* SG, const float2* W, const float* inv, float2* out,
+                 int64_t part_stride, int B, int G, cudaStream_t st) {
+    constexpr int T = 4, NH = 16;
+    const int nblk = (int)p->gf2_blocks[lv].size() / 4;
+    if (nblk == 0) return CGB200_OK;
+    const int Kb = ((2 * std::max(p->max_tau_out, 1) + 31) / 32) * 32;
+    const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
+    const size_t fixed = (size_t)4 * 128 * 32 * 4 + (size_t)2 * 32 * Kb * 4 + (size_t)3 * T * p->max_n * 32 * sizeof(float2) +
+                         2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
+    const size_t per_m = (size_t)NH * 32 * sizeof(float2);
+    const size_t budget = 227 * 1024;
+    if (fixed + 4 * per_m > budget) {
+        set_error("tensor-core input gradient: staging areas do not fit in shared memory");
+        return CGB200_ERR_UNSUPPORTED;
+    }
+    const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
+    const size_t smem = fixed + (size_t)Mc * per_m;
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(32 * ((p->max_n + 3) / 4))) cols <<= 1;
+    auto kern = fused_gf_tc_kernel<T>;
+    CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    launch_begin(K_GF_TC, st);
+    kern<<<dim3(nblk, G), kGfWarps * 32, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, SF, SG, W, inv,
+                                                     out, part_stride, B, Mc, p->max_n, Kb, band_floats, cols, p->d_status);
+    launch_end(K_GF_TC, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;
 }

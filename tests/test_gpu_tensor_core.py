@@ -113,3 +113,48 @@ def test_tensor_core_weight_gradient_is_deterministic():
     a = _weight_gradient(plan, case, True, tc=True)
     b = _weight_gradient(plan, case, True, tc=True)
     assert np.array_equal(a, b)
+
+
+def _input_gradient(plan, case, bn, tc):
+    from cgnet_b200 import _lib
+    dev = torch.device("cuda", 0)
+    os.environ["CGB200_TC_GF"] = "1" if tc else "0"
+    try:
+        F = torch.tensor(case["F"], device=dev)
+        W = torch.tensor(case["W"], device=dev)
+        gO = torch.tensor(case["gO"], device=dev)
+        stds = torch.tensor(case["stds"], device=dev) if bn else None
+        gF, _ = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT if bn else 0, gO)
+        torch.cuda.synchronize()
+        st = ctypes.c_int32(-1)
+        _lib.check(_lib.load().cgb200_plan_status(plan.handle, st), "cgb200_plan_status")
+        assert st.value == 0, "a bounded wait inside the tensor-core kernel ran out"
+        return gF.cpu().numpy()
+    finally:
+        os.environ.pop("CGB200_TC_GF", None)
+
+
+@pytest.mark.parametrize("bn", [False, True])
+@pytest.mark.parametrize("taus,tau_out,B,mode", CASES + [([4] * 15, [20] * 15, 33, "mst"), ([8] * 4, [40] * 4, 9, "default")])
+def test_tensor_core_input_gradient(taus, tau_out, B, mode, bn):
+    """gF from the input-gradient kernel whose gFF tiles come from tcgen05 MMAs (3xTF32, accumulator in tensor memory,
+    moved to shared memory for the CG contraction) against the oracle's autograd gradient and the CUDA-core kernel."""
+    from cgnet_b200 import get_plan
+    case = make_case(taus, tau_out, B, mode, seed=55)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
+    if plan.tile != 4:
+        pytest.skip(f"tile edge {plan.tile}: the tensor-core input gradient is built for 4")
+    _, gF_want, _, _ = oracle_layer(case, bn, False, cnt=2.0)
+    gF_tc = _input_gradient(plan, case, bn, tc=True)
+    assert_fragments_close(gF_tc, gF_want, taus, "gF (tensor-core phase 1) vs oracle")
+    gF_cc = _input_gradient(plan, case, bn, tc=False)
+    assert_fragments_close(gF_tc, gF_cc, taus, "gF (tensor-core phase 1) vs CUDA-core kernel")
+
+
+def test_tensor_core_input_gradient_is_deterministic():
+    from cgnet_b200 import get_plan
+    case = make_case([8] * 5, [16] * 5, 70, "default", seed=56)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], torch.device("cuda", 0))
+    a = _input_gradient(plan, case, True, tc=True)
+    b = _input_gradient(plan, case, True, tc=True)
+    assert np.array_equal(a, b)

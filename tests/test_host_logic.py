@@ -67,7 +67,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.SIGNATURES), "ctypes signature table and header disagree"
     loaded = _lib.load()
     assert loaded.cgb200_version() >= 100 and loaded.cgb200_max_lmax() == 511
-    assert loaded.cgb200_kernel_count() == 17
+    assert loaded.cgb200_kernel_count() == 18
     assert loaded.cgb200_kernel_name(9) == b"fused_fwd"
 
 
