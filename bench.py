@@ -41,6 +41,9 @@ WORKLOADS = {
                           describe="5-layer CGNet lmax=10 tau=5 batch=100 fwd+bwd (BASELINE configs[1])"),
     "layer_lmax5": dict(lmax=5, tau_in=8, tau=8, layers=1, batch=32, hidden=256, classes=10,
                         describe="single CG layer lmax=5 tau=8 batch=32 fwd+bwd (BASELINE configs[0] shape)"),
+    "cgnet2_lmax14_tau16": dict(lmax=14, tau_in=16, tau=16, layers=2, batch=64, hidden=256, classes=10,
+                                describe="2-layer CGNet lmax=14 tau=16 batch=64 fwd+bwd (layer shape of BASELINE configs[2]; "
+                                         "tensor-core forward and weight gradient)"),
     # single fused layer, inference forward only (BASELINE configs[4], the sweep's points that fit a quick run)
     "fused_layer_lmax10_tau16": dict(kind="layer_infer", lmax=10, tau_in=16, tau=16, layers=1, batch=256, classes=10, hidden=0,
                                      describe="one fused CG layer lmax=10 tau=16 batch=256, inference forward (BASELINE configs[4])"),

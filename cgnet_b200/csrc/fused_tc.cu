@@ -399,7 +399,7 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
                 __syncwarp();
                 for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
                 __syncwarp();
-                gen_slab<T, false>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+                gen_slab<T, false, true>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
 #pragma unroll
                 for (int kk = 0; kk < MR; ++kk) {
                     const float x = (kk & 1) ? v[kk >> 1].y : v[kk >> 1].x;
