@@ -1035,11 +1035,9 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     CGB_CUDA(cudaEventRecord(p->ev_fork, st));
     CGB_CUDA(cudaStreamWaitEvent(p->side_stream, p->ev_fork, 0));
     // from here on the join is enqueued whatever the launches return (a capturing stream must be joined)
-    static const bool gw_first = [] { const char* e = getenv("CGB200_BWD_ORDER"); return e && e[0] == 'w'; }();
-    int rc_w = CGB200_OK, rc_f = CGB200_OK;
-    if (gw_first) rc_w = enqueue_gw(p->side_stream);
-    rc_f = enqueue_gf();
-    if (!gw_first) rc_w = enqueue_gw(p->side_stream);
+    // the input gradient is enqueued first: its large blocks take the SMs, the weight gradient's small ones fill the tail
+    const int rc_f = enqueue_gf();
+    const int rc_w = enqueue_gw(p->side_stream);
     CGB_CUDA(cudaEventRecord(p->ev_join, p->side_stream));
     CGB_CUDA(cudaStreamWaitEvent(st, p->ev_join, 0));
     return rc_f ? rc_f : rc_w;
