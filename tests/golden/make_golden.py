@@ -2,7 +2,7 @@
 
     python tests/golden/make_golden.py [--ref /path/to/CGNet-checkout]
 
-Needs a checkout of zlin7/CGNet (default /root/reference) and its ``ClebschGordan`` C++ module built by
+Needs a checkout of zlin7/CGNet (the --ref argument) and its ``ClebschGordan`` C++ module built by
 ``make -C oracle ref``.  The fixtures it writes (``*.npz``, a few hundred kB in total) are committed, so the test-suite
 itself never needs the checkout.
 
