@@ -251,3 +251,32 @@ def test_input_gradient_is_optional():
     O = layer(F, straight_output=True)          # F does not require grad
     (O * gO).sum().backward()
     assert torch.equal(layer.bnWMM.W.grad, gW_full)
+
+
+def test_layer_runs_inside_a_cuda_graph():
+    """Forward and backward captured into one CUDA graph (the backward forks its weight gradient onto a second stream
+    and joins it back inside the call, which a capture must be able to follow) and replayed on new inputs."""
+    from cgnet_b200 import _lib
+    case = make_case([5] * 6, [5] * 6, 40, "default", seed=16)
+    other = make_case([5] * 6, [5] * 6, 40, "default", seed=17)
+    plan = plan_for(case)
+    F, W, gO, stds = t(case["F"]), t(case["W"]), t(case["gO"]), t(case["stds"])
+    flags = _lib.FN_PRESENT
+    plan.layer_fwd(F, W, stds, 1.0, 1e-5, flags)          # first calls outside the capture: lazy set-up happens here
+    plan.layer_bwd(F, W, stds, 1e-5, flags, gO)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        O = plan.layer_fwd(F, W, stds, 1.0, 1e-5, flags)
+        gF, gW = plan.layer_bwd(F, W, stds, 1e-5, flags, gO)
+    for src in (other, case):
+        F.copy_(t(src["F"]))
+        gO.copy_(t(src["gO"]))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [x.cpu().numpy().copy() for x in (O, gF, gW)]
+        O2 = plan.layer_fwd(F, W, stds, 1.0, 1e-5, flags)
+        gF2, gW2 = plan.layer_bwd(F, W, stds, 1e-5, flags, gO)
+        torch.cuda.synchronize()
+        for a, b in zip(got, (O2, gF2, gW2)):
+            assert np.array_equal(a, b.cpu().numpy())
