@@ -418,12 +418,11 @@ __device__ __forceinline__ int find_degree(const int64_t* __restrict__ cum, int 
 }
 
 // ---- pieces of the fused input-gradient kernels (CUDA-core and tensor-core variant) ----------------------------------
-// Work split inside a block.  A phase ends at a barrier, so it lasts as long as its busiest warp.  With 2l+1 = 21 m's or
-// rows on 16 warps whole units would leave a third of the warp-time idle; both phases therefore use half units:
+// Work split inside a block.  A phase ends at a barrier, so it lasts as long as its busiest warp:
 //   phase 1  unit = (m, half of the tile's NH entries), all of about equal cost, dealt round-robin;
-//   phase 2  unit = (row, first ceil(T/2) or last floor(T/2) owned channels); their cost follows the row's band
-//            length, and the plan holds a longest-processing-time assignment of the 2(2l+1) units of every owned
-//            degree to the 16 warps (PlanDev-independent table `owner`, 2 l^2 + u for unit u of degree l).
+//   phase 2  unit = a row of the owned fragment (or, optionally, its first ceil(T/2) / last floor(T/2) owned channels);
+//            a unit's cost follows the row's band length, and the plan holds a longest-processing-time assignment of
+//            every owned degree's units to the 16 warps (table `owner`, index 2 l^2 + u for unit u of degree l).
 template <int T, bool DW>
 struct GfShape {
     static constexpr int NH = DW ? T : T * T;
@@ -475,6 +474,33 @@ __device__ __forceinline__ void gf_row_unit(const float2* __restrict__ H, const 
         cur.y += x[a].y;
         *pa = cur;
     }
+}
+
+// One phase-2 unit of a block.  Without the split a unit is a whole row (all T owned channels); with it, units
+// 0 .. nt-1 carry the first ceil(T/2) owned channels of their row and units nt .. 2 nt-1 the rest.  Measured on B200 the
+// whole-row units win at every shape tried (tile edges 3, 4, 5; 3 to 32 channels) by 2-8 %; rows in groups of two or
+// three, which load a gFF tile element once for several rows, were 10-80 % slower (fewer, longer units on 16 warps).
+template <int T, bool DW, bool SPLIT>
+__device__ __forceinline__ void gf_phase2_unit(int u, bool first, const float2* __restrict__ H, const float2* __restrict__ fo,
+                                               const float* __restrict__ band, float2* __restrict__ acc, int lt, int nt, int l,
+                                               int lo_, int l2, int n2, int mc0, int mcn, int lane) {
+    using S = GfShape<T, DW>;
+    constexpr bool kSplit = SPLIT && S::AL > 0;
+    constexpr int AH = kSplit ? S::AH : T;
+    const bool heavy = u < nt;
+    const int r = heavy ? u : u - nt;
+    if (heavy) {
+        if (first) gf_row_unit<T, DW, true, 0, AH>(H, fo, band, acc, r, lt, nt, l, lo_, l2, n2, mc0, mcn, lane);
+        else gf_row_unit<T, DW, false, 0, AH>(H, fo, band, acc, r, lt, nt, l, lo_, l2, n2, mc0, mcn, lane);
+    } else if constexpr (kSplit) {
+        if (first) gf_row_unit<T, DW, true, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, l2, n2, mc0, mcn, lane);
+        else gf_row_unit<T, DW, false, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, l2, n2, mc0, mcn, lane);
+    }
+}
+// number of phase-2 units of a block that owns a fragment with nt rows
+template <int T, bool DW, bool SPLIT>
+__device__ __forceinline__ int gf_phase2_units(int nt) {
+    return ((SPLIT && GfShape<T, DW>::AL > 0) ? 2 : 1) * nt;
 }
 
 }  // namespace cgb200

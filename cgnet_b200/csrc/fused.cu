@@ -534,7 +534,7 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
     for (int k = 0; k < KN; ++k) h[(K0 + k) * 32] = gt[k];
 }
 
-template <int T, bool DW>
+template <int T, bool DW, bool SPLIT>
 __global__ void __launch_bounds__(kGfWarps * kWarp)
 fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
                 const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
@@ -558,7 +558,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     float2* H = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(ulist) + ((kGfWarps * 4 * max_n + 15) & ~15));   // [Mc][NH][32]
     for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
     int n_units = 0;   // this warp's phase-2 units, listed once per block (every lane keeps the same count)
-    for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u)
+    for (int u = 0; u < gf_phase2_units<T, DW, SPLIT>(nt); ++u)
         if (owner_tab[2 * lt * lt + u] == warp) {
             if (lane == 0) ulist[warp * 2 * max_n + n_units] = (unsigned short)u;
             ++n_units;
@@ -659,15 +659,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
             if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
             for (int k = 0; k < n_units; ++k) {
                 const int u = ulist[warp * 2 * max_n + k];
-                const bool heavy = u < nt;
-                const int r = heavy ? u : u - nt;
-                if (heavy) {
-                    if (first) gf_row_unit<T, DW, true, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                    else gf_row_unit<T, DW, false, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                } else if constexpr (S::AL > 0) {
-                    if (first) gf_row_unit<T, DW, true, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                    else gf_row_unit<T, DW, false, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                }
+                gf_phase2_unit<T, DW, SPLIT>(u, first, H, fo, band, acc, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
             }
         }
         en = nxt;
@@ -732,6 +724,14 @@ int gw_slices(const cgb200_plan* p, int64_t G) {
     s = std::min<int64_t>(s, G);
     while (s > 1 && s * p->d.w_len * (int64_t)sizeof(float2) > (256ll << 20)) --s;
     return (int)std::max<int64_t>(s, 1);
+}
+
+// Phase-2 units of the input-gradient kernel: whole rows (default, faster at every shape measured) or rows split into
+// two channel groups (CGB200_GF_SPLIT=1).  The plan holds a warp assignment for both.
+bool gf_split(const cgb200_plan* p) {
+    (void)p;
+    const char* env = getenv("CGB200_GF_SPLIT");
+    return env && env[0] == '1';
 }
 
 // Splitting level of the input-gradient kernel: the coarsest one that gives every SM about two blocks.
@@ -1001,10 +1001,13 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
             const size_t smem = fixed + (size_t)Mc * per_m;
             launch_begin(K_GF, st);
+            // phase-2 shape: whole rows, or the owned channels of a row split over two units (see gf_split)
+            const bool split_units = gf_split(p);
+            const unsigned char* owner = p->d_gf_owner + (size_t)(split_units ? 1 : 0) * 2 * (p->d.lmax + 1) * (p->d.lmax + 1);
             CGB_DISPATCH_TILE(T, p->d.depthwise, {
-                auto kern = fused_gf_kernel<TT, DD>;
+                auto kern = split_units ? fused_gf_kernel<TT, DD, true> : fused_gf_kernel<TT, DD, false>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+                kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
             });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());

@@ -547,7 +547,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
     if (warp == 0) tmem_alloc(&tmem_base_slot, tmem_cols);
     for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
     int n_units = 0;   // this warp's phase-2 units, listed once per block
-    for (int u = 0; u < (S::AL > 0 ? 2 : 1) * nt; ++u)
+    for (int u = 0; u < gf_phase2_units<T, false, false>(nt); ++u)
         if (owner_tab[2 * lt * lt + u] == warp) {
             if (lane == 0) ulist[warp * 2 * max_n + n_units] = (unsigned short)u;
             ++n_units;
@@ -745,15 +745,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
             if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
             for (int k = 0; k < n_units; ++k) {
                 const int u = ulist[warp * 2 * max_n + k];
-                const bool heavy = u < nt;
-                const int r = heavy ? u : u - nt;
-                if (heavy) {
-                    if (first) gf_row_unit<T, false, true, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                    else gf_row_unit<T, false, false, 0, S::AH>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                } else if constexpr (S::AL > 0) {
-                    if (first) gf_row_unit<T, false, true, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                    else gf_row_unit<T, false, false, S::AH, S::AL>(H, fo, band, acc, r, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-                }
+                gf_phase2_unit<T, false, false>(u, first, H, fo, band, acc, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
             }
         }
         en = nxt;

@@ -580,13 +580,16 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     }
     if ((rc = upload(p, p->gf_info, &p->d_gf_info))) return rc;
     {
-        // Phase 2 of the input-gradient kernel: rows of the owned fragment, each split into a unit for the first
-        // ceil(T/2) owned channels and one for the rest, dealt to the block's 16 warps by longest processing time first.
-        // A unit's cost is its share of the row's band length summed over the fragment's entries plus a fixed part.
+        // Phase 2 of the input-gradient kernel: the rows of the owned fragment, each one unit or (split) one unit for
+        // the first ceil(T/2) owned channels and one for the rest, dealt to the block's warps by longest processing time
+        // first.  A unit's cost is its share of the row's band length summed over the fragment's entries plus a fixed
+        // part.  Two tables, [split][2 l^2 + unit].
         constexpr int kWarps = kGfWarps;
         const int ah = (T + 1) / 2, al = T - ah;
-        p->gf_owner.assign((size_t)2 * L1 * L1, 255);
+        p->gf_owner.assign((size_t)2 * 2 * L1 * L1, 255);
+        for (int cfg = 0; cfg < 2; ++cfg)
         for (int l = 0; l < L1; ++l) {
+            const bool split = cfg == 1 && al > 0;
             const int nt = 2 * l + 1;
             std::vector<double> row(nt, 0.0);
             for (int e = p->gf_begin[l]; e < p->gf_begin[l + 1]; ++e) {
@@ -600,8 +603,8 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             }
             std::vector<std::pair<double, int>> units;
             for (int r = 0; r < nt; ++r) {
-                units.push_back({row[r] * (0.15 + ah), r});
-                if (al > 0) units.push_back({row[r] * (0.15 + al), nt + r});
+                units.push_back({row[r] * (0.15 + (split ? ah : T)), r});
+                if (split) units.push_back({row[r] * (0.15 + al), nt + r});
             }
             std::stable_sort(units.begin(), units.end(), [](const std::pair<double, int>& a, const std::pair<double, int>& b) { return a.first > b.first; });
             double load[kWarps] = {0.0};
@@ -610,7 +613,7 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
                 for (int w = 1; w < kWarps; ++w)
                     if (load[w] < load[best]) best = w;
                 load[best] += u.first;
-                p->gf_owner[(size_t)2 * l * l + u.second] = (unsigned char)best;
+                p->gf_owner[(size_t)cfg * 2 * L1 * L1 + (size_t)2 * l * l + u.second] = (unsigned char)best;
             }
         }
         if ((rc = upload(p, p->gf_owner, &p->d_gf_owner))) return rc;
