@@ -189,12 +189,14 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
 // round-robin, each lane keeps up to kFwdTo output channels of its sample in registers, and the warps' partial sums
 // are added in warp order.  `slab` is this lane's view of the group's input slab (global or shared memory).
 // ---------------------------------------------------------------------------------------------------------------
-// Per-warp staging area of the forward kernels: the mixing-weight tile of the current cell, its norm factors and the
-// CG band row of the current (cell, m), loaded by the lanes together (coalesced, all loads in flight at once) and then
-// read back as broadcasts.  Without it every one of those warp-uniform values is a dependent load at L2 latency.
-__host__ __device__ inline int fwd_stage_bytes(int step, int nv, int max_n) {
+// Per-warp staging area of the forward kernels: the mixing-weight tile of a cell, its norm factors and the CG band row
+// of its (cell, m), fetched by the lanes together and then read back as broadcasts (without it every one of those
+// warp-uniform values is a dependent load at L2 latency).  Two buffers per warp: the next cell's values arrive by
+// asynchronous copies while the current cell is computed.
+__host__ __device__ inline int fwd_stage_half_bytes(int step, int nv, int max_n) {
     return ((step * nv * 8 + nv * 4 + max_n * 4) + 15) & ~15;
 }
+__host__ __device__ inline int fwd_stage_bytes(int step, int nv, int max_n) { return 2 * fwd_stage_half_bytes(step, nv, max_n); }
 
 template <int T, bool DW, int NW, int NTO>
 __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restrict__ slab, const float2* __restrict__ W,
@@ -208,35 +210,53 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
     const float2* Wl = W + P.cumW[l];
     constexpr int step = NTO;   // output channels per pass, a compile-time constant so that no issue slot is wasted
     constexpr int red_to = NTO;
-    float2* wbuf = reinterpret_cast<float2*>(stage);          // [step][NV]
-    float* ibuf = reinterpret_cast<float*>(wbuf + step * NV);  // [NV]
-    float* cbuf = ibuf + NV;                                   // [2*l2+1]
+    const int half = fwd_stage_half_bytes(step, NV, P.lmax * 2 + 1);
     for (int to0 = 0; to0 < to_n; to0 += step) {
         float2 o[NTO];
 #pragma unroll
         for (int t = 0; t < NTO; ++t) o[t] = make_float2(0.f, 0.f);
-        int c = c_begin + warp;
-        CellInfo ci;
-        if (c < c_end) ci = P.cell_info[c];
-        while (c < c_end) {
-            const int cn = c + NW;
-            CellInfo nxt;
-            if (cn < c_end) nxt = P.cell_info[cn];   // in flight while this cell is computed
-            const int n2 = 2 * ci.l2 + 1;
-            __syncwarp();   // the previous cell's readers are done with the staging area
+        // asynchronous copies of one cell's tile of W (zero where the tile or the pass has no channel), its norm factors
+        // and its band row into one of the warp's two staging buffers
+        auto stage_cell = [&](const CellInfo& x, unsigned char* st) {
+            float2* wb = reinterpret_cast<float2*>(st);          // [step][NV]
+            float* ib = reinterpret_cast<float*>(wb + step * NV);  // [NV]
+            float* cb = ib + NV;                                   // [2*l2+1]
+            const int xn2 = 2 * x.l2 + 1;
             for (int e = lane; e < step * NV; e += 32) {
                 const int t = e / NV, idx = e - t * NV;
                 const int i = DW ? idx : idx / T, j = DW ? 0 : idx % T;
-                const bool ok = (i < ci.v1) && (DW || j < ci.v2) && (to0 + t < to_n);
-                wbuf[e] = ok ? __ldg(Wl + (int64_t)(to0 + t) * tff + ci.wch0 + (DW ? i : i * ci.tau2 + j)) : make_float2(0.f, 0.f);
+                const bool ok = (i < x.v1) && (DW || j < x.v2) && (to0 + t < to_n);
+                const float2* src = ok ? Wl + (int64_t)(to0 + t) * tff + x.wch0 + (DW ? i : i * x.tau2 + j) : Wl;
+                __pipeline_memcpy_async(wb + e, src, 8, ok ? 0 : 8);
             }
             for (int idx = lane; idx < NV; idx += 32) {
                 const int i = DW ? idx : idx / T, j = DW ? 0 : idx % T;
-                const bool ok = (i < ci.v1) && (DW || j < ci.v2);
-                ibuf[idx] = ok ? __ldg(inv + ci.kch0 + (DW ? i : i * ci.tau2 + j)) : 0.f;
+                const bool ok = (i < x.v1) && (DW || j < x.v2);
+                __pipeline_memcpy_async(ib + idx, ok ? inv + x.kch0 + (DW ? i : i * x.tau2 + j) : inv, 4, ok ? 0 : 4);
             }
-            for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
+            for (int e = lane; e < xn2; e += 32) __pipeline_memcpy_async(cb + e, P.cg + x.cgoff + mi * xn2 + e, 4);
+            __pipeline_commit();
+        };
+        int c = c_begin + warp;
+        int buf = 0;
+        CellInfo ci, nx;
+        __syncwarp();   // the previous pass's readers are done with the staging area
+        if (c < c_end) {
+            ci = P.cell_info[c];
+            stage_cell(ci, stage);
+            if (c + NW < c_end) nx = P.cell_info[c + NW];
+        }
+        while (c < c_end) {
+            const int cn = c + NW;
+            const bool has_next = cn < c_end;
+            CellInfo nx2;
+            if (cn + NW < c_end) nx2 = P.cell_info[cn + NW];   // two cells ahead: in flight while this cell is computed
+            if (has_next) stage_cell(nx, stage + (buf ^ 1) * half);
+            if (has_next) __pipeline_wait_prior(1); else __pipeline_wait_prior(0);   // this cell's copies have landed
             __syncwarp();
+            const float2* wbuf = reinterpret_cast<const float2*>(stage + buf * half);
+            const float* ibuf = reinterpret_cast<const float*>(wbuf + step * NV);
+            const float* cbuf = ibuf + NV;
             float2 v[NV];
             gen_slab<T, DW>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
 #pragma unroll
@@ -246,8 +266,11 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
 #pragma unroll
                 for (int t = 0; t < NTO; ++t) cfma(o[t], wbuf[t * NV + idx], x);   // masked entries carry zero weights
             }
-            ci = nxt;
+            __syncwarp();   // every lane is done with this buffer before the next iteration's copies overwrite it
+            ci = nx;
+            nx = nx2;
             c = cn;
+            buf ^= 1;
         }
         __syncthreads();   // protects `red` from the previous pass / row
 #pragma unroll
