@@ -158,7 +158,7 @@ class ClockSampler:
 # DRAM bytes of one launch (read + write) from the ncu captures summarised under profiles/, per (workload, kernel).
 # They are measurements of a fixed build on a fixed shape, not computed here; a pair without a capture reports null.
 NCU_TRAFFIC = {
-    ("cgnet5_lmax10", "fused_grad_f"): 1.94e6,
+    ("cgnet5_lmax10", "fused_grad_f"): 1.93e6,
     ("cgnet5_lmax10", "fused_grad_w"): 1.58e6,
     ("cgnet5_lmax10", "fused_stats"): 0.93e6,
     ("cgnet5_lmax10", "fused_fwd"): 1.27e6,
