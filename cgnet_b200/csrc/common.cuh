@@ -87,7 +87,6 @@ struct GfEntry {
     short role;
     short in0;
 };
-constexpr int kGfOut = 2;   // channels of the output fragment a block of the input-gradient kernel owns
 
 // Plan tables in device memory.
 struct PlanDev {
@@ -211,15 +210,11 @@ struct cgb200_plan {
     size_t gen_band_bytes = 0;        // largest CG band of a triple, padded to 16 bytes
     size_t gen_sample_bytes = 0;      // largest zero-padded operand pair of a triple, per sample
     std::vector<int> gw_begin;        // [n_triples+1] warp-tasks of the fused weight-gradient kernel per triple
-    const int* d_gw_begin = nullptr;
     int gw_i = 1;                     // t1 channels per weight-gradient task
     int gw_to = 1;                    // output channels per weight-gradient task
     std::vector<cgb200::GfEntry> gf_entries;
     std::vector<int> gf_begin;        // [lmax+2] entries of fragment l
-    const cgb200::GfEntry* d_gf_entries = nullptr;
     const int* d_gf_begin = nullptr;
-    std::vector<int> gf_blocks;       // (fragment, first channel) per block of the input-gradient kernel
-    const int* d_gf_blocks = nullptr;
     // blocks of the cell-staged input-gradient kernel for several degrees of splitting: level s splits the entry
     // list of the most expensive fragment s ways and the others in proportion to their cost
     static constexpr int kGfLevels = 6;               // s = 1, 2, 4, 8, 16, 32

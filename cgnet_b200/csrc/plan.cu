@@ -542,7 +542,6 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         for (auto& o : order) sorted.push_back(p->gw_tasks[o.second]);
         p->gw_tasks.swap(sorted);
     }
-    if ((rc = upload(p, p->gw_begin, &p->d_gw_begin))) return rc;
     if ((rc = upload(p, p->gw_tasks, &p->d_gw_tasks))) return rc;
     // entries of the fused input-gradient kernel, per fragment
     p->gf_begin.assign(L1 + 1, 0);
@@ -651,14 +650,7 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             if ((rc = upload(p, p->gf2_parts[lv], &p->d_gf2_parts[lv]))) return rc;
         }
     }
-    if ((rc = upload(p, p->gf_entries, &p->d_gf_entries))) return rc;
     if ((rc = upload(p, p->gf_begin, &p->d_gf_begin))) return rc;
-    for (int l = 0; l < L1; ++l)
-        for (int t = 0; t < p->tF[l]; t += kGfOut) {
-            p->gf_blocks.push_back(l);
-            p->gf_blocks.push_back(t);
-        }
-    if ((rc = upload(p, p->gf_blocks, &p->d_gf_blocks))) return rc;
 
     CGB_CUDA(cudaMalloc(&p->d_status, sizeof(int)));
     p->allocations.push_back(p->d_status);
