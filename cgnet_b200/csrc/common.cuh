@@ -52,9 +52,18 @@ struct CellInfo {
 // One warp-task of the fused weight-gradient kernel.
 struct GwTask {
     int triple;
-    short q1, gi;     // t1 tile and group of I rows inside it
+    short q1, gi;     // t1 tile and first row of the task inside it
     short q2, qo;     // t2 tile, tau_out tile
+    short ni, pad_;   // rows of t1 the task covers
 };
+// Rows of t1 per weight-gradient task, by tile edge: a tile is cut into groups of A rows and, where A does not divide
+// the edge, one last group of B rows (tile edge 5 = 3 + 2), so that no task carries a masked row.
+template <int T>
+struct GwRows {
+    static constexpr int A = T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 3 : 1;
+    static constexpr int B = T % A;
+};
+inline int gw_rows_a(int T) { return T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 3 : 1; }
 
 // One entry of the fused input-gradient kernel with its triple's data inlined.
 struct GfInfo {

@@ -342,7 +342,100 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
 // the end.  The task list is sorted by cost, most expensive first, so the blocks that start first carry the long bands
 // and the cheap tasks fill the tail.
 // ---------------------------------------------------------------------------------------------------------------
+// One task of the weight-gradient kernel with exactly I rows of t1.
 template <int T, int I, int TO>
+__device__ __forceinline__ void gw_unit(const PlanDev& P, const GwTask tk, int slice, int slices, const float2* __restrict__ SF,
+                                        const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ out,
+                                        int G, float* __restrict__ band, int lane) {
+    const TripleRec tr = P.triples[tk.triple];
+    const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
+    const int to_n = P.tO[l], tff = P.tFF[l];
+    const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
+    const int j0 = tk.gi;   // first t1 row of the task inside its tile; the task covers exactly I rows
+    __syncwarp();   // the previous task's readers are done with the band
+    for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
+    __syncwarp();
+    const float* C = band;
+    int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
+#pragma unroll
+    for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
+    int goff[TO];  // slab offset of output channel qo*TO+o at m index 0 (clamped to the last channel, masked at the end)
+#pragma unroll
+    for (int o = 0; o < TO; ++o) {
+        const int to = min(qo * TO + o, to_n - 1);
+        goff[o] = ((to / T) * n * T + to % T) * 32;
+    }
+
+    float2 acc[TO][I][T];
+#pragma unroll
+    for (int o = 0; o < TO; ++o)
+#pragma unroll
+        for (int i = 0; i < I; ++i)
+#pragma unroll
+            for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
+
+    for (int g = slice; g < G; g += slices) {
+        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
+        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
+        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
+        for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
+            float2 Y[TO][I];
+#pragma unroll
+            for (int o = 0; o < TO; ++o)
+#pragma unroll
+                for (int i = 0; i < I; ++i) Y[o][i] = make_float2(0.f, 0.f);
+            const int mlo = max(-l, m2 - tr.l1), mhi = min(l, m2 + tr.l1);
+            const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
+            const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
+            const float2* pg = go + (mlo + l) * (T * 32);
+            for (int k = mhi - mlo; k >= 0; --k) {
+                const float c = *pc;
+                float2 a[I];
+#pragma unroll
+                for (int i = 0; i < I; ++i) {
+                    a[i] = p1[jrow[i] * 32];
+                    a[i].x *= c;
+                    a[i].y *= c;
+                }
+#pragma unroll
+                for (int o = 0; o < TO; ++o) {
+                    const float2 gv = pg[goff[o]];
+#pragma unroll
+                    for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
+                }
+                pc += n2;
+                p1 += T * 32;
+                pg += T * 32;
+            }
+            const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
+            float2 bj[T];
+#pragma unroll
+            for (int j = 0; j < T; ++j) bj[j] = p2[j * 32];
+#pragma unroll
+            for (int o = 0; o < TO; ++o)
+#pragma unroll
+                for (int i = 0; i < I; ++i)
+#pragma unroll
+                    for (int j = 0; j < T; ++j) cfma_conj(acc[o][i][j], bj[j], Y[o][i]);
+        }
+    }
+#pragma unroll
+    for (int o = 0; o < TO; ++o)
+#pragma unroll
+        for (int i = 0; i < I; ++i)
+#pragma unroll
+            for (int j = 0; j < T; ++j) {
+                const float sx = warp_sum(acc[o][i][j].x), sy = warp_sum(acc[o][i][j].y);
+                const int t1 = q1 * T + j0 + i, t2 = q2 * T + j, to = qo * TO + o;
+                if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
+                    const int ch = t1 * tr.tau2 + t2;
+                    const float s = inv[tr.kglob + ch];
+                    out[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
+                }
+            }
+}
+
+template <int T, int TO>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
@@ -356,92 +449,11 @@ fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const 
         const int task = unit / slices, slice = unit - task * slices;
         float2* __restrict__ out = gW + (int64_t)slice * slice_stride;
         const GwTask tk = tasks[task];
-        const TripleRec tr = P.triples[tk.triple];
-        const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
-        const int to_n = P.tO[l], tff = P.tFF[l];
-        const int q1 = tk.q1, q2 = tk.q2, qo = tk.qo;
-        const int j0 = tk.gi * I;
-        __syncwarp();   // the previous task's readers are done with the band
-        for (int e = lane; e < n * n2; e += 32) band[e] = __ldg(P.cg + tr.cgoff + e);
-        __syncwarp();
-        const float* C = band;
-        int jrow[I];   // channel inside the tile read for row i (clamped: rows past the tile are masked at the end)
-#pragma unroll
-        for (int i = 0; i < I; ++i) jrow[i] = min(j0 + i, T - 1);
-        int goff[TO];  // slab offset of output channel qo*TO+o at m index 0 (clamped to the last channel, masked at the end)
-#pragma unroll
-        for (int o = 0; o < TO; ++o) {
-            const int to = min(qo * TO + o, to_n - 1);
-            goff[o] = ((to / T) * n * T + to % T) * 32;
-        }
-
-        float2 acc[TO][I][T];
-#pragma unroll
-        for (int o = 0; o < TO; ++o)
-#pragma unroll
-            for (int i = 0; i < I; ++i)
-#pragma unroll
-                for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
-
-        for (int g = slice; g < G; g += slices) {
-            const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
-            const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
-            const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
-            for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
-                float2 Y[TO][I];
-#pragma unroll
-                for (int o = 0; o < TO; ++o)
-#pragma unroll
-                    for (int i = 0; i < I; ++i) Y[o][i] = make_float2(0.f, 0.f);
-                const int mlo = max(-l, m2 - tr.l1), mhi = min(l, m2 + tr.l1);
-                const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
-                const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
-                const float2* pg = go + (mlo + l) * (T * 32);
-                for (int k = mhi - mlo; k >= 0; --k) {
-                    const float c = *pc;
-                    float2 a[I];
-#pragma unroll
-                    for (int i = 0; i < I; ++i) {
-                        a[i] = p1[jrow[i] * 32];
-                        a[i].x *= c;
-                        a[i].y *= c;
-                    }
-#pragma unroll
-                    for (int o = 0; o < TO; ++o) {
-                        const float2 gv = pg[goff[o]];
-#pragma unroll
-                        for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
-                    }
-                    pc += n2;
-                    p1 += T * 32;
-                    pg += T * 32;
-                }
-                const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
-                float2 bj[T];
-#pragma unroll
-                for (int j = 0; j < T; ++j) bj[j] = p2[j * 32];
-#pragma unroll
-                for (int o = 0; o < TO; ++o)
-#pragma unroll
-                    for (int i = 0; i < I; ++i)
-#pragma unroll
-                        for (int j = 0; j < T; ++j) cfma_conj(acc[o][i][j], bj[j], Y[o][i]);
-            }
-        }
-#pragma unroll
-        for (int o = 0; o < TO; ++o)
-#pragma unroll
-            for (int i = 0; i < I; ++i)
-#pragma unroll
-                for (int j = 0; j < T; ++j) {
-                    const float sx = warp_sum(acc[o][i][j].x), sy = warp_sum(acc[o][i][j].y);
-                    const int t1 = q1 * T + j0 + i, t2 = q2 * T + j, to = qo * TO + o;
-                    if (lane == 0 && j0 + i < T && to < to_n && t1 < tr.tau1 && t2 < tr.tau2) {
-                        const int ch = t1 * tr.tau2 + t2;
-                        const float s = inv[tr.kglob + ch];
-                        out[P.cumW[l] + (int64_t)to * tff + tr.toff + ch] = make_float2(sx * s, sy * s);
-                    }
-                }
+        // the row groups of a tile are exact (GwRows): a task has GwRows<T>::A rows or, for the last group of a tile
+        // whose edge is not a multiple of A, GwRows<T>::B rows
+        if (tk.ni == GwRows<T>::A) gw_unit<T, GwRows<T>::A, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane);
+        if constexpr (GwRows<T>::B > 0)
+            if (tk.ni == GwRows<T>::B) gw_unit<T, GwRows<T>::B, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane);
     }
 }
 
@@ -842,8 +854,7 @@ int launch_prep(const cgb200_plan* p, const PrepJob& a, const PrepJob& b, int nj
     }
 
 template <int T>
-struct GwShape {   // must match kGwI / kGwTo of the plan
-    static constexpr int I = T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1;
+struct GwShape {   // output channels per weight-gradient task; must match gw_to of the plan (kGwTo in plan.cu)
     static constexpr int TO = T == 1 ? 8 : T == 2 ? 8 : T == 3 ? 4 : T == 4 ? 4 : T == 5 ? 5 : 6;
 };
 
@@ -979,7 +990,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             });
         } else {
             CGB_DISPATCH_TILE(T, false, {
-                auto kern = fused_gw_kernel<TT, GwShape<TT>::I, GwShape<TT>::TO>;
+                auto kern = fused_gw_kernel<TT, GwShape<TT>::TO>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                 const int slices = ws.gw_slices;
                 const int grid = (int)(((int64_t)n_tasks * slices + kGwWarps - 1) / kGwWarps);

@@ -505,9 +505,8 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
 
     // warp-tasks of the fused weight-gradient kernel: (t1 group, t2 tile, tau_out tile) per triple
     // rows of t1 and output channels per task, by tile edge: about 32..50 complex accumulators per lane
-    static const int kGwI[kMaxTile + 1] = {0, 1, 2, 3, 2, 2, 1};
     static const int kGwTo[kMaxTile + 1] = {0, 8, 8, 4, 4, 5, 6};
-    p->gw_i = dw ? T : kGwI[T];
+    p->gw_i = dw ? T : gw_rows_a(T);
     p->gw_to = dw ? T : kGwTo[T];
     p->gw_begin.assign(n + 1, 0);
     for (int k = 0; k < n; ++k) {
@@ -523,7 +522,8 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             for (int gi = 0; gi < groups; ++gi)
                 for (int q2 = 0; q2 < (dw ? 1 : t.nt2); ++q2)
                     for (int qo = 0; qo < (int)no; ++qo)
-                        p->gw_tasks.push_back({k, (short)q1, (short)gi, (short)q2, (short)qo});
+                        p->gw_tasks.push_back({k, (short)q1, (short)(dw ? gi : gi * p->gw_i), (short)q2, (short)qo,
+                                               (short)(dw ? T : std::min(p->gw_i, T - gi * p->gw_i)), 0});
         CGB_REQUIRE((int)p->gw_tasks.size() == p->gw_begin[k + 1], "internal: weight-gradient task count");
     }
     {   // the warps of the weight-gradient kernel pull tasks from a queue: most expensive first
@@ -531,7 +531,7 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             const TripleRec& t = p->triples[tk.triple];
             double nnz = 0;
             for (int m = -t.l; m <= t.l; ++m) nnz += std::min(t.l2, m + t.l1) - std::max(-t.l2, m - t.l1) + 1;
-            return nnz + 6.0 * (2 * t.l2 + 1);
+            return (nnz + 6.0 * (2 * t.l2 + 1)) * (2.0 + tk.ni);   // the per-row part and the part shared by the rows
         };
         std::vector<std::pair<double, int>> order;
         order.reserve(p->gw_tasks.size());
