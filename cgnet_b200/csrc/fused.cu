@@ -297,7 +297,7 @@ fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restri
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* red = reinterpret_cast<float2*>(smem_raw);
     const int l = rows[2 * blockIdx.x], mi = rows[2 * blockIdx.x + 1];
-    const int g = blockIdx.y;
+    const int g = blockIdx.y;   // group-major block order: consecutive blocks on an SM read the same group's slab through L1
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* stage = smem_raw + (size_t)kFwdWarps * red_to * 32 * sizeof(float2) + (size_t)warp * stage_bytes;
     fwd_row<T, DW, kFwdWarps, NTO>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, stage, l, mi, g * 32 + lane, B, warp,
@@ -578,10 +578,13 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     using S = GfShape<T, DW>;
     constexpr int NH = S::NH, NHP = S::NHP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int lt = blocks[4 * blockIdx.x], q = blocks[4 * blockIdx.x + 1];
-    const int part = blocks[4 * blockIdx.x + 2], parts = blocks[4 * blockIdx.x + 3];
+    // blockIdx.x = block * G + group: the blocks are listed most expensive first, and the sample groups of one block
+    // start together, so the cheap blocks of every group are what is left for the last wave
+    const int G = (B + 31) >> 5;
+    const int blk = blockIdx.x / G, g = blockIdx.x - blk * G;
+    const int lt = blocks[4 * blk], q = blocks[4 * blk + 1];
+    const int part = blocks[4 * blk + 2], parts = blocks[4 * blk + 3];
     const int nt = 2 * lt + 1, t_0 = q * T;
-    const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int tau_t = P.tF[lt];
@@ -1041,7 +1044,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             CGB_DISPATCH_TILE(T, p->d.depthwise, {
                 auto kern = split_units ? fused_gf_kernel<TT, DD, true> : fused_gf_kernel<TT, DD, false>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<dim3(nblk, G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
             });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());
