@@ -401,6 +401,49 @@ __device__ __forceinline__ void gen_slab(float2 (&v)[TileShape<T, DW>::NV], cons
     }
 }
 
+// The generator restricted to the rows I0 .. I0+IN of the tile (full product only): v[i*T + j] for i < IN is the tile's
+// entry (I0 + i, j).  Operand loads software-pipelined as in gen_slab<.., true>.
+template <int T, int I0, int IN>
+__device__ __forceinline__ void gen_slab_rows(float2 (&v)[IN * T], const float* __restrict__ Crow, const float2* __restrict__ S1,
+                                              const float2* __restrict__ S2, int m, int l1, int l2) {
+    const int lo = max(-l2, m - l1), hi = min(l2, m + l1);
+#pragma unroll
+    for (int i = 0; i < IN * T; ++i) v[i] = make_float2(0.f, 0.f);
+    if (hi < lo) return;
+    const float2* p2 = S2 + (lo + l2) * (T * 32);
+    const float2* p1 = S1 + (m - lo + l1) * (T * 32) + I0 * 32;
+    const float* pc = Crow + lo + l2;
+    float c = *pc;
+    float2 a[IN], b[T];
+#pragma unroll
+    for (int j = 0; j < T; ++j) b[j] = p2[j * 32];
+#pragma unroll
+    for (int i = 0; i < IN; ++i) a[i] = p1[i * 32];
+    for (int k = hi - lo; k >= 0; --k) {
+        const int adv = k > 0 ? 1 : 0;   // the last step fetches its own operands again: no peeled tail, no stray address
+        pc += adv;
+        p2 += adv * (T * 32);
+        p1 -= adv * (T * 32);
+        const float cn = *pc;
+        float2 an[IN], bn[T];
+#pragma unroll
+        for (int j = 0; j < T; ++j) bn[j] = p2[j * 32];
+#pragma unroll
+        for (int i = 0; i < IN; ++i) an[i] = p1[i * 32];
+#pragma unroll
+        for (int i = 0; i < IN; ++i) {
+            const float2 ac = make_float2(a[i].x * c, a[i].y * c);
+#pragma unroll
+            for (int j = 0; j < T; ++j) cfma(v[i * T + j], ac, b[j]);
+        }
+        c = cn;
+#pragma unroll
+        for (int j = 0; j < T; ++j) b[j] = bn[j];
+#pragma unroll
+        for (int i = 0; i < IN; ++i) a[i] = an[i];
+    }
+}
+
 // Mid channel (relative to the triple's first) of tile entry idx, and whether the entry exists.
 template <int T, bool DW>
 __device__ __forceinline__ int tile_channel(int idx, int t1_0, int t2_0, int tau2) {

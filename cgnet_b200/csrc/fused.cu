@@ -125,32 +125,28 @@ __device__ __forceinline__ float moving_std_f(float old, double sigma, float cnt
     return (float)((double)s + sigma / (double)(cnt + 1.f));
 }
 
-template <int T, bool DW>
-__global__ void __launch_bounds__(256)
-fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__ stds, float* __restrict__ inv, float cnt,
-                   float eps, int B, int G) {
-    constexpr int NV = TileShape<T, DW>::NV;
-    __shared__ double red[8][NV][2];
-    extern __shared__ __align__(16) float sband[];   // the triple's CG band, (2l+1) x (2l2+1)
-    const int cidx = P.n_cells - 1 - blockIdx.x;     // the last degrees carry the long bands: start them first
-    const CellRec cell = P.cells[cidx];
-    const TripleRec tr = P.triples[cell.triple];
+// Body of the statistics kernel for the tile entries [E0, E0 + NE): the whole tile, or (full product, SPLIT) the rows
+// I0 .. I0+IN of it, in which case two blocks share a cell and each needs half the registers, so that two blocks fit an SM.
+template <int T, bool DW, int I0, int IN>
+__device__ __forceinline__ void stats_body(const PlanDev& P, const CellRec& cell, const TripleRec& tr, const float2* __restrict__ SF,
+                                           float* __restrict__ stds, float* __restrict__ inv, float cnt, float eps, int B, int G,
+                                           const float* __restrict__ C, double (*red)[TileShape<T, DW>::NV][2]) {
+    constexpr int NE = DW ? IN : IN * T;      // tile entries handled here
+    constexpr int E0 = DW ? I0 : I0 * T;      // first of them
     const int n = 2 * tr.l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < n * n2; i += 256) sband[i] = P.cg[tr.cgoff + i];
-    __syncthreads();
-    float s1[NV], s1c[NV], s2[NV];
+    float s1[NE], s1c[NE], s2[NE];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) s1[i] = s1c[i] = s2[i] = 0.f;
-    const float* C = sband;
+    for (int i = 0; i < NE; ++i) s1[i] = s1c[i] = s2[i] = 0.f;
     const int o1 = P.cumSF[tr.l1] + (cell.t1_0 / T) * n1 * T, o2 = P.cumSF[tr.l2] + (cell.t2_0 / T) * n2 * T;
     for (int task = warp; task < G * n; task += 8) {
         const int g = task / n, mi = task - g * n;
         const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
-        float2 v[NV];
-        gen_slab<T, DW, true>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
+        float2 v[NE];
+        if constexpr (!DW && IN < T) gen_slab_rows<T, I0, IN>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
+        else gen_slab<T, DW, true>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
+        for (int i = 0; i < NE; ++i) {
             const float nrm = v[i].x * v[i].x + v[i].y * v[i].y;
             const float r = sqrtf(nrm);
             s2[i] += nrm;
@@ -159,7 +155,7 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
         }
     }
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
+    for (int i = 0; i < NE; ++i) {
         const double a = warp_sum((double)s1[i] + (double)s1c[i]), b = warp_sum((double)s2[i]);
         if (lane == 0) {
             red[warp][i][0] = a;
@@ -168,7 +164,7 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
     }
     __syncthreads();
     const int idx = threadIdx.x;
-    if (idx < NV && tile_valid<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau1, tr.tau2)) {
+    if (idx < NE && tile_valid<T, DW>(E0 + idx, cell.t1_0, cell.t2_0, tr.tau1, tr.tau2)) {
         double m1 = 0.0, m2 = 0.0;
         for (int w = 0; w < 8; ++w) {
             m1 += red[w][idx][0];
@@ -177,10 +173,34 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
         const double N = (double)B * n;
         const double var = m2 / N - (m1 / N) * (m1 / N);
         const double sigma = var > 0.0 ? sqrt(var) : 0.0;
-        const int k = tr.kglob + tile_channel<T, DW>(idx, cell.t1_0, cell.t2_0, tr.tau2);
+        const int k = tr.kglob + tile_channel<T, DW>(E0 + idx, cell.t1_0, cell.t2_0, tr.tau2);
         const float s = moving_std_f(stds[k], sigma, cnt);
         stds[k] = s;
         inv[k] = 1.f / fmaxf(eps, s);
+    }
+}
+
+// grid = cells, or 2 x cells with SPLIT (block 2c handles the first ceil(T/2) rows of cell c's tile, block 2c+1 the rest)
+template <int T, bool DW, bool SPLIT>
+__global__ void __launch_bounds__(256, (SPLIT || T <= 4) ? 2 : 1)
+fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__ stds, float* __restrict__ inv, float cnt,
+                   float eps, int B, int G) {
+    constexpr int NV = TileShape<T, DW>::NV;
+    __shared__ double red[8][NV][2];
+    extern __shared__ __align__(16) float sband[];   // the triple's CG band, (2l+1) x (2l2+1)
+    const int blk = SPLIT ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int cidx = P.n_cells - 1 - blk;            // the last degrees carry the long bands: start them first
+    const CellRec cell = P.cells[cidx];
+    const TripleRec tr = P.triples[cell.triple];
+    const int n = 2 * tr.l + 1, n2 = 2 * tr.l2 + 1;
+    for (int i = threadIdx.x; i < n * n2; i += 256) sband[i] = P.cg[tr.cgoff + i];
+    __syncthreads();
+    if constexpr (SPLIT && !DW && T > 1) {
+        constexpr int AH = (T + 1) / 2;
+        if ((blockIdx.x & 1) == 0) stats_body<T, DW, 0, AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
+        else stats_body<T, DW, AH, T - AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
+    } else {
+        stats_body<T, DW, 0, T>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
     }
 }
 
@@ -893,10 +913,14 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     if (update && p->d.n_cells > 0) {
         const size_t band = p->gen_band_bytes;
         launch_begin(K_STATS, st);
+        // tile edge 5 and 6 need ~200 registers for a whole tile (one block of 8 warps per SM): two blocks per cell, each
+        // with half the tile's rows and under 128 registers, put two blocks on an SM
+        static const int split_env = [] { const char* e = getenv("CGB200_STATS_SPLIT"); return e ? atoi(e) : -1; }();
+        const bool split_rows = !p->d.depthwise && (split_env >= 0 ? split_env != 0 : T >= 5);
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
-            auto kern = fused_stats_kernel<TT, DD>;
+            auto kern = split_rows ? fused_stats_kernel<TT, DD, true> : fused_stats_kernel<TT, DD, false>;
             if (band > 40 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band));
-            kern<<<p->d.n_cells, 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G);
+            kern<<<p->d.n_cells * (split_rows ? 2 : 1), 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G);
         });
         launch_end(K_STATS, st);
         CGB_CUDA(cudaGetLastError());
