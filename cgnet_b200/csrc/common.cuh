@@ -57,13 +57,14 @@ struct GwTask {
     short ni, pad_;   // rows of t1 the task covers
 };
 // Rows of t1 per weight-gradient task, by tile edge: a tile is cut into groups of A rows and, where A does not divide
-// the edge, one last group of B rows (tile edge 5 = 3 + 2), so that no task carries a masked row.
+// the edge, one last group of B rows (tile edge 5 = 2 + 2 + 1), so that no task carries a masked row.  Two rows keep
+// the kernel under 168 registers with its operand prefetch, i.e. three blocks per SM; groups of three rows need 254.
 template <int T>
 struct GwRows {
-    static constexpr int A = T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 3 : 1;
+    static constexpr int A = T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1;
     static constexpr int B = T % A;
 };
-inline int gw_rows_a(int T) { return T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 3 : 1; }
+inline int gw_rows_a(int T) { return T == 1 ? 1 : T == 2 ? 2 : T == 3 ? 3 : T == 4 ? 2 : T == 5 ? 2 : 1; }
 
 // One entry of the fused input-gradient kernel with its triple's data inlined.
 struct GfInfo {

@@ -408,24 +408,41 @@ __device__ __forceinline__ void gw_unit(const PlanDev& P, const GwTask tk, int s
             const float* pc = C + (mlo + l) * n2 + m2 + tr.l2;
             const float2* p1 = f1 + (mlo - m2 + tr.l1) * (T * 32);
             const float2* pg = go + (mlo + l) * (T * 32);
-            for (int k = mhi - mlo; k >= 0; --k) {
-                const float c = *pc;
-                float2 a[I];
+            // software pipeline: the operands of band step k+1 are in flight while step k's FMAs run (the last step
+            // fetches its own again); they come from global memory through L1
+            if (mhi >= mlo) {
+                float c = *pc;
+                float2 a[I], gv[TO];
 #pragma unroll
-                for (int i = 0; i < I; ++i) {
-                    a[i] = p1[jrow[i] * 32];
-                    a[i].x *= c;
-                    a[i].y *= c;
+                for (int i = 0; i < I; ++i) a[i] = p1[jrow[i] * 32];
+#pragma unroll
+                for (int o = 0; o < TO; ++o) gv[o] = pg[goff[o]];
+                for (int k = mhi - mlo; k >= 0; --k) {
+                    const int adv = k > 0 ? 1 : 0;
+                    pc += adv * n2;
+                    p1 += adv * (T * 32);
+                    pg += adv * (T * 32);
+                    const float cn = *pc;
+                    float2 an[I], gn[TO];
+#pragma unroll
+                    for (int i = 0; i < I; ++i) an[i] = p1[jrow[i] * 32];
+#pragma unroll
+                    for (int o = 0; o < TO; ++o) gn[o] = pg[goff[o]];
+#pragma unroll
+                    for (int i = 0; i < I; ++i) {
+                        a[i].x *= c;
+                        a[i].y *= c;
+                    }
+#pragma unroll
+                    for (int o = 0; o < TO; ++o)
+#pragma unroll
+                        for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv[o]);
+                    c = cn;
+#pragma unroll
+                    for (int i = 0; i < I; ++i) a[i] = an[i];
+#pragma unroll
+                    for (int o = 0; o < TO; ++o) gv[o] = gn[o];
                 }
-#pragma unroll
-                for (int o = 0; o < TO; ++o) {
-                    const float2 gv = pg[goff[o]];
-#pragma unroll
-                    for (int i = 0; i < I; ++i) cfma_conj(Y[o][i], a[i], gv);
-                }
-                pc += n2;
-                p1 += T * 32;
-                pg += T * 32;
             }
             const float2* p2 = f2 + (m2 + tr.l2) * (T * 32);
             float2 bj[T];
@@ -456,7 +473,7 @@ __device__ __forceinline__ void gw_unit(const PlanDev& P, const GwTask tk, int s
 }
 
 template <int T, int TO>
-__global__ void __launch_bounds__(kGwWarps * kWarp)
+__global__ void __launch_bounds__(kGwWarps * kWarp, 3)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
                 int band_floats, int slices, int64_t slice_stride) {
