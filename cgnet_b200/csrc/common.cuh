@@ -190,7 +190,9 @@ bool tc_gw_wanted(const cgb200_plan* p);
 bool tc_gf_wanted(const cgb200_plan* p);
 int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* SG, const float2* W, const float* inv, float2* out,
                  int64_t part_stride, int B, int G, cudaStream_t st);
-int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, int G, cudaStream_t st);
+int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
+                 int max_slices, int G, cudaStream_t st);
+void launch_gw_reduce(const cgb200_plan* p, const float2* partial, int slices, float2* gW, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
 int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
                   cudaStream_t st);
@@ -238,6 +240,7 @@ struct cgb200_plan {
     // tensor-core forward (tile edge 2 or 4, full product): per degree the padded GEMM width N' = 2*tau_out rounded
     // up to 16, the offset (in floats) of the degree's packed weights, and the list of row tiles (l, first m index)
     bool tc_ok = false;
+    bool tc_gw_ok = false;            // the tensor-core weight gradient's tables exist (tile edge 4 or 5)
     std::vector<int> tc_npad;
     std::vector<int64_t> tc_pack_off;   // [lmax+2]
     std::vector<int> tc_tiles;          // (l, m0) pairs, longest K first

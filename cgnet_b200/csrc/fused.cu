@@ -508,6 +508,13 @@ gw_reduce_kernel(const float2* __restrict__ partial, int slices, int64_t slice_s
     }
 }
 
+void launch_gw_reduce(const cgb200_plan* p, const float2* partial, int slices, float2* gW, cudaStream_t st) {
+    launch_begin(K_GW_REDUCE, st);
+    const int gx = (int)std::min<int64_t>((p->d.w_len + 255) / 256, 4 * p->num_sms);
+    gw_reduce_kernel<<<gx, 256, 0, st>>>(partial, slices, p->d.w_len, gW, p->d.w_len);
+    launch_end(K_GW_REDUCE, st);
+}
+
 // weight gradient, depthwise product: warp-task = (triple, t tile, tau_out tile); FF tile generated directly.
 template <int T>
 __global__ void __launch_bounds__(kGwWarps * kWarp)
@@ -1017,7 +1024,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     // weight gradient (enqueued on stream gs): every (to, k) of every degree with both output and mid channels belongs to exactly one task
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
     auto enqueue_gw = [&](cudaStream_t gs) -> int {
-        if (tc_gw_wanted(p)) return launch_gw_tc(p, ws.SF, ws.SG, ws.inv, (float2*)gW, G, gs);
+        if (tc_gw_wanted(p)) return launch_gw_tc(p, ws.SF, ws.SG, ws.inv, (float2*)gW, ws.gw_part, ws.gw_slices, G, gs);
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;
@@ -1044,9 +1051,9 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             if (ws.gw_slices > 1) {
                 launch_end(K_GW, gs);
                 CGB_CUDA(cudaGetLastError());
-                launch_begin(K_GW_REDUCE, gs);
-                const int gx = (int)std::min<int64_t>((p->d.w_len + 255) / 256, 4 * p->num_sms);
-                gw_reduce_kernel<<<gx, 256, 0, gs>>>(ws.gw_part, ws.gw_slices, p->d.w_len, (float2*)gW, p->d.w_len);
+                launch_gw_reduce(p, ws.gw_part, ws.gw_slices, (float2*)gW, gs);
+                CGB_CUDA(cudaGetLastError());
+                return CGB200_OK;
             }
         }
         launch_end(K_GW, gs);

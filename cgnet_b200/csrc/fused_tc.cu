@@ -319,10 +319,10 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
 //   gW_l[to, k] = 1/std_k * sum_{b, m} conj(FF_l[b, k, m]) * gO_l[b, to, m]
 //
 // as a real GEMM that contracts over (m, b):  D[(k, re|im), (to, re|im)] = sum A'[(k, .), (m, b)] * B'[(to, .), (m, b)],
-// from which gW.re = D[kr, tor] + D[ki, toi] and gW.im = D[kr, toi] - D[ki, tor].  Block = four cells of one degree
-// (4 x 2T^2 = 128 rows of D for T = 4 = the 128 lanes of tensor memory) against all output channels; it walks every
-// (sample group, m) of the layer, 32 samples = one K chunk = four K steps of the MMA.  Generator group s (four warps,
-// warp w <-> cell w of the block) fills pipeline stage s for the chunks s, s + S, ...: the cell's FF values of its lane's
+// from which gW.re = D[kr, tor] + D[ki, toi] and gW.im = D[kr, toi] - D[ki, tor].  Block = four cells (tile edge 4) or two
+// cells (tile edge 5) of one degree = up to 128 rows of D = the 128 lanes of tensor memory, against all output channels;
+// it walks every (sample group of its slice, m), 32 samples = one K chunk = four K steps of the MMA.  Generator group s
+// (four warps, see GwTcShape) fills pipeline stage s for the chunks s, s + S, ...: the cell's FF values of its lane's
 // sample, split into TF32 high / low parts, go to shared memory as the M x K operand (K-major: a lane owns one K
 // column), and the four warps share the chunk's gO values as the N x K operand.  The K stride between core matrices is
 // 144 bytes instead of 128, so that the eight lane quads of a warp, which write eight different core matrices of the
@@ -332,20 +332,55 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
 constexpr uint32_t kGwLbo = 144;           // bytes between K-adjacent core matrices (8 rows x 16 bytes, then 16 bytes of padding)
 constexpr uint32_t kGwSbo = 8 * kGwLbo;    // bytes between 8-row groups: a K chunk of 32 samples = 8 core matrices
 
+// Shape of a weight-gradient block by tile edge.  Tile edge 4: four cells of 32 real rows, one generator warp per cell.
+// Tile edge 5: two cells of 50 real rows (100 of the 128 accumulator rows used), two generator warps per cell, each
+// with half the tile's rows (3 + 2), which also halves the registers of the generator.
+template <int T>
+struct GwTcShape {
+    static constexpr int NV = T * T;
+    static constexpr int MR = 2 * NV;            // real rows of D per cell
+    static constexpr int kCells = 128 / MR;      // cells per block
+    static constexpr int kSplit = 4 / kCells;    // generator warps per cell
+    static_assert(kCells * kSplit == 4 && kCells * MR <= 128, "a generator group is four warps");
+};
+
+// one generator warp's values of a chunk: rows [I0, I0 + IN) of cell `c`'s tile -> TF32 high / low parts in the A' stage
+template <int T, int I0, int IN>
+__device__ __forceinline__ void gw_tc_generate(const CellInfo& ci, const float2* __restrict__ slab, const float* __restrict__ cbuf,
+                                               int mi, int l, int c, unsigned char* __restrict__ a_hi, uint32_t a_bytes) {
+    constexpr int MR = 2 * T * T;
+    float2 v[IN * T];
+    if constexpr (IN == T) gen_slab<T, false, true>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+    else gen_slab_rows<T, I0, IN>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+    const int rbase = c * MR + 2 * I0 * T;   // even: a value's (re, im) rows share an 8-row group
+#pragma unroll
+    for (int e = 0; e < IN * T; ++e) {
+        const int r = rbase + 2 * e;
+        unsigned char* ph = a_hi + (uint32_t)(r >> 3) * kGwSbo + (uint32_t)(r & 7) * 16;
+        const float hx = to_tf32(v[e].x), hy = to_tf32(v[e].y);
+        *reinterpret_cast<float*>(ph) = hx;
+        *reinterpret_cast<float*>(ph + 16) = hy;
+        *reinterpret_cast<float*>(ph + a_bytes) = v[e].x - hx;
+        *reinterpret_cast<float*>(ph + a_bytes + 16) = v[e].y - hy;
+    }
+}
+
+// grid = (blocks of cells, slices of the sample groups); slice s handles the groups s, s + slices, ... and, with more
+// than one slice, writes its partial sums to gW + s * slice_stride for gw_reduce_kernel
 template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
-                   int max_n, int* __restrict__ status, int n_stages) {
-    constexpr int NV = T * T;
-    constexpr int MR = 2 * NV;   // real rows of D per cell
-    static_assert(4 * MR == 128, "four cells must fill the 128 rows of the accumulator");
+                   int max_n, int* __restrict__ status, int n_stages, int64_t slice_stride) {
+    using S = GwTcShape<T>;
+    constexpr int MR = S::MR;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
     const int l = tiles[2 * blockIdx.x], cell0 = tiles[2 * blockIdx.x + 1];
+    const int slice = blockIdx.y, slices = gridDim.y;
     const int n = 2 * l + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
@@ -356,8 +391,10 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
     const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
     float* cbuf = reinterpret_cast<float*>(smem_raw + (size_t)n_stages * stage_bytes) + (size_t)warp * max_n;
     const int gen_warps = 4 * n_stages;
-    const int n_chunks = n * G;
+    const int n_groups = slice < G ? (G - slice + slices - 1) / slices : 0;   // sample groups of this slice
+    const int n_chunks = n * n_groups;
     volatile int* failed = &failed_flag;
+    float2* __restrict__ out_base = gW + (int64_t)slice * slice_stride;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) {
@@ -377,7 +414,8 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
     if (warp < gen_warps) {
         // ---------------- generators ----------------
         const int s = warp >> 2, wq = warp & 3;
-        const int cell = cell0 + wq;
+        const int c = wq / S::kSplit, half = wq % S::kSplit;   // cell of the block, part of its rows
+        const int cell = cell0 + c;
         const bool live = cell < ncell;
         CellInfo ci{};
         if (live) ci = P.cell_info[c_begin + cell];
@@ -385,8 +423,7 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
         unsigned char* st_base = smem_raw + (size_t)s * stage_bytes;
         // this lane's K column inside a chunk: core matrix lane/4 along K, word lane%4 inside its 16-byte row
         const uint32_t col_off = (uint32_t)(lane >> 2) * kGwLbo + (uint32_t)(lane & 3) * 4;
-        unsigned char* a_hi = st_base + (uint32_t)(wq * (MR / 8)) * kGwSbo + col_off;   // this warp's 32 rows
-        unsigned char* a_lo = a_hi + a_bytes;
+        unsigned char* a_hi = st_base + col_off;
         unsigned char* b_hi = st_base + 2 * a_bytes + col_off;
         unsigned char* b_lo = b_hi + b_bytes;
         const int to_per = (to_n + 3) >> 2, to_lo = wq * to_per, to_hi = min(to_n, to_lo + to_per);
@@ -394,21 +431,19 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
         for (int q = s, u = 0; q < n_chunks && ok; q += n_stages, ++u) {
             if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
             if (!ok) break;
-            const int g = q / n, mi = q - g * n;
+            const int gi = q / n, mi = q - gi * n;
+            const int g = slice + gi * slices;
             if (live) {
                 const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
-                float2 v[NV];
                 __syncwarp();
                 for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
                 __syncwarp();
-                gen_slab<T, false, true>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
-#pragma unroll
-                for (int kk = 0; kk < MR; ++kk) {
-                    const float x = (kk & 1) ? v[kk >> 1].y : v[kk >> 1].x;
-                    const float h = to_tf32(x);
-                    const uint32_t off = (uint32_t)(kk >> 3) * kGwSbo + (uint32_t)(kk & 7) * 16;
-                    *reinterpret_cast<float*>(a_hi + off) = h;
-                    *reinterpret_cast<float*>(a_lo + off) = x - h;
+                if constexpr (S::kSplit == 1) {
+                    gw_tc_generate<T, 0, T>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
+                } else {
+                    constexpr int AH = (T + 1) / 2;
+                    if (half == 0) gw_tc_generate<T, 0, AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
+                    else gw_tc_generate<T, AH, T - AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
                 }
             }
             const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
@@ -425,28 +460,33 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
             fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
             mbar_arrive(&full_bar[s]);
         }
-        // ---------------- epilogue (first generator group): warp w owns the accumulator rows of cell w ----------------
+        // ---------------- epilogue (first generator group): warp w reads accumulator rows 32 w .. 32 w + 31 ----------------
         if (s == 0) {
             if (n_chunks > 0) ok = ok && mbar_wait(&done_bar, 0u, failed);
             tc_fence_after();
-            const int idx = lane >> 1, i = idx / T, j = idx - i * T;
-            const bool writer = live && (lane & 1) == 0 && i < ci.v1 && j < ci.v2;
-            const int ch = i * ci.tau2 + j;
-            const float sc = writer ? inv[ci.kch0 + ch] : 0.f;
-            float2* out = gW + P.cumW[l] + ci.wch0 + ch;
+            const int row = wq * 32 + lane;
+            const int ec = row / MR, kk = row - ec * MR;   // cell of the block and real row inside it
+            const int idx = kk >> 1, i = idx / T, j = idx - i * T;
+            CellInfo ei{};
+            const bool e_live = ec < S::kCells && cell0 + ec < ncell;
+            if (e_live) ei = P.cell_info[c_begin + cell0 + ec];
+            const bool writer = e_live && (kk & 1) == 0 && i < ei.v1 && j < ei.v2;
+            const int ch = i * ei.tau2 + j;
+            const float sc = writer ? inv[ei.kch0 + ch] : 0.f;
+            float2* out = out_base + P.cumW[l] + ei.wch0 + ch;
             for (int col0 = 0; col0 < N; col0 += 16) {
                 uint32_t rr[16];
                 if (n_chunks > 0 && ok) {
                     tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) rr[c] = 0u;
+                    for (int cc = 0; cc < 16; ++cc) rr[cc] = 0u;
                 }
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float mr = __uint_as_float(rr[2 * c]), mim = __uint_as_float(rr[2 * c + 1]);
+                for (int cc = 0; cc < 8; ++cc) {
+                    const float mr = __uint_as_float(rr[2 * cc]), mim = __uint_as_float(rr[2 * cc + 1]);
                     const float orr = __shfl_xor_sync(0xffffffffu, mr, 1), oim = __shfl_xor_sync(0xffffffffu, mim, 1);
-                    const int to = (col0 >> 1) + c;
+                    const int to = (col0 >> 1) + cc;
                     // even lane = row (k, re), its neighbour = row (k, im)
                     if (writer && to < to_n) out[(int64_t)to * tff] = make_float2((mr + oim) * sc, (mim - orr) * sc);
                 }
@@ -826,13 +866,17 @@ int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const
 // Weight gradient on the tensor cores: tile edge 4, full product, where the forward's tables exist.  Same default
 // threshold as the forward (16 output channels); CGB200_TC_GW=0 / 1 overrides it.
 bool tc_gw_wanted(const cgb200_plan* p) {
-    if (!p->tc_ok || p->d.tile != 4 || p->tc_gw_tiles.empty()) return false;
+    if (!p->tc_gw_ok || p->tc_gw_tiles.empty()) return false;
     if (const char* env = getenv("CGB200_TC_GW")) return env[0] == '1';
-    return p->max_tau_out >= 16;
+    // tile edge 5 is built and tested but stays off by default: at 5 channels (lmax 10, batch 100) it takes 126 us against
+    // 98 us for the CUDA-core kernel - blocks of two cells with at most 21 chunks each spend their time filling and
+    // draining the pipeline
+    return p->d.tile == 4 && p->max_tau_out >= 16;
 }
 
-int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, int G, cudaStream_t st) {
-    constexpr int T = 4;
+template <int T>
+static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
+                          int max_slices, int G, cudaStream_t st) {
     int n_max = 16;
     for (int v : p->tc_npad) n_max = std::max(n_max, v);
     const int n_tiles = (int)p->tc_gw_tiles.size() / 2;
@@ -845,15 +889,32 @@ int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const
         set_error("tensor-core weight gradient: pipeline stages do not fit in shared memory");
         return CGB200_ERR_UNSUPPORTED;
     }
+    // with few blocks (few cells) the sample groups are sliced over several blocks and the partial sums reduced in order
+    int slices = (int)std::min<int64_t>(std::min(max_slices, G), (4 * (int64_t)p->num_sms + n_tiles - 1) / n_tiles);
+    slices = std::max(1, std::min(slices, 65535));
+    if (gw_part == nullptr) slices = 1;
     const size_t smem = n_stages * stage_bytes + cbuf_bytes;
     auto kern = fused_gw_tc_kernel<T>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_GW_TC, st);
-    kern<<<n_tiles, 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv, gW, G, n_max, p->max_n,
-                                                         p->d_status, n_stages);
+    kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
+                                                                       slices > 1 ? gw_part : gW, G, n_max, p->max_n, p->d_status,
+                                                                       n_stages, p->d.w_len);
     launch_end(K_GW_TC, st);
     CGB_CUDA(cudaGetLastError());
+    if (slices > 1) {
+        launch_gw_reduce(p, gw_part, slices, gW, st);
+        CGB_CUDA(cudaGetLastError());
+    }
     return CGB200_OK;
+}
+
+int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
+                 int max_slices, int G, cudaStream_t st) {
+    if (p->d.tile == 4) return launch_gw_tc_t<4>(p, SF, SG, inv, gW, gw_part, max_slices, G, st);
+    if (p->d.tile == 5) return launch_gw_tc_t<5>(p, SF, SG, inv, gW, gw_part, max_slices, G, st);
+    set_error("internal: tensor-core weight gradient asked for an unsupported tile edge");
+    return CGB200_ERR_UNSUPPORTED;
 }
 
 // Input gradient with phase 1 on the tensor cores: tile edge 4, full product, 2 lmax + 1 <= 64 (the gFF tile of an entry

@@ -409,15 +409,20 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         }
     }
 
-    // tensor-core forward tables
-    p->tc_ok = !dw && has_out && (T == 2 || T == 4) && p->max_tau_out >= 4 && p->max_tau_out <= 64 && 2 * lmax + 1 <= 128;
+    // tensor-core tables: forward (tile edge 2 or 4) and weight gradient (tile edge 4 or 5)
+    const bool tc_common = !dw && has_out && p->max_tau_out >= 4 && p->max_tau_out <= 64 && 2 * lmax + 1 <= 128;
+    p->tc_ok = tc_common && (T == 2 || T == 4);
+    p->tc_gw_ok = tc_common && (T == 4 || T == 5);
+    if (p->tc_ok || p->tc_gw_ok) {
+        p->tc_npad.assign(L1, 0);
+        for (int l = 0; l < L1; ++l) p->tc_npad[l] = p->tO[l] > 0 ? ((2 * p->tO[l] + 15) / 16) * 16 : 0;
+        if ((rc = upload(p, p->tc_npad, &p->d_tc_npad))) return rc;
+    }
     if (p->tc_ok) {
         const int Kc = 2 * T * T;
-        p->tc_npad.assign(L1, 0);
         p->tc_pack_off.assign(L1 + 1, 0);
         std::vector<std::pair<int, int>> order;   // (cells, l)
         for (int l = 0; l < L1; ++l) {
-            p->tc_npad[l] = p->tO[l] > 0 ? ((2 * p->tO[l] + 15) / 16) * 16 : 0;
             const int64_t ncell = p->cell_begin[l + 1] - p->cell_begin[l];
             p->tc_pack_off[l + 1] = p->tc_pack_off[l] + ncell * 2 * p->tc_npad[l] * Kc;
             if (p->tO[l] > 0) order.push_back({(int)ncell, l});
@@ -428,20 +433,20 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
                 p->tc_tiles.push_back(o.second);
                 p->tc_tiles.push_back(m0);
             }
-        if ((rc = upload(p, p->tc_npad, &p->d_tc_npad))) return rc;
         if ((rc = upload(p, p->tc_pack_off, &p->d_tc_pack_off))) return rc;
         if ((rc = upload(p, p->tc_tiles, &p->d_tc_tiles))) return rc;
-        if (T == 4) {   // weight gradient: blocks of four cells, degrees with the longest contraction (2l+1) first
-            for (int l = L1 - 1; l >= 0; --l) {
-                if (p->tO[l] == 0) continue;
-                const int ncell = p->cell_begin[l + 1] - p->cell_begin[l];
-                for (int c0 = 0; c0 < ncell; c0 += 4) {
-                    p->tc_gw_tiles.push_back(l);
-                    p->tc_gw_tiles.push_back(c0);
-                }
+    }
+    if (p->tc_gw_ok) {   // weight gradient: blocks of 128 / (2 T^2) cells, degrees with the longest contraction (2l+1) first
+        const int per_block = 128 / (2 * T * T);
+        for (int l = L1 - 1; l >= 0; --l) {
+            if (p->tO[l] == 0) continue;
+            const int ncell = p->cell_begin[l + 1] - p->cell_begin[l];
+            for (int c0 = 0; c0 < ncell; c0 += per_block) {
+                p->tc_gw_tiles.push_back(l);
+                p->tc_gw_tiles.push_back(c0);
             }
-            if ((rc = upload(p, p->tc_gw_tiles, &p->d_tc_gw_tiles))) return rc;
         }
+        if ((rc = upload(p, p->tc_gw_tiles, &p->d_tc_gw_tiles))) return rc;
     }
 
     // which triples use fragment l as first / second operand (for the gather-style input gradient)

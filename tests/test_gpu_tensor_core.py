@@ -87,8 +87,16 @@ def _weight_gradient(plan, case, bn, tc):
         os.environ.pop("CGB200_TC_GW", None)
 
 
+GW_CASES = CASES + [
+    ([5] * 6, [5] * 6, 40, "default"),            # tile edge 5: two cells per block, generator warps split the rows 3 + 2
+    ([5] * 11, [5] * 11, 100, "default"),         # the benchmark layer: sample groups sliced over blocks, partial sums reduced
+    ([10] * 4, [7] * 4, 33, "default"),
+    ([5, 3, 10, 5, 1], [4, 5, 2, 7, 5], 70, "mst"),
+]
+
+
 @pytest.mark.parametrize("bn", [False, True])
-@pytest.mark.parametrize("taus,tau_out,B,mode", CASES)
+@pytest.mark.parametrize("taus,tau_out,B,mode", GW_CASES)
 def test_tensor_core_weight_gradient(taus, tau_out, B, mode, bn):
     """gW from the tcgen05 weight-gradient kernel (3xTF32, contraction over samples and m in tensor memory) against the
     oracle's autograd gradient and against the CUDA-core kernel."""
@@ -96,8 +104,8 @@ def test_tensor_core_weight_gradient(taus, tau_out, B, mode, bn):
     import cg_oracle as o
     case = make_case(taus, tau_out, B, mode, seed=53)
     plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
-    if plan.tile != 4:
-        pytest.skip(f"tile edge {plan.tile}: the tensor-core weight gradient is built for 4")
+    if plan.tile not in (4, 5):
+        pytest.skip(f"tile edge {plan.tile}: the tensor-core weight gradient is built for 4 and 5")
     t_ff, _ = o.tau_ff_and_offsets(case["lmax"], taus, case["llls"])
     _, _, gW_want, _ = oracle_layer(case, bn, False, cnt=2.0)
     gW_tc = _weight_gradient(plan, case, bn, tc=True)
