@@ -812,12 +812,12 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 // Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
-// when the mixing dominates: measured on B200, 1.2x faster than the CUDA-core forward at 16 output channels, 2.2-2.7x at
-// 32 and 64, slower below 16.  CGB200_TC=0 / 1 overrides the default.
+// when the mixing dominates: measured on B200 against the CUDA-core forward (packing included) 1.25x faster at 12 and 16
+// output channels, 2.2-2.7x at 32 and 64, 8 % slower at 8.  CGB200_TC=0 / 1 overrides the default.
 bool tc_wanted(const cgb200_plan* p) {
     if (!p->tc_ok) return false;
     if (const char* env = getenv("CGB200_TC")) return env[0] == '1';
-    return p->max_tau_out >= 16;
+    return p->max_tau_out >= 12;
 }
 
 int64_t tc_pack_floats(const cgb200_plan* p) { return p->tc_ok ? p->tc_pack_off.back() : 0; }
@@ -868,10 +868,11 @@ int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const
 bool tc_gw_wanted(const cgb200_plan* p) {
     if (!p->tc_gw_ok || p->tc_gw_tiles.empty()) return false;
     if (const char* env = getenv("CGB200_TC_GW")) return env[0] == '1';
-    // tile edge 5 is built and tested but stays off by default: at 5 channels (lmax 10, batch 100) it takes 126 us against
-    // 98 us for the CUDA-core kernel - blocks of two cells with at most 21 chunks each spend their time filling and
+    // tile edge 4: faster than the CUDA-core kernel at every width measured (2x at 8 output channels, 2.9x at 12, 3.3x at
+    // 16, 5-8x at 32 and 64).  Tile edge 5 is built and tested but stays off by default: at 5 channels (lmax 10, batch
+    // 100) it takes 126 us against 98 us - blocks of two cells with at most 21 chunks each spend their time filling and
     // draining the pipeline
-    return p->d.tile == 4 && p->max_tau_out >= 16;
+    return p->d.tile == 4;
 }
 
 template <int T>
