@@ -280,3 +280,21 @@ def test_layer_runs_inside_a_cuda_graph():
         torch.cuda.synchronize()
         for a, b in zip(got, (O2, gF2, gW2)):
             assert np.array_equal(a, b.cpu().numpy())
+
+
+@pytest.mark.parametrize("taus,tau_out,B", [([3, 2, 2], [2, 3, 1], 4800), ([5] * 3, [5] * 3, 4770)])
+def test_more_sample_groups_than_sms(taus, tau_out, B):
+    """A batch of more than 148 x 32 samples: more sample groups than SMs, so the forward leaves its persistent
+    shared-memory variant for the row-per-block one, and every kernel's group loops and group slices run long."""
+    from cgnet_b200 import _lib
+    case = make_case(taus, tau_out, B, "default", seed=18)
+    plan = plan_for(case)
+    O_want, gF_want, gW_want, stds_want = oracle_layer(case, True, True, cnt=3.0)
+    F, W, gO, stds = t(case["F"]), t(case["W"]), t(case["gO"]), t(case["stds"])
+    O = plan.layer_fwd(F, W, stds, 3.0, 1e-5, _lib.FN_PRESENT | _lib.FN_UPDATE)
+    gF, gW = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT, gO)
+    torch.cuda.synchronize()
+    assert_fragments_close(O.cpu().numpy(), O_want, tau_out, "O, large batch")
+    assert_fragments_close(gF.cpu().numpy(), gF_want, taus, "gF, large batch")
+    assert_weights_close(gW.cpu().numpy(), gW_want, case["t_ff"], tau_out, "gW, large batch")
+    np.testing.assert_allclose(stds.cpu().numpy(), stds_want, rtol=2e-5, atol=1e-7)
