@@ -24,6 +24,7 @@ SHAPES = [
     ([8] * 6, [8] * 6, 32, "default"),                 # BASELINE config 1 shape
     ([6, 0, 3, 2], [2, 2, 0, 3], 4, "default"),        # empty fragments on both sides
     ([7, 6, 5], [20, 3, 17], 3, "default"),            # more than 16 output channels, ragged tiles
+    ([2] * 21, [2] * 21, 5, "mst"),                    # lmax = 20: fragments of 41 rows
 ]
 
 
