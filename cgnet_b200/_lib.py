@@ -25,6 +25,8 @@ SIGNATURES = {
     "cgb200_plan_query": (ctypes.c_int, [vp, ctypes.c_int, c_i64p]),
     "cgb200_plan_t_ff": (ctypes.c_int, [vp, c_i32p]),
     "cgb200_plan_status": (ctypes.c_int, [vp, c_i32p]),
+    "cgb200_plan_set_option": (ctypes.c_int, [vp, ctypes.c_int, ctypes.c_int]),
+    "cgb200_plan_get_option": (ctypes.c_int, [vp, ctypes.c_int, c_i32p]),
     "cgb200_plan_cg_table": (vp, [vp]),
     "cgb200_cg_product_fwd": (ctypes.c_int, [vp, vp, vp, ctypes.c_int64, vp]),
     "cgb200_cg_product_bwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, vp]),
@@ -33,6 +35,7 @@ SIGNATURES = {
     "cgb200_layer_fwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_int, vp, vp, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
+    "cgb200_layer_fwd_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
     "cgb200_layer_fwd_static": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp]),
     "cgb200_launch_count": (ctypes.c_int64, [ctypes.c_int]),
     "cgb200_kernel_count": (ctypes.c_int, []),
@@ -44,6 +47,14 @@ SIGNATURES = {
 Q_N_F, Q_N_FF, Q_N_O, Q_W_LEN, Q_SUM_TFF, Q_CG_LEN, Q_N_TRIPLES, Q_TILE = range(8)
 FN_PRESENT, FN_UPDATE = 0x1, 0x2
 PLAN_DEPTHWISE = 0x1
+AUTO = -1
+(OPT_TC_FWD, OPT_TC_GRAD_W, OPT_TC_GRAD_F, OPT_TC_STAGES, OPT_FWD_SLAB, OPT_GRAD_F_SPLIT, OPT_STATS_SPLIT, OPT_BWD_SERIAL,
+ OPT_WAIT_POLLS, OPT_TEST_IDLE_MMA) = range(10)
+
+
+def plan_tile_flag(tile):
+    """Plan-creation flag that forces the channel-tile edge (CGB200_PLAN_TILE in the header)."""
+    return (int(tile) & 0xF) << 8
 
 
 def load():

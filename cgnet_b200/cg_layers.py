@@ -30,7 +30,7 @@ from torch import nn
 from . import _lib
 from . import cgutils as CGutils
 
-__all__ = ["CGBN_cuda", "CG_woFilter_cuda", "MyBatchNormWeightMM_cuda", "precomputeCG", "Plan", "get_plan"]
+__all__ = ["CGBN_cuda", "CG_woFilter_cuda", "MyBatchNormWeightMM_cuda", "precomputeCG", "Plan", "PlanShapes", "get_plan"]
 
 
 def _stream_ptr(device):
@@ -49,17 +49,59 @@ def _check_cuda_f32(t, name):
     return t.contiguous()
 
 
-class Plan:
+def _expect(t, name, shape_tail, device, allow_none=False):
+    """Raise unless ``t`` is a contiguous float32 tensor on ``device`` whose trailing dimensions are ``shape_tail``
+    (the leading one is the batch).  Runs before any pointer reaches the library: a wrong length or a tensor on
+    another GPU would otherwise be an out-of-bounds or peer access inside a kernel."""
+    if t is None:
+        if allow_none:
+            return
+        raise RuntimeError(f"{name} is None")
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a tensor, got {type(t).__name__}")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32, got {t.dtype}")
+    if t.device != device:
+        raise RuntimeError(f"{name} lives on {t.device}, the plan on {device}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if tuple(t.shape[t.dim() - len(shape_tail):]) != tuple(shape_tail) or t.dim() > len(shape_tail) + 1:
+        raise RuntimeError(f"{name} has shape {tuple(t.shape)}, expected (..., {', '.join(str(x) for x in shape_tail)})")
+
+
+class PlanShapes:
+    """The sizes a plan fixes and the argument checks that follow from them (kept apart from the device handle so that
+    the checks can be exercised without a GPU)."""
+
+    def __init__(self, device, n_F, n_FF, n_O, w_len, sum_tff):
+        self.device = torch.device(device)
+        self.n_F, self.n_FF, self.n_O, self.w_len, self.sum_tff = int(n_F), int(n_FF), int(n_O), int(w_len), int(sum_tff)
+
+    def check_weights(self, W, stds, flags):
+        _expect(W, "W", (self.w_len, 2), self.device)
+        if flags & _lib.FN_PRESENT:
+            _expect(stds, "bn_stds", (self.sum_tff,), self.device)
+
+    def check_batch(self, B, **named):
+        """named: name=(tensor, per-sample length); all must share the batch size B."""
+        for name, (t, n) in named.items():
+            _expect(t, name, (n, 2), self.device)
+            if t.dim() != 3 or t.shape[0] != B:
+                raise RuntimeError(f"{name} has shape {tuple(t.shape)}, expected ({B}, {n}, 2)")
+
+
+class Plan(PlanShapes):
     """Owner of one ``cgb200_plan`` handle: index tables, CG table and work lists for a fixed
     (lmax, tau_in, tau_out, triple list) on one device."""
 
-    def __init__(self, lmax, taus, tau_out, llls, device, depthwise=False):
+    def __init__(self, lmax, taus, tau_out, llls, device, depthwise=False, tile=0):
         lib = _lib.load()
-        self.device = torch.device(device)
-        if self.device.type != "cuda":
+        device = torch.device(device)
+        if device.type != "cuda":
             raise RuntimeError("cgnet_b200 plans live on a CUDA device")
-        if self.device.index is None:
-            self.device = torch.device("cuda", torch.cuda.current_device())
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
         self.lmax = int(lmax)
         if self.lmax > lib.cgb200_max_lmax():
             raise AssertionError(f"Does not support lmax={lmax}")
@@ -67,16 +109,13 @@ class Plan:
         a_in = _lib.i32(taus)
         a_out = _lib.i32(tau_out) if tau_out is not None else None
         a_l = _lib.i32(llls)
+        flags = (_lib.PLAN_DEPTHWISE if depthwise else 0) | _lib.plan_tile_flag(tile)
         with torch.cuda.device(self.device):
-            _lib.check(lib.cgb200_plan_create(handle, self.lmax, a_in, a_out, a_l, len(llls),
-                                              _lib.PLAN_DEPTHWISE if depthwise else 0), "cgb200_plan_create")
+            _lib.check(lib.cgb200_plan_create(handle, self.lmax, a_in, a_out, a_l, len(llls), flags), "cgb200_plan_create")
         self.handle = handle
         self._finalizer = weakref.finalize(self, lib.cgb200_plan_destroy, handle)
-        self.n_F = self.query(_lib.Q_N_F)
-        self.n_FF = self.query(_lib.Q_N_FF)
-        self.n_O = self.query(_lib.Q_N_O)
-        self.w_len = self.query(_lib.Q_W_LEN)
-        self.sum_tff = self.query(_lib.Q_SUM_TFF)
+        super().__init__(self.device, self.query(_lib.Q_N_F), self.query(_lib.Q_N_FF), self.query(_lib.Q_N_O),
+                         self.query(_lib.Q_W_LEN), self.query(_lib.Q_SUM_TFF))
         self.tile = self.query(_lib.Q_TILE)
 
     def query(self, what):
@@ -89,9 +128,28 @@ class Plan:
         _lib.check(_lib.load().cgb200_plan_t_ff(self.handle, out), "cgb200_plan_t_ff")
         return list(out)
 
-    # ---- thin wrappers over the C ABI; every tensor must already be contiguous float32 on self.device ----
+    def set_option(self, option, value):
+        """Select a kernel variant for this plan (``_lib.OPT_*``; ``_lib.AUTO`` restores the library's default)."""
+        _lib.check(_lib.load().cgb200_plan_set_option(self.handle, int(option), int(value)), "cgb200_plan_set_option")
+
+    def get_option(self, option):
+        v = _lib.ctypes.c_int32()
+        _lib.check(_lib.load().cgb200_plan_get_option(self.handle, int(option), v), "cgb200_plan_get_option")
+        return int(v.value)
+
+    def check_status(self):
+        """Raise if a kernel of this plan gave up on a bounded device-side wait since the last check (its outputs were
+        then filled with NaN).  Synchronises the device: call it once per epoch or checkpoint, not per step."""
+        st = _lib.ctypes.c_int32(-1)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().cgb200_plan_status(self.handle, st), "cgb200_plan_status")
+        if st.value != 0:
+            raise RuntimeError("a cgnet_b200 tensor-core kernel gave up on a bounded wait; the outputs of that call are NaN")
+
+    # ---- thin wrappers over the C ABI: arguments are checked against the plan's sizes and device before any launch ----
     def cg_product_fwd(self, F):
         B = F.shape[0]
+        self.check_batch(B, F=(F, self.n_F))
         FF = torch.empty(B, self.n_FF, 2, device=F.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().cgb200_cg_product_fwd(self.handle, _ptr(F), _ptr(FF), B, _stream_ptr(self.device)),
@@ -99,6 +157,7 @@ class Plan:
         return FF
 
     def cg_product_bwd(self, F, gFF):
+        self.check_batch(F.shape[0], F=(F, self.n_F), gFF=(gFF, self.n_FF))
         gF = torch.empty_like(F)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().cgb200_cg_product_bwd(self.handle, _ptr(F), _ptr(gFF), _ptr(gF), F.shape[0],
@@ -107,6 +166,8 @@ class Plan:
 
     def fn_wmm_fwd(self, FF, W, stds, cnt, eps, flags):
         B = FF.shape[0]
+        self.check_batch(B, FF=(FF, self.n_FF))
+        self.check_weights(W, stds, flags)
         O = torch.empty(B, self.n_O, 2, device=FF.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().cgb200_fn_wmm_fwd(self.handle, _ptr(FF), _ptr(W), _ptr(stds), cnt, eps, flags, _ptr(O), B,
@@ -114,6 +175,8 @@ class Plan:
         return O
 
     def fn_wmm_bwd(self, gO, FF, W, stds, eps, flags):
+        self.check_batch(FF.shape[0], FF=(FF, self.n_FF), gO=(gO, self.n_O))
+        self.check_weights(W, stds, flags)
         gFF = torch.empty_like(FF)
         gW = torch.empty_like(W)
         with torch.cuda.device(self.device):
@@ -122,22 +185,27 @@ class Plan:
                        "cgb200_fn_wmm_bwd")
         return gFF, gW
 
-    def _workspace(self, B):
-        n = int(_lib.load().cgb200_layer_workspace_bytes(self.handle, B))
+    def _workspace(self, B, fwd_only=False):
+        lib = _lib.load()
+        n = int((lib.cgb200_layer_fwd_workspace_bytes if fwd_only else lib.cgb200_layer_workspace_bytes)(self.handle, B))
         if n < 0:
             _lib.check(1, "cgb200_layer_workspace_bytes")
         return torch.empty(max(n, 256), dtype=torch.uint8, device=self.device), n
 
     def layer_fwd(self, F, W, stds, cnt, eps, flags):
         B = F.shape[0]
+        self.check_batch(B, F=(F, self.n_F))
+        self.check_weights(W, stds, flags)
         O = torch.empty(B, self.n_O, 2, device=F.device, dtype=torch.float32)
-        ws, n = self._workspace(B)
+        ws, n = self._workspace(B, fwd_only=True)
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().cgb200_layer_fwd(self.handle, _ptr(F), _ptr(W), _ptr(stds), cnt, eps, flags, _ptr(O), B,
                                                     _ptr(ws), n, _stream_ptr(self.device)), "cgb200_layer_fwd")
         return O
 
     def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True):
+        self.check_batch(F.shape[0], F=(F, self.n_F), gO=(gO, self.n_O))
+        self.check_weights(W, stds, flags)
         gF = torch.empty_like(F) if need_gF else None
         gW = torch.empty_like(W)
         ws, n = self._workspace(F.shape[0])
@@ -149,17 +217,18 @@ class Plan:
 
 
 @functools.lru_cache(maxsize=64)
-def _cached_plan(lmax, taus, tau_out, llls, device, depthwise):
-    return Plan(lmax, taus, tau_out, llls, device, depthwise)
+def _cached_plan(lmax, taus, tau_out, llls, device, depthwise, tile):
+    return Plan(lmax, taus, tau_out, llls, device, depthwise, tile)
 
 
-def get_plan(lmax, taus, tau_out, llls, device, depthwise=False):
-    """Plans are immutable, so modules with the same shape on the same device share one."""
+def get_plan(lmax, taus, tau_out, llls, device, depthwise=False, tile=0):
+    """Modules with the same shape on the same device share one plan (its tables never change; its kernel-selection
+    options are shared with it).  ``tile`` forces the channel-tile edge, 0 leaves the choice to the library."""
     dev = torch.device(device)
     if dev.type == "cuda" and dev.index is None:
         dev = torch.device("cuda", torch.cuda.current_device())
     return _cached_plan(int(lmax), tuple(int(t) for t in taus), None if tau_out is None else tuple(int(t) for t in tau_out),
-                        tuple(int(c) for c in llls), str(dev), bool(depthwise))
+                        tuple(int(c) for c in llls), str(dev), bool(depthwise), int(tile))
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -322,6 +391,8 @@ class MyBatchNormWeightMM_cuda(nn.Module):
             state_dict[key] = self.bn_cnt_buf.detach().clone()
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
         self._cnt_cache = None
+        # the kernels take eps as a host float: follow the checkpoint's value (the reference passes the parameter itself)
+        self._eps = float(self.bn_eps.detach().cpu().item())
 
     def reset_parameters(self):
         if self._init_method not in {"debug", "random"}:

@@ -14,6 +14,9 @@
 namespace cgb200 {
 
 constexpr int kMaxLmax = 511;        // same ceiling the reference asserts (cudaCG_sparse.cu:23)
+// Dynamic shared memory a launch may ask for: the 227 KB a block can own less 1 KB for the kernels' static __shared__
+// variables (barriers, counters, reduction scratch), which count against the same limit.
+constexpr size_t kMaxDynSmem = 226 * 1024;
 constexpr int kMaxTile = 6;          // largest channel-tile edge the register-tiled kernels are instantiated for
 
 // One admissible (l, l1, l2) triple with everything a kernel needs to find its operands and its outputs.
@@ -185,6 +188,8 @@ bool timing_active();   // per-kernel event timing is on (cgb200_timing_enable)
 // tensor-core forward (fused_tc.cu)
 struct cgb200_plan;
 namespace cgb200 {
+constexpr uint32_t kDefaultWaitPolls = 4000000;   // polls of mbarrier.try_wait before a bounded wait gives up
+inline uint32_t wait_polls(const cgb200_plan* p);
 bool tc_wanted(const cgb200_plan* p);
 bool tc_gw_wanted(const cgb200_plan* p);
 bool tc_gf_wanted(const cgb200_plan* p);
@@ -203,6 +208,8 @@ struct cgb200_plan {
     int device = 0;
     int num_sms = 148;
     int flags = 0;
+    int opt[CGB200_OPT_COUNT];        // kernel selection (cgb200_plan_set_option); CGB200_AUTO = the measured default
+    cgb200_plan() { for (int& o : opt) o = CGB200_AUTO; }
     cgb200::PlanDev d{};
     std::vector<int> tF, tO, tFF, cumT;
     std::vector<int64_t> cumF, cumFF, cumO, cumW;
@@ -262,6 +269,13 @@ struct cgb200_plan {
     mutable cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     mutable std::mutex side_mutex;
 };
+
+namespace cgb200 {
+inline uint32_t wait_polls(const cgb200_plan* p) {
+    const int v = p->opt[CGB200_OPT_WAIT_POLLS];
+    return v > 0 ? (uint32_t)v : kDefaultWaitPolls;
+}
+}  // namespace cgb200
 
 #ifdef __CUDACC__
 namespace cgb200 {

@@ -18,8 +18,6 @@
 //   grad_f        gF via gFF tiles built from gO and W in registers, contracted with conj(F) and C into per-warp
 //                 shared-memory accumulators that one block owns
 #include <cuda_pipeline.h>
-#include <stdlib.h>
-
 #include <algorithm>
 
 #include "common.cuh"
@@ -809,12 +807,8 @@ int gw_slices(const cgb200_plan* p, int64_t G) {
 }
 
 // Phase-2 units of the input-gradient kernel: whole rows (default, faster at every shape measured) or rows split into
-// two channel groups (CGB200_GF_SPLIT=1).  The plan holds a warp assignment for both.
-bool gf_split(const cgb200_plan* p) {
-    (void)p;
-    const char* env = getenv("CGB200_GF_SPLIT");
-    return env && env[0] == '1';
-}
+// two channel groups (CGB200_OPT_GRAD_F_SPLIT).  The plan holds a warp assignment for both.
+bool gf_split(const cgb200_plan* p) { return p->opt[CGB200_OPT_GRAD_F_SPLIT] == 1; }
 
 // Splitting level of the input-gradient kernel: the coarsest one that gives every SM about two blocks.
 int gf_level(const cgb200_plan* p, int64_t G) {
@@ -825,33 +819,37 @@ int gf_level(const cgb200_plan* p, int64_t G) {
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
-Workspace carve(const cgb200_plan* p, int64_t B, void* base) {
+// Layout of the caller's workspace.  The forward needs only the input slab, the norm factors, the row counters and
+// (tensor-core forward) the packed weights; the backward adds the slab of the output gradient and the partial sums.
+// Both layouts start at the same base and nothing in the workspace survives a call, so a buffer sized for the larger
+// one serves both.
+Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = false) {
     const int64_t G = (B + 31) / 32;
-    Workspace w;
+    Workspace w{};
     int64_t off = 0;
     char* c = (char*)base;
     w.SF = (float2*)(c + off);
     off += align256(std::max<int64_t>(p->d.nSF, 1) * G * 32 * (int64_t)sizeof(float2));
     w.SG = (float2*)(c + off);
-    off += align256(std::max<int64_t>(p->d.nSO, 1) * G * 32 * (int64_t)sizeof(float2));
+    if (!fwd_only) off += align256(std::max<int64_t>(p->d.nSO, 1) * G * 32 * (int64_t)sizeof(float2));
     w.inv = (float*)(c + off);
     off += align256(std::max<int64_t>(p->d.sum_tff, 1) * (int64_t)sizeof(float));
     w.counters = (int*)(c + off);
     off += align256(G * (int64_t)sizeof(int));
     w.gf_level = gf_level(p, G);
     w.gf_part = (float2*)(c + off);
-    if (p->gf2_max_parts[w.gf_level] > 1)
+    if (!fwd_only && p->gf2_max_parts[w.gf_level] > 1)
         off += align256((int64_t)p->gf2_max_parts[w.gf_level] * B * std::max<int64_t>(p->d.n_F, 1) * (int64_t)sizeof(float2));
     w.tc_pack = (float*)(c + off);
     if (tc_wanted(p)) off += align256(tc_pack_floats(p) * (int64_t)sizeof(float));
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
-    if (w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
+    if (!fwd_only && w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
     w.bytes = off;
     return w;
 }
 
-int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_bytes) {
+int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_bytes, bool fwd_only) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(p->d.has_out, "the plan was created without tau_out");
     CGB_REQUIRE(B >= 0 && B <= 65535 * 32, "batch size out of range (at most 2097120 samples per call of the fused layer)");
@@ -859,7 +857,7 @@ int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_byte
     CGB_CUDA(cudaGetDevice(&dev));
     CGB_REQUIRE(dev == p->device, "the plan belongs to another CUDA device than the current one");
     if (B > 0) {
-        const int64_t need = carve(p, B, nullptr).bytes;
+        const int64_t need = carve(p, B, nullptr, fwd_only).bytes;
         if (ws == nullptr || ws_bytes < need) {
             set_error("workspace too small: need " + std::to_string(need) + " bytes");
             return CGB200_ERR_WORKSPACE;
@@ -915,9 +913,17 @@ int64_t cgb200_layer_workspace_bytes(const cgb200_plan* p, int64_t B) {
     return carve(p, std::max<int64_t>(B, 1), nullptr).bytes;
 }
 
+int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* p, int64_t B) {
+    if (p == nullptr || B < 0) {
+        set_error("null plan or negative batch");
+        return -1;
+    }
+    return carve(p, std::max<int64_t>(B, 1), nullptr, true).bytes;
+}
+
 int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float* stds, float cnt, float eps, int flags,
                      float* O, int64_t B, void* workspace, int64_t workspace_bytes, void* stream) {
-    int rc = check_layer(p, B, workspace, workspace_bytes);
+    int rc = check_layer(p, B, workspace, workspace_bytes, true);
     if (rc) return rc;
     const bool fn = (flags & CGB200_FN_PRESENT) != 0;
     const bool update = fn && (flags & CGB200_FN_UPDATE);
@@ -927,7 +933,7 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     CGB_REQUIRE(al8(F) && al8(W) && al8(O), "buffers must be 8-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     const int G = (int)((B + 31) / 32);
-    Workspace ws = carve(p, B, workspace);
+    Workspace ws = carve(p, B, workspace, true);
     const int T = p->d.tile;
 
     PrepJob jf{(const float2*)F, ws.SF, p->d.n_F, p->d.cumF, p->d.cumSF, p->d.tF, p->d.nSF, has_pad(p->tF, T) ? 1 : 0};
@@ -939,8 +945,8 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
         launch_begin(K_STATS, st);
         // tile edge 5 and 6 need ~200 registers for a whole tile (one block of 8 warps per SM): two blocks per cell, each
         // with half the tile's rows and under 128 registers, put two blocks on an SM
-        static const int split_env = [] { const char* e = getenv("CGB200_STATS_SPLIT"); return e ? atoi(e) : -1; }();
-        const bool split_rows = !p->d.depthwise && (split_env >= 0 ? split_env != 0 : T >= 5);
+        const int split_opt = p->opt[CGB200_OPT_STATS_SPLIT];
+        const bool split_rows = !p->d.depthwise && (split_opt >= 0 ? split_opt != 0 : T >= 5);
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = split_rows ? fused_stats_kernel<TT, DD, true> : fused_stats_kernel<TT, DD, false>;
             if (band > 40 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band));
@@ -961,10 +967,10 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     const size_t slab_bytes = (size_t)p->d.nSF * 32 * sizeof(float2);
     const size_t smem_slab = slab_bytes + (size_t)kSlabWarps * (red_to * 32 * sizeof(float2) + stage_bytes);
     const size_t smem_rows = (size_t)kFwdWarps * (red_to * 32 * sizeof(float2) + stage_bytes);
-    const char* force = getenv("CGB200_FWD");
-    const bool fits = smem_slab <= 227 * 1024 && G <= p->num_sms;
-    const bool use_slab = fits && (force ? force[0] == 's' : true);
-    if (smem_rows > 227 * 1024) {
+    // 227 KB per block less the kernels' few bytes of static shared memory
+    const bool fits = smem_slab <= kMaxDynSmem && G <= p->num_sms;
+    const bool use_slab = fits && p->opt[CGB200_OPT_FWD_SLAB] != 0;
+    if (smem_rows > kMaxDynSmem) {
         set_error("lmax too large for the fused forward kernel");
         return CGB200_ERR_UNSUPPORTED;
     }
@@ -993,7 +999,7 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
 int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const float* stds, float eps, int flags,
                      const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,
                      void* stream) {
-    int rc = check_layer(p, B, workspace, workspace_bytes);
+    int rc = check_layer(p, B, workspace, workspace_bytes, false);
     if (rc) return rc;
     const bool fn = (flags & CGB200_FN_PRESENT) != 0;
     CGB_REQUIRE(!fn || stds != nullptr, "stds is null although CGB200_FN_PRESENT is set");
@@ -1028,7 +1034,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;
-        if (smem > 227 * 1024) {
+        if (smem > kMaxDynSmem) {
             set_error("lmax too large for the fused weight-gradient kernel");
             return CGB200_ERR_UNSUPPORTED;
         }
@@ -1078,11 +1084,11 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
                                  2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
             const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
-            if (fixed + per_m > 227 * 1024) {
+            if (fixed + per_m > kMaxDynSmem) {
                 set_error("lmax or tau_out too large for the fused input-gradient kernel");
                 return CGB200_ERR_UNSUPPORTED;
             }
-            const size_t budget = 227 * 1024;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
+            const size_t budget = kMaxDynSmem;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
             const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
             const size_t smem = fixed + (size_t)Mc * per_m;
             launch_begin(K_GF, st);
@@ -1108,8 +1114,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     };
 
     const bool want_gw = n_tasks > 0;
-    static const bool serial_env = [] { const char* e = getenv("CGB200_BWD_SERIAL"); return e && atoi(e) != 0; }();
-    if (!(want_gw && want_gf) || timing_active() || serial_env) {
+    if (!(want_gw && want_gf) || timing_active() || p->opt[CGB200_OPT_BWD_SERIAL] == 1) {
         if (want_gw && (rc = enqueue_gw(st))) return rc;
         if (want_gf && (rc = enqueue_gf())) return rc;
         return CGB200_OK;
@@ -1156,10 +1161,10 @@ int cgb200_layer_fwd_static(const cgb200_plan* p, const float* F, const float* W
                             int flags, float* O, int64_t B, void* stream) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(B >= 0, "negative batch size");
-    const int64_t need = cgb200_layer_workspace_bytes(p, B);
+    const int64_t need = cgb200_layer_fwd_workspace_bytes(p, B);   // the forward's own need, not the backward's
     if (need < 0) return CGB200_ERR_ARGUMENT;
     if (need > (int64_t)CGB200_STATIC_SCRATCH_BYTES) {
-        set_error("cgb200_layer_fwd_static: this plan and batch need " + std::to_string(need) +
+        set_error("cgb200_layer_fwd_static: the forward of this plan and batch needs " + std::to_string(need) +
                   " bytes of scratch, the built-in array holds " + std::to_string((int64_t)CGB200_STATIC_SCRATCH_BYTES) +
                   "; use a smaller batch or cgb200_layer_fwd with a caller-provided workspace");
         return CGB200_ERR_WORKSPACE;

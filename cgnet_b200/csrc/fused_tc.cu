@@ -23,7 +23,6 @@
 // Every wait is bounded: a wait that runs out sets a flag in shared memory and a status word in global memory, all
 // roles then skip to the end, tensor memory is released and the kernel returns.
 #include <cuda_pipeline.h>
-#include <stdlib.h>
 
 #include <algorithm>
 
@@ -33,7 +32,7 @@ namespace cgb200 {
 
 constexpr int kTcMaxStages = 5;   // pipeline stages = generator groups; the launch picks as many as shared memory holds
 constexpr int kTcMaxThreads = 32 * (4 * kTcMaxStages + 1);
-constexpr uint32_t kTcSpinLimit = 4000000;   // polls of mbarrier.try_wait before a wait gives up
+constexpr uint32_t kNaNBits = 0x7fc00000u;   // what a block that gave up writes into the outputs it owns
 
 // ---- thin PTX wrappers --------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -47,10 +46,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity; false when the limit ran out or another role already failed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+// Bounded wait for the phase with the given parity; false when the limit (polls of mbarrier.try_wait) ran out or another
+// role already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kTcSpinLimit; ++spin) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -60,10 +60,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok) return true;
-        if ((spin & 1023) == 1023 && *failed) return false;
+        if ((spin & 255) == 255 && *failed) return false;
     }
     *failed = 1;
     return false;
+}
+// The same wait for a whole warp: every lane polls, and the warp gives up together if any lane did, so that the code
+// after it (warp-synchronous generator steps, tcgen05.ld.sync.aligned) never runs with diverged lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, failed, limit) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -174,7 +179,7 @@ template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
                     const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O, int B, int n_max,
-                    int max_n, int* __restrict__ status, int n_stages) {
+                    int max_n, int* __restrict__ status, int n_stages, uint32_t wait_limit, int idle_mma) {
     constexpr int Kc = 2 * T * T;            // real K extent of one cell
     constexpr int NV = T * T;
     constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
@@ -229,7 +234,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
         const uint32_t b_bytes = (uint32_t)(2 * N * Kc * sizeof(float));
         bool ok = true;
         for (int k = s, u = 0; k < ncell && ok; k += n_stages, ++u) {
-            if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
+            if (u > 0) ok = mbar_wait_warp(&empty_bar[s], (uint32_t)((u - 1) & 1), failed, wait_limit);
             if (!ok) break;
             if (wq == 0 && lane == 0) {
                 mbar_expect_tx(&full_bar[s], b_bytes);
@@ -263,15 +268,15 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
         if (s == 0) {
             const int b = g * 32 + lane;
             float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
-            if (ncell > 0) ok = ok && mbar_wait(&done_bar, 0u, failed);
+            if (ncell > 0) ok = mbar_wait_warp(&done_bar, 0u, failed, wait_limit) && ok;   // warp-uniform
             tc_fence_after();
             for (int col0 = 0; col0 < N; col0 += 16) {
                 uint32_t rr[16];
                 if (ncell > 0 && ok) {
                     tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
-                } else {
+                } else {   // a degree without cells is zero; a block that gave up marks its outputs
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) rr[j] = 0u;
+                    for (int j = 0; j < 16; ++j) rr[j] = ncell > 0 ? kNaNBits : 0u;
                 }
                 if (live_m && b < B) {
 #pragma unroll
@@ -282,13 +287,13 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
                 }
             }
         }
-    } else if (lane == 0) {
+    } else if (lane == 0 && !idle_mma) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = tc_idesc(128, N);
         bool ok = true;
         for (int k = 0; k < ncell && ok; ++k) {
             const int s = k % n_stages, u = k / n_stages;
-            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed);
+            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t a_hi = smem_u32(stages + s * stage_floats);
@@ -371,7 +376,7 @@ template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
-                   int max_n, int* __restrict__ status, int n_stages, int64_t slice_stride) {
+                   int max_n, int* __restrict__ status, int n_stages, int64_t slice_stride, uint32_t wait_limit, int idle_mma) {
     using S = GwTcShape<T>;
     constexpr int MR = S::MR;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -429,7 +434,7 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
         const int to_per = (to_n + 3) >> 2, to_lo = wq * to_per, to_hi = min(to_n, to_lo + to_per);
         bool ok = true;
         for (int q = s, u = 0; q < n_chunks && ok; q += n_stages, ++u) {
-            if (u > 0) ok = mbar_wait(&empty_bar[s], (uint32_t)((u - 1) & 1), failed);
+            if (u > 0) ok = mbar_wait_warp(&empty_bar[s], (uint32_t)((u - 1) & 1), failed, wait_limit);
             if (!ok) break;
             const int gi = q / n, mi = q - gi * n;
             const int g = slice + gi * slices;
@@ -462,7 +467,7 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
         }
         // ---------------- epilogue (first generator group): warp w reads accumulator rows 32 w .. 32 w + 31 ----------------
         if (s == 0) {
-            if (n_chunks > 0) ok = ok && mbar_wait(&done_bar, 0u, failed);
+            if (n_chunks > 0) ok = mbar_wait_warp(&done_bar, 0u, failed, wait_limit) && ok;   // warp-uniform
             tc_fence_after();
             const int row = wq * 32 + lane;
             const int ec = row / MR, kk = row - ec * MR;   // cell of the block and real row inside it
@@ -478,9 +483,9 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
                 uint32_t rr[16];
                 if (n_chunks > 0 && ok) {
                     tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
-                } else {
+                } else {   // nothing to sum gives zero; a block that gave up marks its outputs
 #pragma unroll
-                    for (int cc = 0; cc < 16; ++cc) rr[cc] = 0u;
+                    for (int cc = 0; cc < 16; ++cc) rr[cc] = n_chunks > 0 ? kNaNBits : 0u;
                 }
 #pragma unroll
                 for (int cc = 0; cc < 8; ++cc) {
@@ -492,13 +497,13 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
                 }
             }
         }
-    } else if (lane == 0) {
+    } else if (lane == 0 && !idle_mma) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = tc_idesc(128, N);
         bool ok = true;
         for (int q = 0; q < n_chunks && ok; ++q) {
             const int s = q % n_stages, u = q / n_stages;
-            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed);
+            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t a_hi = smem_u32(smem_raw + (size_t)s * stage_bytes);
@@ -540,9 +545,9 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
 // with m % 4 == w % 4) in chunks of Mc m's and run phase 2 on every chunk exactly as the CUDA-core kernel does.
 // All waits are bounded; a wait that runs out sets the plan's status word and the block finishes without hanging.
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool mbar_wait_checked(uint64_t* bar, uint32_t parity, volatile int* failed) {
-    if (*failed) return false;
-    return mbar_wait(bar, parity, failed);
+__device__ __forceinline__ bool mbar_wait_checked(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit) {
+    if (__any_sync(0xffffffffu, *failed)) return false;   // warp-uniform
+    return mbar_wait_warp(bar, parity, failed, limit);
 }
 
 template <int T>
@@ -551,7 +556,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
                    const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
                    float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int Kb, int band_floats,
-                   uint32_t tmem_cols, int* __restrict__ status) {
+                   uint32_t tmem_cols, int* __restrict__ status, uint32_t wait_limit, int idle_mma) {
     using S = GfShape<T, false>;
     constexpr int NH = T * T;                       // complex entries of a tile
     constexpr int NR = 2 * NH;                      // real columns of D = rows of the B operand
@@ -712,7 +717,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
             if (s_ + 1 < n_steps) load_step(s_ + 1, gv_next);
             {
                 const int ab = a_step & 1, use = a_step >> 1;
-                if (use > 0) ok = mbar_wait_checked(&empty_bar[ab], (uint32_t)((use - 1) & 1), failed) && ok;
+                if (use > 0) ok = mbar_wait_checked(&empty_bar[ab], (uint32_t)((use - 1) & 1), failed, wait_limit) && ok;
                 const int mi = 4 * t + mq;
                 if (mi < n) {
                     const int r = 32 * mq + lane;
@@ -731,7 +736,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
                 fence_proxy_async();   // A chunk and (first step of the entry) the B operand become visible to the MMA
                 tc_fence_before();
                 __syncthreads();
-                if (threadIdx.x == 0) {
+                if (threadIdx.x == 0 && !idle_mma) {
                     if (ok && !*failed) {
                         tc_fence_after();
                         const uint32_t a_hi = smem_u32(a_st + (size_t)ab * 2 * kABytes), a_lo = a_hi + kABytes;
@@ -756,7 +761,7 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
             for (int i = 0; i < 4; ++i) gv[i] = gv_next[i];
         }
         if (n_tiles * n_kc > 0) {
-            ok = mbar_wait_checked(&done_bar, (uint32_t)(n_entry & 1), failed) && ok;
+            ok = mbar_wait_checked(&done_bar, (uint32_t)(n_entry & 1), failed, wait_limit) && ok;
             ++n_entry;   // phases of done_bar completed so far
         }
         tc_fence_after();
@@ -774,9 +779,9 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
                         uint32_t rr[16];
                         if (ok && n_tiles * n_kc > 0) {
                             tmem_ld16(tmem_base + ((uint32_t)(32 * mq) << 16) + (uint32_t)((mi >> 2) * NR + half * 16), rr);
-                        } else {
+                        } else {   // an entry without work is zero; a block that gave up marks what it owns
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) rr[c] = 0u;
+                            for (int c = 0; c < 16; ++c) rr[c] = n_tiles * n_kc > 0 ? kNaNBits : 0u;
                         }
                         float2* h = H + ((size_t)(mi - mc0) * NH + half * 8) * 32 + lane;
 #pragma unroll
@@ -813,10 +818,10 @@ fused_gf_tc_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __r
 // ---------------------------------------------------------------------------------------------------------------
 // Use the tensor-core forward?  Needs the plan's tables (tile edge 2 or 4, full product, tau_out <= 64) and pays off
 // when the mixing dominates: measured on B200 against the CUDA-core forward (packing included) 1.25x faster at 12 and 16
-// output channels, 2.2-2.7x at 32 and 64, 8 % slower at 8.  CGB200_TC=0 / 1 overrides the default.
+// output channels, 2.2-2.7x at 32 and 64, 8 % slower at 8.  CGB200_OPT_TC_FWD overrides the default.
 bool tc_wanted(const cgb200_plan* p) {
     if (!p->tc_ok) return false;
-    if (const char* env = getenv("CGB200_TC")) return env[0] == '1';
+    if (p->opt[CGB200_OPT_TC_FWD] != CGB200_AUTO) return p->opt[CGB200_OPT_TC_FWD] == 1;
     return p->max_tau_out >= 12;
 }
 
@@ -838,7 +843,7 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
     const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
     int n_stages = (int)std::min<size_t>(kTcMaxStages, (220 * 1024 - cbuf_bytes) / stage_bytes);
-    if (const char* env = getenv("CGB200_TC_STAGES")) n_stages = std::min(n_stages, std::max(1, atoi(env)));
+    if (p->opt[CGB200_OPT_TC_STAGES] >= 2) n_stages = std::min(n_stages, p->opt[CGB200_OPT_TC_STAGES]);
     const size_t smem = n_stages * stage_bytes + cbuf_bytes;
     if (n_stages < 2) {
         set_error("tensor-core forward: pipeline stages do not fit in shared memory");
@@ -848,7 +853,8 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
     kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
-                                                                  n_max, p->max_n, p->d_status, n_stages);
+                                                                  n_max, p->max_n, p->d_status, n_stages, wait_polls(p),
+                                                                  p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;
@@ -864,10 +870,10 @@ int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const
 
 
 // Weight gradient on the tensor cores: tile edge 4, full product, where the forward's tables exist.  Same default
-// threshold as the forward (16 output channels); CGB200_TC_GW=0 / 1 overrides it.
+// threshold as the forward (16 output channels); CGB200_OPT_TC_GRAD_W overrides it.
 bool tc_gw_wanted(const cgb200_plan* p) {
     if (!p->tc_gw_ok || p->tc_gw_tiles.empty()) return false;
-    if (const char* env = getenv("CGB200_TC_GW")) return env[0] == '1';
+    if (p->opt[CGB200_OPT_TC_GRAD_W] != CGB200_AUTO) return p->opt[CGB200_OPT_TC_GRAD_W] == 1;
     // tile edge 4: faster than the CUDA-core kernel at every width measured (2x at 8 output channels, 2.9x at 12, 3.3x at
     // 16, 5-8x at 32 and 64).  Tile edge 5 is built and tested but stays off by default: at 5 channels (lmax 10, batch
     // 100) it takes 126 us against 98 us - blocks of two cells with at most 21 chunks each spend their time filling and
@@ -884,8 +890,8 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     if (n_tiles == 0) return CGB200_OK;
     const size_t stage_bytes = (size_t)2 * 16 * kGwSbo + (size_t)2 * (n_max / 8) * kGwSbo;
     const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
-    int n_stages = (int)std::min<size_t>(kTcMaxStages, (226 * 1024 - cbuf_bytes) / stage_bytes);
-    if (const char* env = getenv("CGB200_TC_STAGES")) n_stages = std::min(n_stages, std::max(1, atoi(env)));
+    int n_stages = (int)std::min<size_t>(kTcMaxStages, (kMaxDynSmem - cbuf_bytes) / stage_bytes);
+    if (p->opt[CGB200_OPT_TC_STAGES] >= 2) n_stages = std::min(n_stages, p->opt[CGB200_OPT_TC_STAGES]);
     if (n_stages < 2) {
         set_error("tensor-core weight gradient: pipeline stages do not fit in shared memory");
         return CGB200_ERR_UNSUPPORTED;
@@ -900,7 +906,8 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     launch_begin(K_GW_TC, st);
     kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
                                                                        slices > 1 ? gw_part : gW, G, n_max, p->max_n, p->d_status,
-                                                                       n_stages, p->d.w_len);
+                                                                       n_stages, p->d.w_len, wait_polls(p),
+                                                                       p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
     launch_end(K_GW_TC, st);
     CGB_CUDA(cudaGetLastError());
     if (slices > 1) {
@@ -919,15 +926,14 @@ int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const
 }
 
 // Input gradient with phase 1 on the tensor cores: tile edge 4, full product, 2 lmax + 1 <= 64 (the gFF tile of an entry
-// must fit the 512 columns of tensor memory).  Off unless CGB200_TC_GF=1: measured on B200 it matches but does not beat
+// must fit the 512 columns of tensor memory).  Off unless CGB200_OPT_TC_GRAD_F is 1: measured on B200 it matches but does not beat
 // the CUDA-core kernel (lmax 14, 16 channels, batch 64: 8.5 against 7.5 ms; lmax 10, 64 channels: 62 against 59 ms).
 // Every (row tile, 16-channel chunk) step moves a 32 KB A chunk through one of two shared-memory buffers, so a step
 // lasts half the issue-to-completion latency of its MMAs (about 1 us per step); a deeper ring does not fit beside the
 // phase-2 buffers, and a wider N per step (several cells per MMA) needs more than the 512 columns of tensor memory.
 bool tc_gf_wanted(const cgb200_plan* p) {
     if (!p->tc_ok || p->d.tile != 4 || p->max_n > 64) return false;
-    if (const char* env = getenv("CGB200_TC_GF")) return env[0] == '1';
-    return false;
+    return p->opt[CGB200_OPT_TC_GRAD_F] == 1;
 }
 
 int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* SG, const float2* W, const float* inv, float2* out,
@@ -940,7 +946,7 @@ int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* S
     const size_t fixed = (size_t)4 * 128 * 32 * 4 + (size_t)2 * 32 * Kb * 4 + (size_t)3 * T * p->max_n * 32 * sizeof(float2) +
                          2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
     const size_t per_m = (size_t)NH * 32 * sizeof(float2);
-    const size_t budget = 227 * 1024;
+    const size_t budget = kMaxDynSmem;
     if (fixed + 4 * per_m > budget) {
         set_error("tensor-core input gradient: staging areas do not fit in shared memory");
         return CGB200_ERR_UNSUPPORTED;
@@ -953,7 +959,8 @@ int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* S
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_GF_TC, st);
     kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * 32, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, SF, SG, W, inv,
-                                                     out, part_stride, B, Mc, p->max_n, Kb, band_floats, cols, p->d_status);
+                                                     out, part_stride, B, Mc, p->max_n, Kb, band_floats, cols, p->d_status,
+                                                     wait_polls(p), p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
     launch_end(K_GF_TC, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;

@@ -141,23 +141,28 @@ static int build_table(float* cg_dev, int64_t cg_len, int lmax, const int32_t* l
     const int nlf = 3 * lmax + 4;
     std::vector<double> logfact(nlf, 0.0);
     for (int i = 2; i < nlf; ++i) logfact[i] = logfact[i - 1] + log((double)i);   // cudaCG_utils.cu:83-90
-    double* d_lf = nullptr;
-    int* d_llls = nullptr;
-    int64_t* d_offs = nullptr;
-    CGB_CUDA(cudaMalloc(&d_lf, nlf * sizeof(double)));
-    CGB_CUDA(cudaMalloc(&d_llls, n * sizeof(int)));
-    CGB_CUDA(cudaMalloc(&d_offs, (n + 1) * sizeof(int64_t)));
-    CGB_CUDA(cudaMemcpyAsync(d_lf, logfact.data(), nlf * sizeof(double), cudaMemcpyHostToDevice, st));
-    CGB_CUDA(cudaMemcpyAsync(d_llls, llls, n * sizeof(int), cudaMemcpyHostToDevice, st));
-    CGB_CUDA(cudaMemcpyAsync(d_offs, offs.data(), (n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+    // the three temporaries are freed on every path out of this function
+    struct Temps {
+        double* lf = nullptr;
+        int* llls = nullptr;
+        int64_t* offs = nullptr;
+        ~Temps() {
+            cudaFree(lf);
+            cudaFree(llls);
+            cudaFree(offs);
+        }
+    } t;
+    CGB_CUDA(cudaMalloc(&t.lf, nlf * sizeof(double)));
+    CGB_CUDA(cudaMalloc(&t.llls, n * sizeof(int)));
+    CGB_CUDA(cudaMalloc(&t.offs, (n + 1) * sizeof(int64_t)));
+    CGB_CUDA(cudaMemcpyAsync(t.lf, logfact.data(), nlf * sizeof(double), cudaMemcpyHostToDevice, st));
+    CGB_CUDA(cudaMemcpyAsync(t.llls, llls, n * sizeof(int), cudaMemcpyHostToDevice, st));
+    CGB_CUDA(cudaMemcpyAsync(t.offs, offs.data(), (n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st));
     launch_begin(K_CG_TABLE, st);
-    cg_table_kernel<<<n, 128, 0, st>>>(cg_dev, d_llls, d_offs, n, lmax + 1, d_lf);
+    cg_table_kernel<<<n, 128, 0, st>>>(cg_dev, t.llls, t.offs, n, lmax + 1, t.lf);
     launch_end(K_CG_TABLE, st);
     CGB_CUDA(cudaGetLastError());
     CGB_CUDA(cudaStreamSynchronize(st));   // one-off set-up call: the host vectors and temporaries die here
-    cudaFree(d_lf);
-    cudaFree(d_llls);
-    cudaFree(d_offs);
     return CGB200_OK;
 }
 
@@ -175,10 +180,6 @@ static int upload(cgb200_plan* p, const std::vector<T>& v, const T** out) {
 // Channel-tile edge: the largest fraction of useful lanes in the T x T register tiles, weighted by each triple's work,
 // with a mild preference for 4..5 (enough arithmetic per shared-memory load, moderate register use).
 static int choose_tile(const std::vector<TripleRec>& tr, bool dw) {
-    if (const char* env = getenv("CGB200_TILE")) {
-        const int t = atoi(env);
-        if (t >= 1 && t <= kMaxTile) return t;
-    }
     static const double pref[kMaxTile + 1] = {0, 0.55, 0.80, 0.93, 1.00, 1.00, 0.96};
     int best = 1;
     double best_score = -1;
@@ -334,7 +335,9 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         t.woff = p->cumW[t.l] + t.toff;
     }
 
-    const int T = choose_tile(p->triples, dw);
+    const int forced_tile = (flags >> 8) & 0xF;   // CGB200_PLAN_TILE
+    CGB_REQUIRE(forced_tile <= kMaxTile, "CGB200_PLAN_TILE: tile edge out of range [1, 6]");
+    const int T = forced_tile ? forced_tile : choose_tile(p->triples, dw);
     p->triple_begin.assign(L1 + 1, 0);
     p->cell_begin.assign(L1 + 1, 0);
     for (int k = 0; k < n; ++k) {
@@ -695,6 +698,36 @@ int cgb200_plan_query(const cgb200_plan* p, int what, int64_t* v) {
         case CGB200_Q_TILE: *v = p->d.tile; break;
         default: set_error("unknown query"); return CGB200_ERR_ARGUMENT;
     }
+    return CGB200_OK;
+}
+
+int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
+    CGB_REQUIRE(p != nullptr, "plan is null");
+    CGB_REQUIRE(option >= 0 && option < CGB200_OPT_COUNT, "unknown option");
+    if (value != CGB200_AUTO) {
+        switch (option) {
+            case CGB200_OPT_TC_STAGES: CGB_REQUIRE(value >= 2, "CGB200_OPT_TC_STAGES must be at least 2"); break;
+            case CGB200_OPT_WAIT_POLLS: CGB_REQUIRE(value >= 1, "CGB200_OPT_WAIT_POLLS must be positive"); break;
+            default: CGB_REQUIRE(value == 0 || value == 1, "option value must be CGB200_AUTO, 0 or 1"); break;
+        }
+        const bool needs_tables = value == 1;
+        bool have = true;
+        if (option == CGB200_OPT_TC_FWD) have = p->tc_ok;
+        if (option == CGB200_OPT_TC_GRAD_W) have = p->tc_gw_ok && !p->tc_gw_tiles.empty();
+        if (option == CGB200_OPT_TC_GRAD_F) have = p->tc_ok && p->d.tile == 4 && p->max_n <= 64;
+        if (needs_tables && !have) {
+            set_error("this plan has no tables for the requested tensor-core variant (tile edge, depthwise product or channel counts)");
+            return CGB200_ERR_UNSUPPORTED;
+        }
+    }
+    p->opt[option] = value;
+    return CGB200_OK;
+}
+
+int cgb200_plan_get_option(const cgb200_plan* p, int option, int* value) {
+    CGB_REQUIRE(p != nullptr && value != nullptr, "null argument");
+    CGB_REQUIRE(option >= 0 && option < CGB200_OPT_COUNT, "unknown option");
+    *value = p->opt[option];
     return CGB200_OK;
 }
 

@@ -41,6 +41,7 @@ extern "C" {
 /* plan flags */
 #define CGB200_PLAN_DEPTHWISE   0x1 /* channel-wise product (t1 == t2 only; needs tau_l1 == tau_l2).  Not in the
                                        reference (its 'mst' mode keeps the full tau_l1 x tau_l2 product)           */
+#define CGB200_PLAN_TILE(t)     (((t) & 0xF) << 8)  /* force the channel-tile edge (1..6) instead of the plan's choice   */
 
 typedef struct cgb200_plan cgb200_plan;
 
@@ -81,11 +82,35 @@ void cgb200_plan_destroy(cgb200_plan* plan);
 #define CGB200_Q_TILE       7   /* channel-tile edge chosen for the register-tiled kernels    */
 int cgb200_plan_query(const cgb200_plan* plan, int what, int64_t* value);
 /*
- * Device-side status of the plan's kernels (no reference counterpart).  The tensor-core forward waits on hardware
- * barriers with an iteration limit; a wait that runs out makes the kernel return early and sets this word.  The call
- * synchronises the device, returns the word in *status (0 = fine) and clears it.
+ * Device-side status of the plan's kernels (no reference counterpart).  The tensor-core kernels wait on hardware
+ * barriers with an iteration limit; a wait that runs out makes the kernel give up: it sets this word, fills the part
+ * of the output it owns with NaN (so a training loss shows the failure without a device synchronisation), releases
+ * its tensor memory and returns.  The call synchronises the device, returns the word in *status (0 = fine) and clears it.
  */
 int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
+/*
+ * Kernel selection of a plan (no reference counterpart: the reference has one kernel per step).  Every option starts
+ * at CGB200_AUTO, the library's measured default for the plan's shape; 0 / 1 force a variant off / on where the plan has
+ * its tables, otherwise the call returns CGB200_ERR_UNSUPPORTED.  Options are per plan, not per process, and take
+ * effect from the next call; do not change them while a call on the same plan is being enqueued from another thread.
+ */
+#define CGB200_AUTO                 (-1)
+#define CGB200_OPT_TC_FWD           0   /* forward on tcgen05 tensor cores (tile edge 2 or 4, full product)            */
+#define CGB200_OPT_TC_GRAD_W        1   /* weight gradient on tensor cores (tile edge 4 or 5)                            */
+#define CGB200_OPT_TC_GRAD_F        2   /* first phase of the input gradient on tensor cores (tile edge 4)               */
+#define CGB200_OPT_TC_STAGES        3   /* upper limit of the tensor-core kernels' pipeline depth (>= 2)                 */
+#define CGB200_OPT_FWD_SLAB         4   /* CUDA-core forward: persistent blocks with the slab in shared memory           */
+#define CGB200_OPT_GRAD_F_SPLIT     5   /* input gradient: rows of phase 2 split into two channel groups                 */
+#define CGB200_OPT_STATS_SPLIT      6   /* statistics: two blocks per cell                                               */
+#define CGB200_OPT_BWD_SERIAL       7   /* backward: weight and input gradient on one stream instead of forked           */
+#define CGB200_OPT_WAIT_POLLS       8   /* iteration limit of every bounded device-side wait (default 4000000)           */
+#define CGB200_OPT_TEST_IDLE_MMA    9   /* test hook: the tensor-core kernels' MMA warp issues nothing, so every wait on
+                                           it runs out; exercises the give-up path (status word, NaN output) without a
+                                           fault, a trap or an endless loop                                              */
+#define CGB200_OPT_COUNT            10
+int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
+int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
+
 /* Per-degree mid-channel counts t_FF[0..lmax] (CGNet/CG_layers.py:253-262), for cross-checking the host's own. */
 int cgb200_plan_t_ff(const cgb200_plan* plan, int32_t* t_ff_host);
 /* Device address of the plan's CG table (float[CGB200_Q_CG_LEN]); valid until the plan is destroyed. */
@@ -145,6 +170,9 @@ int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, co
 
 /* Scratch bytes the two fused calls need for a batch of B samples (the larger of the two). */
 int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
+/* Scratch bytes cgb200_layer_fwd alone needs (input slab, norm factors, row counters, packed tensor-core weights);
+   never more than cgb200_layer_workspace_bytes.  Both depend on the plan's options at the time of the call. */
+int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* plan, int64_t B);
 
 /*
  * cgb200_layer_fwd for callers that cannot allocate device memory (no counterpart in the reference, whose Python
@@ -155,7 +183,7 @@ int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
  * cudaMalloc after start-up because it stalls the device.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - Returns CGB200_ERR_WORKSPACE, with the needed and available byte counts in cgb200_last_error(), when
- *     cgb200_layer_workspace_bytes(plan, B) exceeds the array.
+ *     cgb200_layer_fwd_workspace_bytes(plan, B) exceeds the array.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress with that device current);
  *     make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps whatever the last call left in it.  The call itself

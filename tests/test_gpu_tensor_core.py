@@ -1,7 +1,6 @@
 """The tensor-core (tcgen05 + tensor memory + bulk async copy, 3xTF32) variant of the fused forward against the CPU
 oracle and against the CUDA-core variant.  Tolerance as everywhere: relative Frobenius error per fragment < 1e-4."""
-import ctypes
-import os
+import contextlib
 
 import numpy as np
 import pytest
@@ -23,23 +22,29 @@ CASES = [
 ]
 
 
+@contextlib.contextmanager
+def option(plan, opt, value):
+    """Select a kernel variant through the plan's options for the duration of a block (plans are shared, so the
+    library's default is restored afterwards)."""
+    from cgnet_b200 import _lib
+    plan.set_option(opt, value)
+    try:
+        yield
+    finally:
+        plan.set_option(opt, _lib.AUTO)
+
+
 def _forward(plan, case, bn, training, tc):
     from cgnet_b200 import _lib
     dev = torch.device("cuda", 0)
-    os.environ["CGB200_TC"] = "1" if tc else "0"
-    try:
+    with option(plan, _lib.OPT_TC_FWD, 1 if tc else 0):
         F = torch.tensor(case["F"], device=dev)
         W = torch.tensor(case["W"], device=dev)
         stds = torch.tensor(case["stds"], device=dev) if bn else None
         flags = (_lib.FN_PRESENT if bn else 0) | (_lib.FN_UPDATE if training else 0)
         O = plan.layer_fwd(F, W, stds, 2.0, 1e-5, flags)
-        torch.cuda.synchronize()
-        st = ctypes.c_int32(-1)
-        _lib.check(_lib.load().cgb200_plan_status(plan.handle, st), "cgb200_plan_status")
-        assert st.value == 0, "a bounded wait inside the tensor-core kernel ran out"
+        plan.check_status()   # raises if a bounded wait inside the tensor-core kernel ran out
         return O.cpu().numpy(), None if stds is None else stds.cpu().numpy()
-    finally:
-        os.environ.pop("CGB200_TC", None)
 
 
 @pytest.mark.parametrize("bn,training", [(False, False), (True, True)])
@@ -71,20 +76,14 @@ def test_tensor_core_forward_is_deterministic():
 def _weight_gradient(plan, case, bn, tc):
     from cgnet_b200 import _lib
     dev = torch.device("cuda", 0)
-    os.environ["CGB200_TC_GW"] = "1" if tc else "0"
-    try:
+    with option(plan, _lib.OPT_TC_GRAD_W, 1 if tc else 0):
         F = torch.tensor(case["F"], device=dev)
         W = torch.tensor(case["W"], device=dev)
         gO = torch.tensor(case["gO"], device=dev)
         stds = torch.tensor(case["stds"], device=dev) if bn else None
         _, gW = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT if bn else 0, gO)
-        torch.cuda.synchronize()
-        st = ctypes.c_int32(-1)
-        _lib.check(_lib.load().cgb200_plan_status(plan.handle, st), "cgb200_plan_status")
-        assert st.value == 0, "a bounded wait inside the tensor-core kernel ran out"
+        plan.check_status()
         return gW.cpu().numpy()
-    finally:
-        os.environ.pop("CGB200_TC_GW", None)
 
 
 GW_CASES = CASES + [
@@ -126,20 +125,14 @@ def test_tensor_core_weight_gradient_is_deterministic():
 def _input_gradient(plan, case, bn, tc):
     from cgnet_b200 import _lib
     dev = torch.device("cuda", 0)
-    os.environ["CGB200_TC_GF"] = "1" if tc else "0"
-    try:
+    with option(plan, _lib.OPT_TC_GRAD_F, 1 if tc else 0):
         F = torch.tensor(case["F"], device=dev)
         W = torch.tensor(case["W"], device=dev)
         gO = torch.tensor(case["gO"], device=dev)
         stds = torch.tensor(case["stds"], device=dev) if bn else None
         gF, _ = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT if bn else 0, gO)
-        torch.cuda.synchronize()
-        st = ctypes.c_int32(-1)
-        _lib.check(_lib.load().cgb200_plan_status(plan.handle, st), "cgb200_plan_status")
-        assert st.value == 0, "a bounded wait inside the tensor-core kernel ran out"
+        plan.check_status()
         return gF.cpu().numpy()
-    finally:
-        os.environ.pop("CGB200_TC_GF", None)
 
 
 @pytest.mark.parametrize("bn", [False, True])
@@ -166,3 +159,54 @@ def test_tensor_core_input_gradient_is_deterministic():
     a = _input_gradient(plan, case, True, tc=True)
     b = _input_gradient(plan, case, True, tc=True)
     assert np.array_equal(a, b)
+
+
+def test_bounded_wait_gives_up_cleanly():
+    """The give-up path of the tensor-core kernels, driven without a fault, a trap or an endless loop: with the test
+    option that keeps the MMA warp idle nothing ever arrives at the barriers the other warps wait on, so their waits run
+    out after a short iteration limit.  The kernel must then return by itself, report through the plan's status word,
+    mark the outputs it owns with NaN, and leave the context usable: the same call with the options restored gives the
+    right answer."""
+    from cgnet_b200 import _lib, get_plan
+    dev = torch.device("cuda", 0)
+    case = make_case([4] * 3, [16] * 3, 5, "default", seed=57)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], dev)
+    assert plan.tile == 4
+    F = torch.tensor(case["F"], device=dev)
+    W = torch.tensor(case["W"], device=dev)
+    gO = torch.tensor(case["gO"], device=dev)
+    plan.set_option(_lib.OPT_WAIT_POLLS, 2000)
+    plan.set_option(_lib.OPT_TEST_IDLE_MMA, 1)
+    plan.set_option(_lib.OPT_TC_STAGES, 2)   # fewer stages than cells: the producers' waits run out too, not only the epilogue's
+    try:
+        with option(plan, _lib.OPT_TC_FWD, 1):
+            O_bad = plan.layer_fwd(F, W, None, 1.0, 1e-5, 0)
+        with pytest.raises(RuntimeError, match="gave up"):
+            plan.check_status()
+        assert torch.isnan(O_bad).all(), "a forward that gave up must mark every output it owns"
+        with option(plan, _lib.OPT_TC_GRAD_W, 1):
+            _, gW_bad = plan.layer_bwd(F, W, None, 1e-5, 0, gO)
+        with pytest.raises(RuntimeError, match="gave up"):
+            plan.check_status()
+        assert torch.isnan(gW_bad).all()
+    finally:
+        plan.set_option(_lib.OPT_TEST_IDLE_MMA, _lib.AUTO)
+        plan.set_option(_lib.OPT_WAIT_POLLS, _lib.AUTO)
+        plan.set_option(_lib.OPT_TC_STAGES, _lib.AUTO)
+    plan.check_status()   # the word was cleared by the reads above
+    O_want, _, gW_want, _ = oracle_layer(case, False, False)
+    O_good, _ = _forward(plan, case, False, False, tc=True)
+    assert_fragments_close(O_good, O_want, case["tau_out"], "O after a run that gave up")
+    import cg_oracle as o
+    t_ff, _ = o.tau_ff_and_offsets(case["lmax"], case["taus"], case["llls"])
+    assert_weights_close(_weight_gradient(plan, case, False, tc=True), gW_want, t_ff, case["tau_out"], "gW after a run that gave up")
+
+
+def test_unsupported_variant_is_refused():
+    """Forcing a tensor-core variant on a plan without its tables is an error at the option call, not a silent fallback."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case([5] * 3, [5] * 3, 2, "default", seed=58)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], torch.device("cuda", 0))
+    assert plan.tile == 5
+    with pytest.raises(RuntimeError, match="no tables"):
+        plan.set_option(_lib.OPT_TC_FWD, 1)

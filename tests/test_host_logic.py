@@ -67,7 +67,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.SIGNATURES), "ctypes signature table and header disagree"
     loaded = _lib.load()
     assert loaded.cgb200_version() >= 100 and loaded.cgb200_max_lmax() == 511
-    assert loaded.cgb200_kernel_count() == 18
+    assert loaded.cgb200_kernel_count() >= 18
     assert loaded.cgb200_kernel_name(9) == b"fused_fwd"
 
 
@@ -93,7 +93,48 @@ def test_modules_fail_loudly_without_a_gpu():
         CGBN_cuda(2, [2, 2, 2], [2, 2, 2], device="cuda")
 
 
-def test_benchmark_work_counts_match_the_survey():
+def test_argument_checks_raise_before_any_launch():
+    """Wrong lengths, dtypes, devices and layouts must be Python errors, never pointers handed to a kernel."""
+    from cgnet_b200 import _lib
+    from cgnet_b200.cg_layers import PlanShapes
+    dev = torch.device("cpu")   # the checks compare devices, they do not need a GPU to be exercised
+    shapes = PlanShapes(dev, n_F=20, n_FF=46, n_O=12, w_len=30, sum_tff=16)
+    F = torch.zeros(3, 20, 2)
+    W = torch.zeros(30, 2)
+    stds = torch.ones(16)
+    shapes.check_batch(3, F=(F, 20))
+    shapes.check_weights(W, stds, _lib.FN_PRESENT)
+    shapes.check_weights(W, None, 0)
+    with pytest.raises(RuntimeError, match="shape"):
+        shapes.check_batch(3, F=(torch.zeros(3, 19, 2), 20))            # activation of the wrong length
+    with pytest.raises(RuntimeError, match="shape"):
+        shapes.check_batch(3, F=(F, 20), gO=(torch.zeros(2, 12, 2), 12))  # cotangent with another batch size
+    with pytest.raises(RuntimeError, match="shape"):
+        shapes.check_weights(torch.zeros(29, 2), stds, _lib.FN_PRESENT)
+    with pytest.raises(RuntimeError, match="shape"):
+        shapes.check_weights(W, torch.ones(15), _lib.FN_PRESENT)
+    with pytest.raises(RuntimeError, match="float32"):
+        shapes.check_weights(W, stds.half(), _lib.FN_PRESENT)           # what model.half() would do to the statistics
+    with pytest.raises(RuntimeError, match="float32"):
+        shapes.check_batch(3, F=(F.double(), 20))
+    with pytest.raises(RuntimeError, match="None"):
+        shapes.check_weights(W, None, _lib.FN_PRESENT)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        shapes.check_batch(3, F=(torch.zeros(3, 2, 20).transpose(1, 2), 20))
+    with pytest.raises(RuntimeError, match="lives on"):
+        PlanShapes(torch.device("meta"), 20, 46, 12, 30, 16).check_batch(3, F=(F, 20))   # tensor on another device than the plan
+
+
+def test_plan_options_are_checked_without_a_gpu():
+    from cgnet_b200 import _lib
+    lib = _lib.load()
+    assert lib.cgb200_plan_set_option(None, 0, 1) == 1
+    v = ctypes.c_int32(0)
+    assert lib.cgb200_plan_get_option(None, 0, v) == 1
+    assert lib.cgb200_layer_fwd_workspace_bytes(None, 4) == -1
+
+
+def test_benchmark_work_counts():
     import bench
     w = bench.layer_work(10, [5] * 11, [5] * 11)
     assert w["n_FF"] == 118525 and w["n_F"] == 605 and w["w_len"] == 47625 and w["cg_len"] == 49535

@@ -55,7 +55,7 @@ def test_static_scratch_rejects_oversized_requests():
     case = make_case([8] * 8, [8] * 8, 4, "default", seed=33)
     plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], dev)
     B = 8192   # far beyond what the built-in array can serve for this layer
-    assert lib.cgb200_layer_workspace_bytes(plan.handle, B) > (8 << 20)
+    assert lib.cgb200_layer_fwd_workspace_bytes(plan.handle, B) > (8 << 20)
     F = torch.zeros(4, plan.n_F, 2, device=dev)   # never read: the call must refuse before launching anything
     W = torch.tensor(case["W"], device=dev)
     O = torch.zeros(4, plan.n_O, 2, device=dev)
@@ -63,3 +63,23 @@ def test_static_scratch_rejects_oversized_requests():
     assert rc == 4
     msg = lib.cgb200_last_error().decode()
     assert "scratch" in msg and str(8 << 20) in msg
+
+
+def test_static_scratch_is_sized_by_the_forward_alone():
+    """A batch whose forward scratch fits the built-in array although forward plus backward would not: the entry point
+    must accept it (its limit is the forward's own need) and agree with the ordinary entry point."""
+    from cgnet_b200 import _lib, get_plan
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    case = make_case([8] * 7, [8] * 7, 1600, "default", seed=34)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], dev)
+    assert lib.cgb200_layer_fwd_workspace_bytes(plan.handle, 1600) <= (8 << 20) < lib.cgb200_layer_workspace_bytes(plan.handle, 1600)
+    F = torch.tensor(case["F"], device=dev)
+    W = torch.tensor(case["W"], device=dev)
+    stds = torch.tensor(case["stds"], device=dev)
+    want = plan.layer_fwd(F, W, stds, 1.0, 1e-5, _lib.FN_PRESENT)
+    rc, got = _run_static(lib, plan, F, W, stds, 1.0, _lib.FN_PRESENT, plan.n_O)
+    assert rc == 0, lib.cgb200_last_error()
+    torch.cuda.synchronize()
+    assert_fragments_close(got.cpu().numpy(), want.cpu().numpy(), case["tau_out"], "static forward, forward-sized scratch", tol=TOL)
