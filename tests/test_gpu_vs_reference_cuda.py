@@ -5,90 +5,30 @@ The reference extension `CG_cuda_ops` (CGNet/cudaCG, unmodified sources) is comp
 are called directly with index tensors laid out as CGNet/CG_layers.py builds them (:244-250, :104-108); the reference's
 Python files are not needed.  Skipped when the extension has not been built.  Tolerance: relative Frobenius error per
 fragment < 1e-4 (fp32 on both sides)."""
-import importlib.util
-import os
-
 import numpy as np
 import pytest
 import torch
 
-import cg_oracle as o
+import ref_cuda_driver as refdrv
 from helpers import assert_fragments_close, assert_weights_close, make_case
 
 pytestmark = pytest.mark.gpu
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_SO = os.path.join(ROOT, "oracle", "_ref", "cuda_build", "CG_cuda_ops.so")
-
 
 @pytest.fixture(scope="module")
 def ref_ops():
-    if not os.path.exists(REF_SO):
+    if not refdrv.available():
         pytest.skip("reference CUDA extension not built (python oracle/build_ref_cuda.py)")
-    spec = importlib.util.spec_from_file_location("CG_cuda_ops", REF_SO)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod
+    return refdrv.load_ops()
 
 
 def dev():
     return torch.device("cuda", 0)
 
 
-def it(x):
-    return torch.tensor(np.asarray(x, dtype=np.int64), dtype=torch.int, device=dev())
-
-
-class RefLayer:
-    """The index tensors of CG_woFilter_cuda / MyBatchNormWeightMM_cuda and thin calls into the reference kernels."""
-
-    def __init__(self, ops, case):
-        self.ops, self.c = ops, case
-        L, taus, tau_out, llls = case["lmax"], case["taus"], case["tau_out"], case["llls"]
-        self.L = L
-        ltuples = [[] for _ in range(L + 1)]
-        for l, l1, l2 in o.decode_triples(L, llls):
-            ltuples[l].append((l1, l2))
-        _, table = o.encode_sorted(ltuples)
-        t_ff, t_off = o.tau_ff_and_offsets(L, taus, llls)
-        self.t_ff = t_ff
-        self.d_t_F, self.d_cum_F = it(taus), it(o.cumulative_tm(taus))
-        self.d_t_FF, self.d_cum_FF = it(t_ff), it(o.cumulative_tm(t_ff))
-        self.d_t_O, self.d_cum_O = it(tau_out), it(o.cumulative_tm(tau_out))
-        self.d_cum_W = it(np.concatenate([[0], np.cumsum(t_ff * np.asarray(tau_out))]))
-        self.d_llls, self.d_table = it(llls), it(table)
-        self.d_t_off = it(list(t_off) + [2 ** 30])   # one spare entry: the kernel may peek one past the last triple
-        offs = o.cg_offsets(L, llls)
-        self.d_cg_off = it(offs)
-        self.CG = torch.zeros(offs[-1], dtype=torch.float, device=dev())
-        ops.sparse_precomputeCG(self.CG, L, self.d_llls, self.d_cg_off)
-        self.n_FF, self.n_O = int(o.cumulative_tm(t_ff)[-1]), int(o.cumulative_tm(tau_out)[-1])
-        self.w_len, self.sum_tff = int((t_ff * np.asarray(tau_out)).sum()), int(t_ff.sum())
-
-    def product_fwd(self, F):
-        FF = torch.zeros(F.shape[0], self.n_FF, 2, device=dev())
-        self.ops.sparse_forward(F, FF, self.L, F.shape[0], self.d_t_F, self.d_cum_F, self.d_t_FF, self.d_cum_FF, self.d_llls,
-                                self.d_table, self.d_t_off, self.CG, self.d_cg_off)
-        return FF
-
-    def product_bwd(self, F, gFF):
-        gF = torch.zeros_like(F)
-        self.ops.sparse_backward(F, gF, gFF, self.L, F.shape[0], self.d_t_F, self.d_cum_F, self.d_t_FF, self.d_cum_FF, self.d_llls,
-                                 self.d_t_off, self.CG, self.d_cg_off)
-        return gF
-
-    def mix_fwd(self, FF, W, stds, cnt, eps, flags):
-        O = torch.zeros(FF.shape[0], self.n_O, 2, device=dev())
-        self.ops.FN_WMM_forward(FF, O, W, self.L, FF.shape[0], self.sum_tff, self.n_O, self.d_t_FF, self.d_cum_FF, self.d_cum_O,
-                                self.d_cum_W, stds if stds is not None else torch.full((1,), eps, device=dev()), cnt, eps, flags)
-        return O
-
-    def mix_bwd(self, gO, FF, W, stds, cnt, eps, flags):
-        gFF, gW = torch.zeros_like(FF), torch.zeros_like(W)
-        self.ops.FN_WMM_backward(gO, gFF, gW, FF, W, self.L, FF.shape[0], self.n_FF, self.w_len, self.d_t_FF, self.d_cum_FF,
-                                 self.d_t_O, self.d_cum_O, self.d_cum_W,
-                                 stds if stds is not None else torch.full((1,), eps, device=dev()), cnt, eps, flags)
-        return gFF, gW
+def RefLayer(ops, case):
+    """The reference's index tensors and kernel calls for one layer case (oracle/ref_cuda_driver.py)."""
+    return refdrv.RefLayer.from_case(ops, case, dev())
 
 
 CASES = [
@@ -96,10 +36,14 @@ CASES = [
     ([3, 2, 1, 1, 1], [3, 2, 1, 1, 1], 1, "default"),
     ([4] * 6, [4] * 6, 3, "default"),
     ([3, 1, 4, 1, 5, 2, 2], [2, 3, 1, 4, 1, 2, 3], 2, "mst"),
-    ([8] * 6, [8] * 6, 32, "default"),          # BASELINE config 1 shape
-    ([5] * 11, [5] * 11, 20, "default"),        # one layer of BASELINE config 2 at a fifth of its batch
-    ([1] * 11, [5] * 11, 20, "default"),        # its first layer
+    ([8] * 6, [8] * 6, 32, "default"),          # single layer lmax 5, 8 channels, batch 32
+    ([5] * 11, [5] * 11, 100, "default"),       # one layer of the 5-layer lmax-10 classifier at its batch of 100
+    ([1] * 11, [5] * 11, 100, "default"),       # its first layer
     ([4] * 11, [3] * 11, 5, "mst"),
+    ([6] * 15, [16] * 15, 4, "default"),        # first layer of the lmax-14 training network (6 input channels)
+    ([16] * 15, [16] * 15, 3, "default"),       # its other layers: tensor-core forward and weight gradient
+    ([32] * 21, [32] * 21, 2, "mst"),           # lmax 20, 32 channels, MST pairs with the full channel product
+    ([64] * 11, [64] * 11, 2, "default"),       # lmax 10, 64 channels
 ]
 
 

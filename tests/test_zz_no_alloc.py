@@ -72,10 +72,11 @@ def test_static_scratch_is_sized_by_the_forward_alone():
     lib = _lib.load()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    case = make_case([8] * 7, [8] * 7, 1600, "default", seed=34)
+    B = 1600
+    case = make_case([8] * 7, [8] * 7, 2, "default", seed=34)   # weights and statistics; the large batch is drawn below
     plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], dev)
-    assert lib.cgb200_layer_fwd_workspace_bytes(plan.handle, 1600) <= (8 << 20) < lib.cgb200_layer_workspace_bytes(plan.handle, 1600)
-    F = torch.tensor(case["F"], device=dev)
+    assert lib.cgb200_layer_fwd_workspace_bytes(plan.handle, B) <= (8 << 20) < lib.cgb200_layer_workspace_bytes(plan.handle, B)
+    F = torch.tensor(np.random.RandomState(35).randn(B, plan.n_F, 2).astype(np.float32), device=dev)
     W = torch.tensor(case["W"], device=dev)
     stds = torch.tensor(case["stds"], device=dev)
     want = plan.layer_fwd(F, W, stds, 1.0, 1e-5, _lib.FN_PRESENT)
