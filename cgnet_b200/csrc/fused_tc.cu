@@ -17,9 +17,13 @@
 //     degree into pipeline stage s (A tile written with st.shared, then fence.proxy.async + mbarrier arrive); its first
 //     lane also starts the bulk copy of the cell's packed weights into the stage;
 //   one MMA warp: a single lane waits for each stage, issues the 3 x (2T^2/8) tcgen05.mma of the cell and commits them
-//     to the stage's "empty" barrier; after the last cell it commits to the "done" barrier;
-//   epilogue: group 0 reads the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 = its own m) and
-//     writes O.
+//     to the stage's "empty" barrier;
+//   flush warps (one or two groups of four): the tensor core adds into its fp32 accumulator with truncation, so the error
+//     of a long contraction grows with the number of accumulation steps (measured 3e-3 at 180 k complex mid channels).
+//     The cells are therefore summed in chunks of kChunkSteps accumulation steps into two alternating accumulator
+//     regions; after each chunk a flush group reads the region with tcgen05.ld (a warp owns the TMEM lanes 32 (w % 4) ..
+//     + 31 = its own m) and adds it to running sums in registers with ordinary rounded fp32 adds, then hands the region
+//     back.  The flush warps write O at the end.
 // Every wait is bounded: a wait that runs out sets a flag in shared memory and a status word in global memory, all
 // roles then skip to the end, tensor memory is released and the kernel returns.
 #include <cuda_pipeline.h>
@@ -175,16 +179,19 @@ tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restric
 // Dynamic shared memory: S x { A high [128 x Kc], A low [128 x Kc], B high+low [2 x n_max x Kc] } floats,
 // then one CG band row per generator warp.
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int kChunkSteps = 384;   // tensor-core accumulation steps (one per MMA) summed in tensor memory before a flush
+
 template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
                     const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O, int B, int n_max,
-                    int max_n, int* __restrict__ status, int n_stages, uint32_t wait_limit, int idle_mma) {
+                    int max_n, int* __restrict__ status, int n_stages, int n_flush, uint32_t wait_limit, int idle_mma) {
     constexpr int Kc = 2 * T * T;            // real K extent of one cell
     constexpr int NV = T * T;
     constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
+    constexpr int kChunkCells = kChunkSteps / (3 * (Kc / 8));   // cells per chunk: three MMAs per K step of 8
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], chunk_full[2], chunk_free[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
@@ -197,7 +204,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
     const int N = npad[l];
     const int to_n = P.tO[l];
-    const uint32_t tmem_cols = N <= 32 ? 32u : N <= 64 ? 64u : 128u;
+    const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
     const size_t stage_floats = (size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc;
     float* stages = reinterpret_cast<float*>(smem_raw);
     float* cbuf = stages + n_stages * stage_floats + (size_t)warp * max_n;
@@ -209,7 +216,10 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
             mbar_init(&full_bar[s], 128);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&done_bar, 1);
+        for (int r = 0; r < 2; ++r) {
+            mbar_init(&chunk_full[r], 1);
+            mbar_init(&chunk_free[r], 4 * n_flush);   // one arrival per flush warp
+        }
         failed_flag = 0;
         fence_mbar_init();
     }
@@ -264,53 +274,83 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
             fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
             mbar_arrive(&full_bar[s]);
         }
-        // ---------------- epilogue (first generator group) ----------------
-        if (s == 0) {
-            const int b = g * 32 + lane;
-            float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
-            if (ncell > 0) ok = mbar_wait_warp(&done_bar, 0u, failed, wait_limit) && ok;   // warp-uniform
-            tc_fence_after();
-            for (int col0 = 0; col0 < N; col0 += 16) {
-                uint32_t rr[16];
-                if (ncell > 0 && ok) {
-                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
-                } else {   // a degree without cells is zero; a block that gave up marks its outputs
+    } else if (warp == gen_warps) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && !idle_mma) {
+            const uint32_t idesc = tc_idesc(128, N);
+            bool ok = true;
+            for (int k = 0; k < ncell && ok; ++k) {
+                const int s = k % n_stages, u = k / n_stages;
+                const int j = k / kChunkCells, r = j & 1;
+                const bool first = k - j * kChunkCells == 0;
+                // the flush warps have read this region's previous chunk (chunk j - 2)
+                if (first && j >= 2) ok = mbar_wait(&chunk_free[r], (uint32_t)(((j >> 1) - 1) & 1), failed, wait_limit);
+                if (!ok) break;
+                ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(r * N);
+                const uint32_t a_hi = smem_u32(stages + s * stage_floats);
+                const uint32_t a_lo = a_hi + 128 * Kc * 4;
+                const uint32_t b_hi = a_lo + 128 * Kc * 4;
+                const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) rr[j] = ncell > 0 ? kNaNBits : 0u;
+                for (int ks = 0; ks < Kc / 8; ++ks) {
+                    const uint64_t dah = smem_desc(a_hi + ks * 256, 128, kSbo), dal = smem_desc(a_lo + ks * 256, 128, kSbo);
+                    const uint64_t dbh = smem_desc(b_hi + ks * 256, 128, kSbo), dbl = smem_desc(b_lo + ks * 256, 128, kSbo);
+                    tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
+                    tc_mma_tf32(d, dal, dbh, idesc, 1u);
+                    tc_mma_tf32(d, dah, dbl, idesc, 1u);
                 }
-                if (live_m && b < B) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int to = (col0 >> 1) + j;
-                        if (to < to_n) out[(int64_t)to * n] = make_float2(__uint_as_float(rr[2 * j]), __uint_as_float(rr[2 * j + 1]));
-                    }
-                }
+                tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+                if (k - j * kChunkCells == kChunkCells - 1 || k == ncell - 1) tc_commit(&chunk_full[r]);   // chunk j is summed
             }
         }
-    } else if (lane == 0 && !idle_mma) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = tc_idesc(128, N);
+    } else {
+        // ---------------- flush warps: running sums in registers, then the output ----------------
+        const int fw = warp - gen_warps - 1;          // 0 .. 4 n_flush - 1
+        const int fg = fw >> 2;                       // flush group: columns [64 fg, 64 fg + 64) of the accumulator
+        const int wq = warp & 3;                      // the TMEM lane quarter this warp may read = its m inside the row tile
+        const int mi = m0 + wq;
+        const bool live_m = mi < n;
+        const int col_base = 64 * fg;
+        const int n_chunks = (ncell + kChunkCells - 1) / kChunkCells;
+        float run[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) run[i] = 0.f;
         bool ok = true;
-        for (int k = 0; k < ncell && ok; ++k) {
-            const int s = k % n_stages, u = k / n_stages;
-            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
+        for (int j = 0; j < n_chunks && ok; ++j) {
+            const int r = j & 1;
+            ok = mbar_wait_warp(&chunk_full[r], (uint32_t)((j >> 1) & 1), failed, wait_limit);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t a_hi = smem_u32(stages + s * stage_floats);
-            const uint32_t a_lo = a_hi + 128 * Kc * 4;
-            const uint32_t b_hi = a_lo + 128 * Kc * 4;
-            const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
 #pragma unroll
-            for (int ks = 0; ks < Kc / 8; ++ks) {
-                const uint64_t dah = smem_desc(a_hi + ks * 256, 128, kSbo), dal = smem_desc(a_lo + ks * 256, 128, kSbo);
-                const uint64_t dbh = smem_desc(b_hi + ks * 256, 128, kSbo), dbl = smem_desc(b_lo + ks * 256, 128, kSbo);
-                tc_mma_tf32(tmem_base, dah, dbh, idesc, (k > 0 || ks > 0) ? 1u : 0u);
-                tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
-                tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const int col0 = col_base + 16 * c4;
+                if (col0 < N) {   // warp-uniform
+                    uint32_t rr[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * N + col0), rr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]);
+                }
             }
-            tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&chunk_free[r]);   // the region may be overwritten by chunk j + 2
         }
-        if (ok && ncell > 0) tc_commit(&done_bar);
+        const int b = g * 32 + lane;
+        if (live_m && b < B) {
+            float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
+            const float nanv = __uint_as_float(kNaNBits);   // a block that gave up marks the outputs it owns
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int to = ((col_base + 16 * c4) >> 1) + i;
+                    if (to < to_n) out[(int64_t)to * n] = ok ? make_float2(run[16 * c4 + 2 * i], run[16 * c4 + 2 * i + 1]) : make_float2(nanv, nanv);
+                }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -376,11 +416,13 @@ template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
-                   int max_n, int* __restrict__ status, int n_stages, int64_t slice_stride, uint32_t wait_limit, int idle_mma) {
+                   int max_n, int* __restrict__ status, int n_stages, int n_flush, int64_t slice_stride, uint32_t wait_limit,
+                   int idle_mma) {
     using S = GwTcShape<T>;
     constexpr int MR = S::MR;
+    constexpr int kFlushChunks = kChunkSteps / 12;   // K chunks (32 samples = 4 K steps x 3 MMAs) summed in tensor memory before a flush
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], chunk_full[2], chunk_free[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
@@ -391,7 +433,7 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
     const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
     const int N = npad[l];
     const int to_n = P.tO[l], tff = P.tFF[l];
-    const uint32_t tmem_cols = N <= 32 ? 32u : N <= 64 ? 64u : 128u;
+    const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
     const uint32_t a_bytes = 16 * kGwSbo, b_bytes = (uint32_t)(n_max / 8) * kGwSbo;
     const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
     float* cbuf = reinterpret_cast<float*>(smem_raw + (size_t)n_stages * stage_bytes) + (size_t)warp * max_n;
@@ -406,7 +448,10 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
             mbar_init(&full_bar[s], 128);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&done_bar, 1);
+        for (int r = 0; r < 2; ++r) {
+            mbar_init(&chunk_full[r], 1);
+            mbar_init(&chunk_free[r], 4 * n_flush);   // one arrival per flush warp
+        }
         failed_flag = 0;
         fence_mbar_init();
     }
@@ -465,63 +510,93 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
             fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
             mbar_arrive(&full_bar[s]);
         }
-        // ---------------- epilogue (first generator group): warp w reads accumulator rows 32 w .. 32 w + 31 ----------------
-        if (s == 0) {
-            if (n_chunks > 0) ok = mbar_wait_warp(&done_bar, 0u, failed, wait_limit) && ok;   // warp-uniform
-            tc_fence_after();
-            const int row = wq * 32 + lane;
-            const int ec = row / MR, kk = row - ec * MR;   // cell of the block and real row inside it
-            const int idx = kk >> 1, i = idx / T, j = idx - i * T;
-            CellInfo ei{};
-            const bool e_live = ec < S::kCells && cell0 + ec < ncell;
-            if (e_live) ei = P.cell_info[c_begin + cell0 + ec];
-            const bool writer = e_live && (kk & 1) == 0 && i < ei.v1 && j < ei.v2;
-            const int ch = i * ei.tau2 + j;
-            const float sc = writer ? inv[ei.kch0 + ch] : 0.f;
-            float2* out = out_base + P.cumW[l] + ei.wch0 + ch;
-            for (int col0 = 0; col0 < N; col0 += 16) {
-                uint32_t rr[16];
-                if (n_chunks > 0 && ok) {
-                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)col0, rr);
-                } else {   // nothing to sum gives zero; a block that gave up marks its outputs
+    } else if (warp == gen_warps) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && !idle_mma) {
+            const uint32_t idesc = tc_idesc(128, N);
+            bool ok = true;
+            for (int q = 0; q < n_chunks && ok; ++q) {
+                const int s = q % n_stages, u = q / n_stages;
+                const int j = q / kFlushChunks, r = j & 1;
+                const bool first = q - j * kFlushChunks == 0;
+                // the flush warps have read this region's previous contents (flush chunk j - 2)
+                if (first && j >= 2) ok = mbar_wait(&chunk_free[r], (uint32_t)(((j >> 1) - 1) & 1), failed, wait_limit);
+                if (!ok) break;
+                ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(r * N);
+                const uint32_t a_hi = smem_u32(smem_raw + (size_t)s * stage_bytes);
+                const uint32_t a_lo = a_hi + a_bytes;
+                const uint32_t b_hi = a_lo + a_bytes;
+                const uint32_t b_lo = b_hi + b_bytes;
 #pragma unroll
-                    for (int cc = 0; cc < 16; ++cc) rr[cc] = n_chunks > 0 ? kNaNBits : 0u;
+                for (int ks = 0; ks < 4; ++ks) {   // 32 samples = 4 K steps of 8 = 2 core matrices each
+                    const uint32_t koff = ks * 2 * kGwLbo;
+                    const uint64_t dah = smem_desc(a_hi + koff, kGwLbo, kGwSbo), dal = smem_desc(a_lo + koff, kGwLbo, kGwSbo);
+                    const uint64_t dbh = smem_desc(b_hi + koff, kGwLbo, kGwSbo), dbl = smem_desc(b_lo + koff, kGwLbo, kGwSbo);
+                    tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
+                    tc_mma_tf32(d, dal, dbh, idesc, 1u);
+                    tc_mma_tf32(d, dah, dbl, idesc, 1u);
                 }
-#pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
-                    const float mr = __uint_as_float(rr[2 * cc]), mim = __uint_as_float(rr[2 * cc + 1]);
-                    const float orr = __shfl_xor_sync(0xffffffffu, mr, 1), oim = __shfl_xor_sync(0xffffffffu, mim, 1);
-                    const int to = (col0 >> 1) + cc;
-                    // even lane = row (k, re), its neighbour = row (k, im)
-                    if (writer && to < to_n) out[(int64_t)to * tff] = make_float2((mr + oim) * sc, (mim - orr) * sc);
-                }
+                tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+                if (q - j * kFlushChunks == kFlushChunks - 1 || q == n_chunks - 1) tc_commit(&chunk_full[r]);
             }
         }
-    } else if (lane == 0 && !idle_mma) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = tc_idesc(128, N);
+    } else {
+        // ---------------- flush warps: running sums of the accumulator in registers, then gW ----------------
+        // (the tensor core adds into its accumulator with truncation: long contractions are summed in pieces, see the
+        // forward kernel).  Warp w reads accumulator rows 32 (w % 4) .. + 31; flush group fg owns columns [64 fg, 64 fg + 64).
+        const int fw = warp - gen_warps - 1;
+        const int fg = fw >> 2;
+        const int wq = warp & 3;
+        const int col_base = 64 * fg;
+        const int n_flushes = (n_chunks + kFlushChunks - 1) / kFlushChunks;
+        float run[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) run[i] = 0.f;
         bool ok = true;
-        for (int q = 0; q < n_chunks && ok; ++q) {
-            const int s = q % n_stages, u = q / n_stages;
-            ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
+        for (int j = 0; j < n_flushes && ok; ++j) {
+            const int r = j & 1;
+            ok = mbar_wait_warp(&chunk_full[r], (uint32_t)((j >> 1) & 1), failed, wait_limit);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t a_hi = smem_u32(smem_raw + (size_t)s * stage_bytes);
-            const uint32_t a_lo = a_hi + a_bytes;
-            const uint32_t b_hi = a_lo + a_bytes;
-            const uint32_t b_lo = b_hi + b_bytes;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {   // 32 samples = 4 K steps of 8 = 2 core matrices each
-                const uint32_t koff = ks * 2 * kGwLbo;
-                const uint64_t dah = smem_desc(a_hi + koff, kGwLbo, kGwSbo), dal = smem_desc(a_lo + koff, kGwLbo, kGwSbo);
-                const uint64_t dbh = smem_desc(b_hi + koff, kGwLbo, kGwSbo), dbl = smem_desc(b_lo + koff, kGwLbo, kGwSbo);
-                tc_mma_tf32(tmem_base, dah, dbh, idesc, (q > 0 || ks > 0) ? 1u : 0u);
-                tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
-                tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const int col0 = col_base + 16 * c4;
+                if (col0 < N) {   // warp-uniform
+                    uint32_t rr[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * N + col0), rr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]);
+                }
             }
-            tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&chunk_free[r]);
         }
-        if (ok && n_chunks > 0) tc_commit(&done_bar);
+        const int row = wq * 32 + lane;
+        const int ec = row / MR, kk = row - ec * MR;   // cell of the block and real row inside it
+        const int idx = kk >> 1, i = idx / T, jj = idx - i * T;
+        CellInfo ei{};
+        const bool e_live = ec < S::kCells && cell0 + ec < ncell;
+        if (e_live) ei = P.cell_info[c_begin + cell0 + ec];
+        const bool writer = e_live && (kk & 1) == 0 && i < ei.v1 && jj < ei.v2;
+        const int ch = i * ei.tau2 + jj;
+        const float sc = writer ? inv[ei.kch0 + ch] : 0.f;
+        float2* out = out_base + P.cumW[l] + ei.wch0 + ch;
+        const float nanv = __uint_as_float(kNaNBits);   // a block that gave up marks the outputs it owns
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                const float mr = ok ? run[16 * c4 + 2 * cc] : nanv, mim = ok ? run[16 * c4 + 2 * cc + 1] : nanv;
+                const float orr = __shfl_xor_sync(0xffffffffu, mr, 1), oim = __shfl_xor_sync(0xffffffffu, mim, 1);
+                const int to = ((col_base + 16 * c4) >> 1) + cc;
+                // even lane = row (k, re), its neighbour = row (k, im)
+                if (writer && to < to_n) out[(int64_t)to * tff] = make_float2((mr + oim) * sc, (mim - orr) * sc);
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -842,7 +917,9 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     CGB_CUDA(cudaGetLastError());
     const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
     const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
-    int n_stages = (int)std::min<size_t>(kTcMaxStages, (220 * 1024 - cbuf_bytes) / stage_bytes);
+    // flush groups: one per 64 accumulator columns; generator groups (= stages) take the warps that are left
+    const int n_flush = n_max > 64 ? 2 : 1;
+    int n_stages = (int)std::min<size_t>(kTcMaxStages - n_flush, (220 * 1024 - cbuf_bytes) / stage_bytes);
     if (p->opt[CGB200_OPT_TC_STAGES] >= 2) n_stages = std::min(n_stages, p->opt[CGB200_OPT_TC_STAGES]);
     const size_t smem = n_stages * stage_bytes + cbuf_bytes;
     if (n_stages < 2) {
@@ -852,8 +929,8 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     auto kern = fused_fwd_tc_kernel<T>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
-    kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
-                                                                  n_max, p->max_n, p->d_status, n_stages, wait_polls(p),
+    kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
+                                                                  n_max, p->max_n, p->d_status, n_stages, n_flush, wait_polls(p),
                                                                   p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
@@ -890,7 +967,8 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     if (n_tiles == 0) return CGB200_OK;
     const size_t stage_bytes = (size_t)2 * 16 * kGwSbo + (size_t)2 * (n_max / 8) * kGwSbo;
     const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
-    int n_stages = (int)std::min<size_t>(kTcMaxStages, (kMaxDynSmem - cbuf_bytes) / stage_bytes);
+    const int n_flush = n_max > 64 ? 2 : 1;   // flush groups: one per 64 accumulator columns
+    int n_stages = (int)std::min<size_t>(kTcMaxStages - n_flush, (kMaxDynSmem - cbuf_bytes) / stage_bytes);
     if (p->opt[CGB200_OPT_TC_STAGES] >= 2) n_stages = std::min(n_stages, p->opt[CGB200_OPT_TC_STAGES]);
     if (n_stages < 2) {
         set_error("tensor-core weight gradient: pipeline stages do not fit in shared memory");
@@ -904,9 +982,9 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     auto kern = fused_gw_tc_kernel<T>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_GW_TC, st);
-    kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
+    kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
                                                                        slices > 1 ? gw_part : gW, G, n_max, p->max_n, p->d_status,
-                                                                       n_stages, p->d.w_len, wait_polls(p),
+                                                                       n_stages, n_flush, p->d.w_len, wait_polls(p),
                                                                        p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
     launch_end(K_GW_TC, st);
     CGB_CUDA(cudaGetLastError());

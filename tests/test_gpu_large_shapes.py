@@ -118,3 +118,32 @@ def test_tensor_core_variants_at_long_contractions():
         assert worst(O, O_want, case["tau_out"]) < TOL, tag
         assert worst(gF, gF_want, case["taus"]) < TOL, tag
         assert worst_w(gW, gW_want, case["t_ff"], case["tau_out"]) < TOL, tag
+
+
+def test_tensor_core_weight_gradient_over_a_long_batch():
+    """The weight gradient contracts over (sample, m): with a large batch in one slice the tensor-core kernel sums
+    thousands of accumulation steps per output.  Held to the CUDA-core kernel of the same plan, which sums in
+    registers with rounded adds (no oracle needed: the product for 2048 samples would not fit the CPU checker)."""
+    from cgnet_b200 import _lib, get_plan
+    dev = torch.device("cuda", 0)
+    taus, tau_out, B = [16] * 5, [16] * 5, 2048
+    small = make_case(taus, tau_out, 2, "default", seed=72)
+    plan = get_plan(small["lmax"], taus, tau_out, small["llls"], dev)
+    assert plan.tile == 4
+    rng = np.random.RandomState(73)
+    F = torch.tensor(rng.randn(B, plan.n_F, 2).astype(np.float32), device=dev)
+    gO = torch.tensor(rng.randn(B, plan.n_O, 2).astype(np.float32), device=dev)
+    W = torch.tensor(small["W"], device=dev)
+    stds = torch.tensor(small["stds"], device=dev)
+    got = {}
+    for tc in (0, 1):
+        plan.set_option(_lib.OPT_TC_GRAD_W, tc)
+        try:
+            _, gW = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT, gO, need_gF=False)
+            plan.check_status()
+        finally:
+            plan.set_option(_lib.OPT_TC_GRAD_W, _lib.AUTO)
+        got[tc] = gW.cpu().numpy()
+    err = worst_w(got[1], got[0], small["t_ff"], tau_out)
+    print(f"\n[parity] weight gradient over {B} samples, tensor cores vs CUDA cores: {err:.2e}")
+    assert err < TOL
