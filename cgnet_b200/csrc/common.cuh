@@ -256,6 +256,11 @@ struct cgb200_plan {
     const int* d_tc_tiles = nullptr;
     std::vector<int> tc_gw_tiles;       // tensor-core weight gradient: (l, first cell of a block of four) pairs, longest first
     const int* d_tc_gw_tiles = nullptr;
+    // CG table with every band row padded to a multiple of four floats (16-byte aligned rows: the four band rows a row
+    // tile of the staged tensor-core forward needs are then one cp.async.bulk), and each cell's offset into it
+    const float* d_cg_pad = nullptr;
+    std::vector<int> cell_cgpad;
+    const int* d_cell_cgpad = nullptr;
     int* d_status = nullptr;          // set to 1 by a kernel whose bounded wait ran out (cgb200_plan_status)
     std::vector<int> fwd_rows;        // (l, m+l) rows of the output, most expensive first (dynamic scheduling order)
     const int* d_fwd_rows = nullptr;

@@ -31,111 +31,14 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace cgb200 {
 
 constexpr int kTcMaxStages = 5;   // pipeline stages = generator groups; the launch picks as many as shared memory holds
 constexpr int kTcMaxThreads = 32 * (4 * kTcMaxStages + 1);
-constexpr uint32_t kNaNBits = 0x7fc00000u;   // what a block that gave up writes into the outputs it owns
-
-// ---- thin PTX wrappers --------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false when the limit (polls of mbarrier.try_wait) ran out or another
-// role already failed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < limit; ++spin) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if ((spin & 255) == 255 && *failed) return false;
-    }
-    *failed = 1;
-    return false;
-}
-// The same wait for a whole warp: every lane polls, and the warp gives up together if any lane did, so that the code
-// after it (warp-synchronous generator steps, tcgen05.ld.sync.aligned) never runs with diverged lanes.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, failed, limit) ? 1 : 0) != 0;
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier (addresses and size multiples of 16)
-__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
-                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], TF32 inputs, fp32 accumulate; one thread issues for the whole block
-__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` = byte distance between
-// the two core matrices an MMA reads along K, `sbo` = byte distance between consecutive 8-row groups.  Field layout:
-// [0,14) start address >> 4, [16,30) lbo >> 4, [32,46) sbo >> 4, [46,48) version = 1 on this architecture,
-// [61,64) swizzle mode = 0.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
-           ((uint64_t)1 << 46);
-}
-// Instruction descriptor of kind::tf32: fp32 accumulator ([4,6) = 1), A and B formats TF32 ([7,10) = [10,13) = 2), both
-// K-major ([15], [16] = 0), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ inline uint32_t tc_idesc(int M, int N) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-
+constexpr int kTcStagedThreads = kTcMaxThreads + 32;   // + the warp that stages the generators' operands
+constexpr int kOpRing = 16;       // ring entries (one per cell) the staging warp may run ahead of the generators
 // ---------------------------------------------------------------------------------------------------------------
 // Weight packing.  One block per cell: the T*T mid channels of the cell against all output channels of its degree,
 // scaled by 1/max(eps, std), expanded to the real form, split into TF32 high and low parts and stored in the order
@@ -179,7 +82,6 @@ tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restric
 // Dynamic shared memory: S x { A high [128 x Kc], A low [128 x Kc], B high+low [2 x n_max x Kc] } floats,
 // then one CG band row per generator warp.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kChunkSteps = 384;   // tensor-core accumulation steps (one per MMA) summed in tensor memory before a flush
 
 template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
@@ -294,10 +196,12 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
                 const uint32_t a_lo = a_hi + 128 * Kc * 4;
                 const uint32_t b_hi = a_lo + 128 * Kc * 4;
                 const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
+                const uint64_t dah0 = smem_desc(a_hi, 128, kSbo), dal0 = smem_desc(a_lo, 128, kSbo);
+                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo), dbl0 = smem_desc(b_lo, 128, kSbo);
 #pragma unroll
                 for (int ks = 0; ks < Kc / 8; ++ks) {
-                    const uint64_t dah = smem_desc(a_hi + ks * 256, 128, kSbo), dal = smem_desc(a_lo + ks * 256, 128, kSbo);
-                    const uint64_t dbh = smem_desc(b_hi + ks * 256, 128, kSbo), dbl = smem_desc(b_lo + ks * 256, 128, kSbo);
+                    const uint64_t dah = desc_advance(dah0, ks * 256), dal = desc_advance(dal0, ks * 256);
+                    const uint64_t dbh = desc_advance(dbh0, ks * 256), dbl = desc_advance(dbl0, ks * 256);
                     tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
                     tc_mma_tf32(d, dal, dbh, idesc, 1u);
                     tc_mma_tf32(d, dah, dbl, idesc, 1u);
@@ -309,6 +213,304 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     } else {
         // ---------------- flush warps: running sums in registers, then the output ----------------
         const int fw = warp - gen_warps - 1;          // 0 .. 4 n_flush - 1
+        const int fg = fw >> 2;                       // flush group: columns [64 fg, 64 fg + 64) of the accumulator
+        const int wq = warp & 3;                      // the TMEM lane quarter this warp may read = its m inside the row tile
+        const int mi = m0 + wq;
+        const bool live_m = mi < n;
+        const int col_base = 64 * fg;
+        const int n_chunks = (ncell + kChunkCells - 1) / kChunkCells;
+        float run[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) run[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_chunks && ok; ++j) {
+            const int r = j & 1;
+            ok = mbar_wait_warp(&chunk_full[r], (uint32_t)((j >> 1) & 1), failed, wait_limit);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const int col0 = col_base + 16 * c4;
+                if (col0 < N) {   // warp-uniform
+                    uint32_t rr[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * N + col0), rr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&chunk_free[r]);   // the region may be overwritten by chunk j + 2
+        }
+        const int b = g * 32 + lane;
+        if (live_m && b < B) {
+            float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
+            const float nanv = __uint_as_float(kNaNBits);   // a block that gave up marks the outputs it owns
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int to = ((col_base + 16 * c4) >> 1) + i;
+                    if (to < to_n) out[(int64_t)to * n] = ok ? make_float2(run[16 * c4 + 2 * i], run[16 * c4 + 2 * i + 1]) : make_float2(nanv, nanv);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, tmem_cols);
+    if (threadIdx.x == 0 && failed_flag) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same forward with everything a cell needs staged in shared memory ahead of time.
+//
+// Measured on the kernel above (lmax 10, 16 channels): with generation and MMAs both switched off, the skeleton alone -
+// per cell: wait for the stage, start the bulk copy of the cell's weights into it, store the A tile, wait for the copy,
+// issue, wait for completion - took half of the kernel's time, because the stage's chain "free -> weights copy -> MMA ->
+// free" is serial and the copy's latency (about 1.5 us from L2) sits in it once per cell; the generator's operand loads
+// from L2 (the slab of a sample group is far larger than L1) came second; the MMAs themselves were 10 %.
+// Here a staging warp runs up to kOpRing cells ahead of the generators and puts, per cell, into one entry of a byte ring:
+//   the four CG band rows of the block's m (one cp.async.bulk from a copy of the table whose rows are padded to 16 bytes),
+//   the rows of the two operand tiles those m can touch (two cp.async.bulk from the slab: they are contiguous there),
+//   the cell's packed weights (one cp.async.bulk),
+// with one mbarrier per entry counting the staging warp's arrival and the copies' bytes.  The generators read their
+// operands from shared memory, compute the tile in registers *before* they wait for their A stage to be free, and the
+// MMA warp takes the B operand straight from the ring entry; the entry goes back to the staging warp when the four
+// generator warps and the cell's MMAs (tcgen05.commit) are done with it.  A stage holds only the A tile.
+// ---------------------------------------------------------------------------------------------------------------
+struct OpEntry {
+    int band;         // ring offset (floats) of the four band rows, row stride (2 l2 + 1) rounded up to a multiple of 4
+    int s1, s2;       // ring offset (float2) of the t1 tile's / t2 tile's virtual row 0 (the fragment's m = -l)
+    int wgt;          // ring offset (floats) of the packed weights: high part, then low part
+    short l1, l2;
+};
+
+template <int T>
+__global__ void __launch_bounds__(kTcStagedThreads)
+fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad,
+                           const int64_t* __restrict__ pack_off, const float* __restrict__ cg_pad, const int* __restrict__ cell_cgpad,
+                           const float2* __restrict__ SF, const float* __restrict__ pack,
+                           float2* __restrict__ O, int B, int* __restrict__ status, int n_stages, int n_abuf, int n_flush,
+                           int ring_bytes, int stage_rows, uint32_t wait_limit, int idle_mma) {
+    constexpr int Kc = 2 * T * T;            // real K extent of one cell
+    constexpr int NV = T * T;
+    constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
+    constexpr int kChunkCells = kChunkSteps / (3 * (Kc / 8));
+    constexpr int kRow = T * 32;             // float2 per operand row (T channels x 32 samples)
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kTcMaxStages], empty_bar[kTcMaxStages], chunk_full[2], chunk_free[2];
+    __shared__ __align__(8) uint64_t op_full[kOpRing], op_empty[kOpRing];
+    __shared__ OpEntry op_tab[kOpRing];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed_flag;
+
+    const int l = tiles[2 * blockIdx.x], m0 = tiles[2 * blockIdx.x + 1];
+    const int g = blockIdx.y;
+    const int n = 2 * l + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
+    const int N = npad[l];
+    const int to_n = P.tO[l];
+    const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
+    constexpr size_t stage_floats = (size_t)2 * 128 * Kc;   // A tile, high and low part
+    float* stages = reinterpret_cast<float*>(smem_raw);
+    unsigned char* ring = smem_raw + (size_t)n_abuf * stage_floats * sizeof(float);
+    float* ringf = reinterpret_cast<float*>(ring);
+    float2* ring2 = reinterpret_cast<float2*>(ring);
+    const int gen_warps = 4 * n_stages;
+    volatile int* failed = &failed_flag;
+
+    if (threadIdx.x == 0) {
+        for (int a = 0; a < n_abuf; ++a) {
+            mbar_init(&full_bar[a], 4);      // one arrival per generator warp
+            mbar_init(&empty_bar[a], 1);
+        }
+        for (int r = 0; r < 2; ++r) {
+            mbar_init(&chunk_full[r], 1);
+            mbar_init(&chunk_free[r], 4 * n_flush);
+        }
+        for (int e = 0; e < kOpRing; ++e) {
+            mbar_init(&op_full[e], 1);     // the staging warp's arrival + the bytes of its copies
+            mbar_init(&op_empty[e], 5);    // four generator warps + the completion of the cell's MMAs
+        }
+        failed_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp < gen_warps) {
+        // ---------------- generators ----------------
+        const int s = warp >> 2, wq = warp & 3;
+        const int mi = m0 + wq;
+        const bool live_m = mi < n;
+        const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;   // this lane's view of the group's slab (operands not staged)
+        const int r = wq * 32 + lane;
+        const size_t row_off = (size_t)(r >> 3) * (Kc / 4) * 8 + (r & 7);   // this lane's row inside an A tile, in float4
+        bool ok = true;
+        // group s generates the cells s, s + S, ...; cell k goes to A buffer k % n_abuf (more buffers than groups: a group
+        // stores its next tile while the MMAs of its previous one are still in flight)
+        for (int k = s; k < ncell && ok; k += n_stages) {
+            const int e = k % kOpRing;
+            const int ab = k % n_abuf, ua = k / n_abuf;
+            float4* row_hi = reinterpret_cast<float4*>(stages + ab * stage_floats) + row_off;
+            float4* row_lo = row_hi + 128 * Kc / 4;
+            ok = mbar_wait_warp(&op_full[e], (uint32_t)((k / kOpRing) & 1), failed, wait_limit);   // the cell's entry is staged
+            if (!ok) break;
+            float2 v[NV];
+            if (live_m) {
+                const OpEntry oe = op_tab[e];
+                const float* crow = ringf + oe.band + wq * ((2 * oe.l2 + 4) & ~3);
+                if (stage_rows) gen_slab<T, false>(v, crow, ring2 + oe.s1 + lane, ring2 + oe.s2 + lane, mi - l, oe.l1, oe.l2);
+                else gen_slab<T, false, true>(v, crow, slab + (int64_t)oe.s1 * 32, slab + (int64_t)oe.s2 * 32, mi - l, oe.l1, oe.l2);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = make_float2(0.f, 0.f);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&op_empty[e]);   // this warp is done reading the entry
+            if (ua > 0) ok = mbar_wait_warp(&empty_bar[ab], (uint32_t)((ua - 1) & 1), failed, wait_limit);   // the buffer's previous MMAs are done
+            if (!ok) break;
+#pragma unroll
+            for (int q = 0; q < Kc / 4; ++q) {
+                const float2 x0 = v[2 * q], x1 = v[2 * q + 1];
+                float4 h, w;
+                h.x = to_tf32(x0.x); h.y = to_tf32(x0.y); h.z = to_tf32(x1.x); h.w = to_tf32(x1.y);
+                w.x = x0.x - h.x; w.y = x0.y - h.y; w.z = x1.x - h.z; w.w = x1.y - h.w;
+                row_hi[q * 8] = h;
+                row_lo[q * 8] = w;
+            }
+            fence_proxy_async();   // make the generic-proxy stores visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[ab]);
+        }
+    } else if (warp == gen_warps) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && !idle_mma) {
+            const uint32_t idesc = tc_idesc(128, N);
+            bool ok = true;
+            for (int k = 0; k < ncell && ok; ++k) {
+                const int s = k % n_abuf, u = k / n_abuf;   // A buffer of the cell and its use count
+                const int e = k % kOpRing;
+                const int j = k / kChunkCells, r = j & 1;
+                const bool first = k - j * kChunkCells == 0;
+                if (first && j >= 2) ok = mbar_wait(&chunk_free[r], (uint32_t)(((j >> 1) - 1) & 1), failed, wait_limit);
+                if (!ok) break;
+                ok = mbar_wait(&op_full[e], (uint32_t)((k / kOpRing) & 1), failed, wait_limit);   // the weights have landed
+                if (!ok) break;
+                const uint32_t wgt = smem_u32(ringf + op_tab[e].wgt);
+                ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(r * N);
+                const uint32_t a_hi = smem_u32(stages + s * stage_floats);
+                const uint32_t a_lo = a_hi + 128 * Kc * 4;
+                const uint32_t b_hi = wgt;
+                const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
+                const uint64_t dah0 = smem_desc(a_hi, 128, kSbo), dal0 = smem_desc(a_lo, 128, kSbo);
+                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo), dbl0 = smem_desc(b_lo, 128, kSbo);
+#pragma unroll
+                for (int ks = 0; ks < Kc / 8; ++ks) {
+                    const uint64_t dah = desc_advance(dah0, ks * 256), dal = desc_advance(dal0, ks * 256);
+                    const uint64_t dbh = desc_advance(dbh0, ks * 256), dbl = desc_advance(dbl0, ks * 256);
+                    tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
+                    tc_mma_tf32(d, dal, dbh, idesc, 1u);
+                    tc_mma_tf32(d, dah, dbl, idesc, 1u);
+                }
+                tc_commit(&empty_bar[s]);    // the MMAs above have finished reading the A stage ...
+                tc_commit(&op_empty[e]);     // ... and the entry's weights
+                if (k - j * kChunkCells == kChunkCells - 1 || k == ncell - 1) tc_commit(&chunk_full[r]);
+            }
+        }
+    } else if (warp == gen_warps + 1) {
+        // ---------------- staging warp ----------------
+        // All lanes run the ring bookkeeping alike (the waits are warp-wide); lane 0 issues the copies.  The cell records
+        // are fetched 32 at a time, one per lane, a batch ahead of their use, and handed out by shuffles.
+        const int mt_lo = m0 - l, mt_hi = min(m0 + 3, n - 1) - l;   // the block's m values
+        const int mrows = mt_hi - mt_lo + 1;
+        const float2* slab0 = SF + (int64_t)g * P.nSF * 32;
+        const int ring_f2 = ring_bytes / 8;
+        const uint32_t wgt_bytes = (uint32_t)(2 * N * Kc * sizeof(float));
+        int start[kOpRing];     // ring offset (float2) where each live entry begins
+        int head = 0, tail = 0; // the live entries occupy [tail, head) of the ring, circularly
+        int kt = 0;             // oldest cell whose entry has not been handed back
+        int last = -1;          // newest cell staged
+        bool ok = true;
+        // this lane's cell of the current and of the next batch: (o1, o2, l1 | l2 << 16, padded band offset)
+        int4 cur = make_int4(0, 0, 0, 0), nxt = make_int4(0, 0, 0, 0);
+        auto fetch = [&](int k0) -> int4 {
+            const int c = k0 + lane;
+            if (c >= ncell) return make_int4(0, 0, 0, 0);
+            const CellInfo x = P.cell_info[c_begin + c];
+            return make_int4(x.o1, x.o2, (int)x.l1 | ((int)x.l2 << 16), cell_cgpad[c_begin + c]);
+        };
+        nxt = fetch(0);
+        for (int k = 0; k < ncell && ok; ++k) {
+            if ((k & 31) == 0) {
+                cur = nxt;
+                nxt = fetch(k + 32);
+            }
+            const int src = k & 31;
+            const int o1 = __shfl_sync(0xffffffffu, cur.x, src), o2 = __shfl_sync(0xffffffffu, cur.y, src);
+            const int ll = __shfl_sync(0xffffffffu, cur.z, src), cgp = __shfl_sync(0xffffffffu, cur.w, src);
+            const int l1 = ll & 0xffff, l2 = ll >> 16, n2p = (2 * l2 + 4) & ~3;
+            // rows (m index + l of the fragment) the block's m values touch: m1 = m - m2, m2 over the band
+            const int r1_lo = max(-l1, mt_lo - l2) + l1, r1_hi = min(l1, mt_hi + l2) + l1;
+            const int r2_lo = max(-l2, mt_lo - l1) + l2, r2_hi = min(l2, mt_hi + l1) + l2;
+            const int n1r = stage_rows ? (r1_hi - r1_lo + 1) * kRow : 0, n2r = stage_rows ? (r2_hi - r2_lo + 1) * kRow : 0;   // float2 per tile
+            const int band_f2 = ((4 * n2p + 31) & ~31) / 2;                                    // 128-byte granules
+            const int need = band_f2 + n1r + n2r + (int)(wgt_bytes / 8);
+            int at = -1;
+            while (ok) {
+                if (k - kt < kOpRing) {
+                    if (kt == k) { head = tail = 0; at = 0; }                          // nothing live: start over
+                    else if (head >= tail) {
+                        if (head + need <= ring_f2) at = head;
+                        else if (need < tail) at = 0;                                   // wrap: the gap at the end stays unused
+                    } else if (head + need < tail) at = head;
+                    if (at >= 0) break;
+                }
+                // entries come back in cell order as far as this warp is concerned: wait for the oldest live one
+                ok = mbar_wait_warp(&op_empty[kt % kOpRing], (uint32_t)((kt / kOpRing) & 1), failed, wait_limit);
+                ++kt;
+                tail = kt < k ? start[kt % kOpRing] : head;
+            }
+            if (!ok) break;
+            const int e = k % kOpRing;
+            start[e] = at;
+            head = at + need;
+            if (kt == k) tail = at;
+            if (lane == 0) {
+                OpEntry oe;
+                oe.band = 2 * at;
+                oe.s1 = stage_rows ? at + band_f2 - r1_lo * kRow : o1;   // ring offset of the staged rows, or the tile's slab offset
+                oe.s2 = stage_rows ? at + band_f2 + n1r - r2_lo * kRow : o2;
+                oe.wgt = 2 * (at + band_f2 + n1r + n2r);
+                oe.l1 = (short)l1;
+                oe.l2 = (short)l2;
+                op_tab[e] = oe;
+                const uint32_t band_bytes = (uint32_t)(mrows * n2p) * 4u;
+                // release: the table entry becomes visible to the waiters
+                mbar_arrive_expect_tx(&op_full[e], band_bytes + (uint32_t)(n1r + n2r) * 8u + wgt_bytes);
+                bulk_g2s(ringf + oe.band, cg_pad + cgp + m0 * n2p, band_bytes, &op_full[e]);
+                if (stage_rows) {
+                    bulk_g2s(ring2 + at + band_f2, slab0 + (int64_t)(o1 + r1_lo * T) * 32, (uint32_t)n1r * 8u, &op_full[e]);
+                    bulk_g2s(ring2 + at + band_f2 + n1r, slab0 + (int64_t)(o2 + r2_lo * T) * 32, (uint32_t)n2r * 8u, &op_full[e]);
+                }
+                bulk_g2s(ringf + oe.wgt, pack + pack_off[l] + (int64_t)k * 2 * N * Kc, wgt_bytes, &op_full[e]);
+            }
+            last = k;
+        }
+        // a block that gave up may leave before the newest entries were consumed: let their copies land first
+        if (lane == 0 && (!ok || *failed))
+            for (int k = max(0, last - kOpRing + 1); k <= last; ++k) mbar_drain(&op_full[k % kOpRing], (uint32_t)((k / kOpRing) & 1), wait_limit);
+    } else {
+        // ---------------- flush warps: running sums in registers, then the output ----------------
+        const int fw = warp - gen_warps - 2;          // 0 .. 4 n_flush - 1
         const int fg = fw >> 2;                       // flush group: columns [64 fg, 64 fg + 64) of the accumulator
         const int wq = warp & 3;                      // the TMEM lane quarter this warp may read = its m inside the row tile
         const int mi = m0 + wq;
@@ -530,11 +732,13 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
                 const uint32_t a_lo = a_hi + a_bytes;
                 const uint32_t b_hi = a_lo + a_bytes;
                 const uint32_t b_lo = b_hi + b_bytes;
+                const uint64_t dah0 = smem_desc(a_hi, kGwLbo, kGwSbo), dal0 = smem_desc(a_lo, kGwLbo, kGwSbo);
+                const uint64_t dbh0 = smem_desc(b_hi, kGwLbo, kGwSbo), dbl0 = smem_desc(b_lo, kGwLbo, kGwSbo);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {   // 32 samples = 4 K steps of 8 = 2 core matrices each
                     const uint32_t koff = ks * 2 * kGwLbo;
-                    const uint64_t dah = smem_desc(a_hi + koff, kGwLbo, kGwSbo), dal = smem_desc(a_lo + koff, kGwLbo, kGwSbo);
-                    const uint64_t dbh = smem_desc(b_hi + koff, kGwLbo, kGwSbo), dbl = smem_desc(b_lo + koff, kGwLbo, kGwSbo);
+                    const uint64_t dah = desc_advance(dah0, koff), dal = desc_advance(dal0, koff);
+                    const uint64_t dbh = desc_advance(dbh0, koff), dbl = desc_advance(dbl0, koff);
                     tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
                     tc_mma_tf32(d, dal, dbh, idesc, 1u);
                     tc_mma_tf32(d, dah, dbl, idesc, 1u);
@@ -915,12 +1119,61 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
         tc_pack_kernel<T><<<p->d.n_cells, 256, 0, st>>>(p->d, p->d_tc_npad, p->d_tc_pack_off, W, inv, pack);
     launch_end(K_TC_PACK, st);
     CGB_CUDA(cudaGetLastError());
-    const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
-    const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
     // flush groups: one per 64 accumulator columns; generator groups (= stages) take the warps that are left
     const int n_flush = n_max > 64 ? 2 : 1;
-    int n_stages = (int)std::min<size_t>(kTcMaxStages - n_flush, (220 * 1024 - cbuf_bytes) / stage_bytes);
-    if (p->opt[CGB200_OPT_TC_STAGES] >= 2) n_stages = std::min(n_stages, p->opt[CGB200_OPT_TC_STAGES]);
+    const int s_cap = p->opt[CGB200_OPT_TC_STAGES] >= 2 ? std::min(kTcMaxStages - n_flush, p->opt[CGB200_OPT_TC_STAGES]) : kTcMaxStages - n_flush;
+    const int idle = p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0;
+
+    // Staged variant: a stage holds the A tile only; the ring takes what is left and must hold the largest cell (band rows,
+    // the operand rows a row tile of four m can touch, the packed weights).  Preferred with room for two such cells.
+    // Off unless asked for (CGB200_OPT_TC_STAGED 1: band rows, operand rows and weights staged; 2: band rows and weights only,
+    // operands read through L1): measured on B200 within +-10 % of the kernel above at every shape tried (lmax 10 with 16,
+    // 32, 64 channels, lmax 14 with 16, lmax 20 MST with 32), because both are bounded by the one thread that issues the
+    // block's MMAs - about 65 cycles per tcgen05.mma, 12 per cell, each re-reading its 4 KB A tile from shared memory for
+    // only 2 tau_out output columns - and, with the operand rows staged, by how few cells fit the ring.
+    if (p->opt[CGB200_OPT_TC_STAGED] >= 1 && p->d_cg_pad != nullptr) {
+        const bool stage_rows = p->opt[CGB200_OPT_TC_STAGED] == 1;
+        size_t need_max = 0;
+        for (const TripleRec& t : p->triples) {
+            if (p->tO[t.l] == 0) continue;
+            const int rows1 = stage_rows ? std::min(2 * t.l1 + 1, 2 * t.l2 + 1 + 3) : 0, rows2 = stage_rows ? 2 * t.l2 + 1 : 0;
+            const size_t band = (size_t)((4 * ((2 * t.l2 + 4) & ~3) + 31) & ~31) * sizeof(float);
+            need_max = std::max(need_max, band + (size_t)(rows1 + rows2) * T * 32 * sizeof(float2) + (size_t)2 * p->tc_npad[t.l] * Kc * sizeof(float));
+        }
+        const size_t a_bytes = (size_t)2 * 128 * Kc * sizeof(float);
+        // A buffers: as many as leave a ring of two of the largest cells (at least one), at most kTcMaxStages
+        int NA = 0;
+        size_t ring = 0;
+        const int na_cap = p->opt[CGB200_OPT_TC_ABUF] >= 2 ? std::min(kTcMaxStages, p->opt[CGB200_OPT_TC_ABUF]) : 4;
+        for (int pass = 0; pass < 2 && NA == 0; ++pass)
+            for (int cand = na_cap; cand >= 2; --cand) {
+                if (cand * a_bytes >= kMaxDynSmem) continue;
+                const size_t r = (kMaxDynSmem - cand * a_bytes) & ~(size_t)127;
+                if (r >= (pass == 0 ? 2 * need_max : need_max + 128)) {
+                    NA = cand;
+                    ring = r;
+                    break;
+                }
+            }
+        const int S = std::min(s_cap, NA);   // generator groups (never more than A buffers: that combination ran into its bounded waits)
+        if (NA >= 2) {
+            const size_t smem = NA * a_bytes + ring;
+            auto kern = fused_fwd_tc_staged_kernel<T>;
+            CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            launch_begin(K_FWD_TC, st);
+            kern<<<dim3(n_tiles, G), 32 * (4 * S + 2 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, p->d_cg_pad,
+                                                                            p->d_cell_cgpad, SF, pack, O, B, p->d_status, S, NA, n_flush, (int)ring,
+                                                                            stage_rows ? 1 : 0, wait_polls(p), idle);
+            launch_end(K_FWD_TC, st);
+            CGB_CUDA(cudaGetLastError());
+            return CGB200_OK;
+        }
+        set_error("tensor-core forward: a cell's operand rows and weights do not fit the shared-memory ring (lmax too large)");
+        return CGB200_ERR_UNSUPPORTED;
+    }
+    const size_t stage_bytes = ((size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc) * sizeof(float);
+    const size_t cbuf_bytes = (size_t)(4 * kTcMaxStages + 1) * p->max_n * sizeof(float);
+    const int n_stages = (int)std::min<size_t>(s_cap, (220 * 1024 - cbuf_bytes) / stage_bytes);
     const size_t smem = n_stages * stage_bytes + cbuf_bytes;
     if (n_stages < 2) {
         set_error("tensor-core forward: pipeline stages do not fit in shared memory");
@@ -930,8 +1183,7 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
     kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
-                                                                  n_max, p->max_n, p->d_status, n_stages, n_flush, wait_polls(p),
-                                                                  p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
+                                                                  n_max, p->max_n, p->d_status, n_stages, n_flush, wait_polls(p), idle);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;

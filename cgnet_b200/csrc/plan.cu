@@ -107,6 +107,19 @@ __global__ void cg_table_kernel(float* __restrict__ cg, const int* __restrict__ 
     }
 }
 
+// Copy of the CG table with rows padded to a multiple of four floats; block per triple.
+__global__ void cg_pad_kernel(const float* __restrict__ cg, float* __restrict__ out, const TripleRec* __restrict__ triples,
+                              const int64_t* __restrict__ poff, int n_triples) {
+    const int k = blockIdx.x;
+    if (k >= n_triples) return;
+    const TripleRec t = triples[k];
+    const int n = 2 * t.l + 1, n2 = 2 * t.l2 + 1, n2p = (n2 + 3) & ~3;
+    for (int e = threadIdx.x; e < n * n2p; e += blockDim.x) {
+        const int r = e / n2p, c = e - r * n2p;
+        out[poff[k] + e] = c < n2 ? cg[t.cgoff + r * n2 + c] : 0.f;
+    }
+}
+
 static int decode_and_check(int lmax, const int32_t* llls, int n, std::vector<int>& ls, std::vector<int>& l1s,
                             std::vector<int>& l2s) {
     CGB_REQUIRE(lmax >= 0 && lmax <= kMaxLmax, "lmax out of range [0, 511]");
@@ -670,6 +683,25 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
     if ((rc = build_table(cg, cgoff, lmax, llls, n, nullptr))) return rc;
     d.cg = cg;
     p->cg_len = cgoff;
+    if (p->tc_ok && n > 0) {   // padded copy for the staged tensor-core forward
+        std::vector<int64_t> poff(n + 1, 0);
+        for (int k = 0; k < n; ++k) {
+            const TripleRec& t = p->triples[k];
+            poff[k + 1] = poff[k] + (int64_t)(2 * t.l + 1) * ((2 * t.l2 + 1 + 3) & ~3);
+        }
+        CGB_REQUIRE(poff[n] < (1ll << 31), "CG table too long");
+        for (const CellRec& c : p->cells) p->cell_cgpad.push_back((int)poff[c.triple]);
+        if ((rc = upload(p, p->cell_cgpad, &p->d_cell_cgpad))) return rc;
+        const int64_t* d_poff = nullptr;
+        if ((rc = upload(p, poff, &d_poff))) return rc;
+        float* pad = nullptr;
+        CGB_CUDA(cudaMalloc(&pad, poff[n] * sizeof(float)));
+        p->allocations.push_back(pad);
+        cg_pad_kernel<<<n, 128>>>(cg, pad, d.triples, d_poff, n);
+        CGB_CUDA(cudaGetLastError());
+        CGB_CUDA(cudaDeviceSynchronize());
+        p->d_cg_pad = pad;
+    }
 
     guard.p = nullptr;
     *out = p;
@@ -707,6 +739,8 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
     if (value != CGB200_AUTO) {
         switch (option) {
             case CGB200_OPT_TC_STAGES: CGB_REQUIRE(value >= 2, "CGB200_OPT_TC_STAGES must be at least 2"); break;
+            case CGB200_OPT_TC_ABUF: CGB_REQUIRE(value >= 2, "CGB200_OPT_TC_ABUF must be at least 2"); break;
+            case CGB200_OPT_TC_STAGED: CGB_REQUIRE(value >= 0 && value <= 2, "CGB200_OPT_TC_STAGED must be CGB200_AUTO, 0, 1 or 2"); break;
             case CGB200_OPT_WAIT_POLLS: CGB_REQUIRE(value >= 1, "CGB200_OPT_WAIT_POLLS must be positive"); break;
             default: CGB_REQUIRE(value == 0 || value == 1, "option value must be CGB200_AUTO, 0 or 1"); break;
         }

@@ -98,7 +98,7 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 #define CGB200_OPT_TC_FWD           0   /* forward on tcgen05 tensor cores (tile edge 2 or 4, full product)            */
 #define CGB200_OPT_TC_GRAD_W        1   /* weight gradient on tensor cores (tile edge 4 or 5)                            */
 #define CGB200_OPT_TC_GRAD_F        2   /* first phase of the input gradient on tensor cores (tile edge 4)               */
-#define CGB200_OPT_TC_STAGES        3   /* upper limit of the tensor-core kernels' pipeline depth (>= 2)                 */
+#define CGB200_OPT_TC_STAGES        3   /* upper limit of the tensor-core kernels' generator groups = pipeline stages (>= 2) */
 #define CGB200_OPT_FWD_SLAB         4   /* CUDA-core forward: persistent blocks with the slab in shared memory           */
 #define CGB200_OPT_GRAD_F_SPLIT     5   /* input gradient: rows of phase 2 split into two channel groups                 */
 #define CGB200_OPT_STATS_SPLIT      6   /* statistics: two blocks per cell                                               */
@@ -107,7 +107,11 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 #define CGB200_OPT_TEST_IDLE_MMA    9   /* test hook: the tensor-core kernels' MMA warp issues nothing, so every wait on
                                            it runs out; exercises the give-up path (status word, NaN output) without a
                                            fault, a trap or an endless loop                                              */
-#define CGB200_OPT_COUNT            10
+#define CGB200_OPT_TC_STAGED        10  /* tensor-core forward, off by default: 1 = a staging warp bulk-copies each cell's CG
+                                           band rows, operand rows and packed weights into a shared-memory ring ahead of the
+                                           generators, 2 = band rows and weights only                                       */
+#define CGB200_OPT_TC_ABUF          11  /* staged tensor-core forward: upper limit of the A-tile buffers (>= 2)                */
+#define CGB200_OPT_COUNT            12
 int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
 int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
 

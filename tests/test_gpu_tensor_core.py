@@ -210,3 +210,20 @@ def test_unsupported_variant_is_refused():
     assert plan.tile == 5
     with pytest.raises(RuntimeError, match="no tables"):
         plan.set_option(_lib.OPT_TC_FWD, 1)
+
+
+@pytest.mark.parametrize("staged", [1, 2])
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
+                                                 ([8] * 11, [32] * 11, 20, "default"), ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default")])
+def test_staged_tensor_core_forward_equals_unstaged(taus, tau_out, B, mode, staged):
+    """The opt-in forward whose staging warp bulk-copies each cell's band rows, operand rows and weights into a
+    shared-memory ring (1) or the band rows and weights only (2): same arithmetic in the same order as the default
+    tensor-core forward, so the same bits."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, mode, seed=59)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
+    assert plan.tile == 4
+    want, _ = _forward(plan, case, True, False, tc=True)
+    with option(plan, _lib.OPT_TC_STAGED, staged):
+        got, _ = _forward(plan, case, True, False, tc=True)
+    assert np.array_equal(got, want)
