@@ -4,5 +4,6 @@ from . import cgutils as CGutils  # noqa: F401
 from .cg_layers import (CGBN_cuda, CG_woFilter_cuda, MyBatchNormWeightMM_cuda, Plan, get_plan,  # noqa: F401
                         precomputeCG)
 from .cgnet import SphericalCNN, SphericalCNN_fast  # noqa: F401
+from .s2_sph import SHProjector  # noqa: F401
 
 __version__ = "0.1.0"

@@ -10,7 +10,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu"]
+SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu", "sh_project.cu"]
 LIB = os.path.join(HERE, "libcgnet_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-O2"]

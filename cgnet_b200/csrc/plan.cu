@@ -30,7 +30,8 @@ int cuda_fail(cudaError_t e, const char* what) {
 static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_product_bwd", "fn_stats", "wmm_fwd",
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
-                                            "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor", "fused_grad_f_tensor"};
+                                            "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor", "fused_grad_f_tensor",
+                                            "sh_pack", "sh_project_tensor"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;

@@ -95,9 +95,10 @@ cg_bwd_gather_kernel(PlanDev P, const float2* __restrict__ F, const float2* __re
             const float* C = P.cg + tr.cgoff;
             const float2* F2 = Fb + tr.f2off;
             const float2* G = Gb + tr.ffoff;
-            for (int m2i = 0; m2i < n2; ++m2i) {
-                const int mi = (mt - lt) + (m2i - tr.l2) + tr.l;   // m + l
-                if (mi < 0 || mi >= n) continue;
+            // m + l = (mt - lt) + (m2i - l2) + l must fall inside [0, n): only that range of m2 is visited
+            const int shift = (mt - lt) - tr.l2 + tr.l;
+            for (int m2i = max(0, -shift); m2i < min(n2, n - shift); ++m2i) {
+                const int mi = shift + m2i;   // m + l
                 const float c = C[mi * n2 + m2i];
                 if (DW) {
                     float2 f2 = F2[t * n2 + m2i];
@@ -121,9 +122,9 @@ cg_bwd_gather_kernel(PlanDev P, const float2* __restrict__ F, const float2* __re
             const float* C = P.cg + tr.cgoff;
             const float2* F1 = Fb + tr.f1off;
             const float2* G = Gb + tr.ffoff;
-            for (int m1i = 0; m1i < n1; ++m1i) {
-                const int mi = (m1i - tr.l1) + (mt - lt) + tr.l;
-                if (mi < 0 || mi >= n) continue;
+            const int shift = (mt - lt) - tr.l1 + tr.l;
+            for (int m1i = max(0, -shift); m1i < min(n1, n - shift); ++m1i) {
+                const int mi = shift + m1i;
                 const float c = C[mi * n2 + mt];
                 if (DW) {
                     float2 f1 = F1[t * n1 + m1i];
@@ -198,32 +199,64 @@ fn_stats_kernel(PlanDev P, const float2* __restrict__ FF, float* __restrict__ st
     }
 }
 
-// Mixing forward, one thread per output element (CGNet/cudaCG/cudaCG_FNWMM.cu:81-123).
-__global__ void __launch_bounds__(256)
+// Mixing forward  O_l[b] = W_l diag(1/sigma) FF_l[b]  (CGNet/cudaCG/cudaCG_FNWMM.cu:81-123, which runs one thread per
+// output element and so reads every FF element tau_out times).  Here a block owns (degree l, sample b) and reads
+// FF_l[b], a contiguous (t_FF x (2l+1)) matrix, exactly once with coalesced loads: thread <-> (row slot kk, column m),
+// walking the rows kk, kk + KC, ...; it keeps the partial sums of up to kWmmTo output channels for its column in
+// registers (the weights W[to][k] / sigma_k of a row are the same for the threads of a row slot: broadcast loads), and
+// the row slots are added in slot order through shared memory, so the sum has a fixed order.
+constexpr int kWmmTo = 16;
+__global__ void __launch_bounds__(kStatThreads)
 wmm_fwd_kernel(PlanDev P, const float2* __restrict__ FF, const float2* __restrict__ W, const float* __restrict__ stds,
                float eps, float2* __restrict__ O, int B) {
-    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= P.n_O) return;
-    const int l = find_degree(P.cumO, P.lmax + 1, e);
+    __shared__ float2 red[kStatThreads];
+    const int l = blockIdx.y;
     const int n = 2 * l + 1;
-    const int r = (int)(e - P.cumO[l]);
-    const int to = r / n, mi = r - to * n;
-    const int tff = P.tFF[l];
-    const float2* Wrow = W + P.cumW[l] + (int64_t)to * tff;
+    const int tff = P.tFF[l], to_n = P.tO[l];
+    if (to_n == 0) return;
+    const int KC = max(1, kStatThreads / n);   // row slots: KC * n <= kStatThreads (n <= kStatThreads is checked on the host)
+    const int tid = threadIdx.x;
+    const int kk = tid / n, mi = tid - kk * n;
+    const bool live = kk < KC;
+    const float2* Wl = W + P.cumW[l];
     const float* sd = stds ? stds + P.cumT[l] : nullptr;
-    for (int b = blockIdx.y; b < B; b += gridDim.y) {
+    for (int b = blockIdx.x; b < B; b += gridDim.x) {
         const float2* src = FF + (int64_t)b * P.n_FF + P.cumFF[l] + mi;
-        float2 acc = make_float2(0.f, 0.f);
-        for (int k = 0; k < tff; ++k) {
-            float2 w = Wrow[k];
-            if (sd) {
-                const float inv = 1.f / fmaxf(eps, sd[k]);
-                w.x *= inv;
-                w.y *= inv;
+        float2* dst = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
+        for (int to0 = 0; to0 < to_n; to0 += kWmmTo) {
+            float2 acc[kWmmTo];
+#pragma unroll
+            for (int i = 0; i < kWmmTo; ++i) acc[i] = make_float2(0.f, 0.f);
+            if (live) {
+                for (int k = kk; k < tff; k += KC) {
+                    float2 z = src[(int64_t)k * n];
+                    if (sd) {
+                        const float inv = 1.f / fmaxf(eps, sd[k]);
+                        z.x *= inv;
+                        z.y *= inv;
+                    }
+#pragma unroll
+                    for (int i = 0; i < kWmmTo; ++i)
+                        if (to0 + i < to_n) cfma(acc[i], Wl[(int64_t)(to0 + i) * tff + k], z);
+                }
             }
-            cfma(acc, w, src[(int64_t)k * n]);
+#pragma unroll
+            for (int i = 0; i < kWmmTo; ++i) {
+                if (to0 + i >= to_n) break;
+                __syncthreads();
+                red[tid] = acc[i];
+                __syncthreads();
+                if (tid < n) {
+                    float2 sum = make_float2(0.f, 0.f);
+                    for (int q = 0; q < KC; ++q) {
+                        const float2 v = red[q * n + tid];
+                        sum.x += v.x;
+                        sum.y += v.y;
+                    }
+                    dst[(int64_t)(to0 + i) * n - mi + tid] = sum;
+                }
+            }
         }
-        O[(int64_t)b * P.n_O + e] = acc;
     }
 }
 
@@ -421,10 +454,14 @@ int cgb200_fn_wmm_fwd(const cgb200_plan* p, const float* FF, const float* W, flo
         launch_end(K_FN_STATS, st);
         CGB_CUDA(cudaGetLastError());
     }
-    const int gx = (int)((p->d.n_O + 255) / 256);
-    const int gy = (int)std::min<int64_t>(B, 65535);
+    {
+        dim3 chk;
+        if ((rc = chunk_grid(p, &chk))) return rc;   // 2 lmax + 1 <= block size
+    }
+    const int gx = (int)std::min<int64_t>(B, 65535);
     launch_begin(K_WMM_FWD, st);
-    wmm_fwd_kernel<<<dim3(gx, gy), 256, 0, st>>>(p->d, (const float2*)FF, (const float2*)W, fn ? stds : nullptr, eps, (float2*)O, (int)B);
+    wmm_fwd_kernel<<<dim3(gx, p->d.lmax + 1), kStatThreads, 0, st>>>(p->d, (const float2*)FF, (const float2*)W, fn ? stds : nullptr, eps,
+                                                                      (float2*)O, (int)B);
     launch_end(K_WMM_FWD, st);
     CGB_CUDA(cudaGetLastError());
     return CGB200_OK;

@@ -198,6 +198,25 @@ int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* plan, int64_t B);
 int cgb200_layer_fwd_static(const cgb200_plan* plan, const float* F, const float* W, float* stds, float cnt, float eps,
                             int flags, float* O, int64_t B, void* stream);
 
+/*
+ * Spherical-harmonic projection of sampled real functions, the step in front of the network:
+ *     coefs[r][c] = scale * sum_p f[r][p] * basis[p][c]        (complex basis and result, real samples)
+ * Replaces the contraction of `get_sph_coefs` (utils/s2_sph.py:79-86, basis = quadrature weight x conj(Y_lm) on the grid,
+ * scale = 4 pi / P) and of `get_coef_C` (utils/geometries.py:125-144, basis = Y_lm at the sample points), which the
+ * reference evaluates with numpy one function at a time; here all `rows` functions go through one tensor-core GEMM
+ * (3xTF32, rounded partial sums).  The basis is packed once per (point set, lmax):
+ *   basis         device float[n_points][n_cols][2]
+ *   packed        device buffer of cgb200_sh_basis_bytes(n_points, n_cols) bytes, 256-byte aligned
+ *   f             device float[rows][n_points]          coefs  device float[rows][n_cols][2], fully written
+ *   workspace     cgb200_sh_workspace_bytes(rows, n_points) bytes, 256-byte aligned, contents undefined
+ *   status_word   device int32, zero on entry; set to 1 if a bounded device-side wait ran out (coefs are then NaN)
+ */
+int64_t cgb200_sh_basis_bytes(int64_t n_points, int n_cols);
+int64_t cgb200_sh_workspace_bytes(int64_t rows, int64_t n_points);
+int cgb200_sh_basis_pack(const float* basis, int64_t n_points, int n_cols, float* packed, void* stream);
+int cgb200_sh_project(const float* f, int64_t rows, int64_t n_points, int n_cols, const float* packed, float scale,
+                      float* coefs, void* workspace, int64_t workspace_bytes, int32_t* status_word, void* stream);
+
 /* Number of kernels this library launched in this process since the last reset (bench accounting). */
 int64_t cgb200_launch_count(int reset);
 
