@@ -41,6 +41,8 @@ SIGNATURES = {
     "cgb200_sh_workspace_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int64]),
     "cgb200_sh_basis_pack": (ctypes.c_int, [vp, ctypes.c_int64, ctypes.c_int, vp, vp]),
     "cgb200_sh_project": (ctypes.c_int, [vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp, ctypes.c_float, vp, vp, ctypes.c_int64, vp, vp]),
+    "cgb200_raycast_workspace_bytes": (ctypes.c_int64, [ctypes.c_int64]),
+    "cgb200_raycast_sphere": (ctypes.c_int, [vp, ctypes.c_int64, vp, ctypes.c_int64, vp, ctypes.c_int64, vp, vp, ctypes.c_int64, vp, vp]),
     "cgb200_launch_count": (ctypes.c_int64, [ctypes.c_int]),
     "cgb200_kernel_count": (ctypes.c_int, []),
     "cgb200_kernel_name": (ctypes.c_char_p, [ctypes.c_int]),

@@ -10,8 +10,11 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu", "sh_project.cu"]
+SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu", "sh_project.cu", "raycast.cu"]
 LIB = os.path.join(HERE, "libcgnet_b200.so")
+# raycast.cu: no fused multiply-add, so that its float64 hit tests round exactly like a host evaluation of the same
+# expressions and rays through shared edges pick the same triangle on both sides
+EXTRA_FLAGS = {"raycast.cu": ["-fmad=false"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-O2"]
 
@@ -43,7 +46,7 @@ def build(force=False, verbose=False):
     procs = []
     for src in SOURCES:
         obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
-        cmd = [_nvcc()] + flags + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [_nvcc()] + flags + EXTRA_FLAGS.get(src, []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     objs = []
     for src, obj, p in procs:

@@ -144,7 +144,7 @@ int cuda_fail(cudaError_t e, const char* what);
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
     K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_GF_TC, K_SH_PACK, K_SH_PROJECT,
-    K_COUNT
+    K_RAY_PACK, K_RAY_CAST, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.

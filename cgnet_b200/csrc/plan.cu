@@ -31,7 +31,7 @@ static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_pr
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
                                             "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor", "fused_grad_f_tensor",
-                                            "sh_pack", "sh_project_tensor"};
+                                            "sh_pack", "sh_project_tensor", "raycast_pack", "raycast_sphere"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;

@@ -217,6 +217,21 @@ int cgb200_sh_basis_pack(const float* basis, int64_t n_points, int n_cols, float
 int cgb200_sh_project(const float* f, int64_t rows, int64_t n_points, int n_cols, const float* packed, float scale,
                       float* coefs, void* workspace, int64_t workspace_bytes, int32_t* status_word, void* stream);
 
+/*
+ * Mesh -> sphere projection by ray casting (the SHREC17 front end).  One ray per grid point g, from g towards the origin;
+ * the first triangle it meets gives image[0][p] = distance from g to the hit (1 without a hit), image[1][p] = n . g and
+ * image[2][p] = |n ^ g| (0 without a hit), n the triangle's unit normal from its winding, g normalised.
+ * Replaces `render_model` (Shrec17/dataset.py:53-95), which takes the intersections from the trimesh package.
+ *   vertices   device float[n_vertices][3]     faces  device int32[n_faces][3] (an index outside the vertices drops the face)
+ *   sgrid      device float[n_points][3]       image  device float[3][n_points], fully written
+ *   workspace  cgb200_raycast_workspace_bytes(n_faces) bytes, 256-byte aligned
+ *   status_word  device int32, zero on entry; set to 1 if a bounded device-side wait ran out (those pixels are NaN)
+ */
+int64_t cgb200_raycast_workspace_bytes(int64_t n_faces);
+int cgb200_raycast_sphere(const float* vertices, int64_t n_vertices, const int32_t* faces, int64_t n_faces, const float* sgrid,
+                          int64_t n_points, float* image, void* workspace, int64_t workspace_bytes, int32_t* status_word,
+                          void* stream);
+
 /* Number of kernels this library launched in this process since the last reset (bench accounting). */
 int64_t cgb200_launch_count(int reset);
 
