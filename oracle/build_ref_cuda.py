@@ -30,7 +30,8 @@ def build(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CGNET_REFERENCE"), required=os.environ.get("CGNET_REFERENCE") is None,
+                    help="path of a zlin7/CGNet checkout (or set CGNET_REFERENCE)")
     args = ap.parse_args()
     mod = build(args.ref)
     print("built", mod.__file__, "sparse_maxL =", mod.sparse_maxL())

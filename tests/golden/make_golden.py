@@ -242,7 +242,8 @@ def layer_fixtures(cgu, cgpy):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CGNET_REFERENCE"), required=os.environ.get("CGNET_REFERENCE") is None,
+                    help="path of a zlin7/CGNet checkout (or set CGNET_REFERENCE)")
     args = ap.parse_args()
     cgu, cgpy = import_reference(args.ref)
     n1 = index_fixtures(cgu)

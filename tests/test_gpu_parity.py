@@ -21,7 +21,7 @@ SHAPES = [
     ([1], [3], 5, "default"),                          # lmax = 0
     ([5] * 4, [5] * 4, 37, "default"),                 # batch not a multiple of the warp size
     ([1] * 6, [5] * 6, 33, "default"),                 # single input channel per degree (first layer of the MNIST net)
-    ([8] * 6, [8] * 6, 32, "default"),                 # BASELINE config 1 shape
+    ([8] * 6, [8] * 6, 32, "default"),                 # the reference's CPU-runnable case: lmax 5, 8 channels, batch 32
     ([6, 0, 3, 2], [2, 2, 0, 3], 4, "default"),        # empty fragments on both sides
     ([7, 6, 5], [20, 3, 17], 3, "default"),            # more than 16 output channels, ragged tiles
     ([2] * 21, [2] * 21, 5, "mst"),                    # lmax = 20: fragments of 41 rows
