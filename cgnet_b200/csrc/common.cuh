@@ -245,6 +245,8 @@ struct cgb200_plan {
     std::vector<int> gf2_parts[kGfLevels];            // [lmax+1] parts per fragment
     const int* d_gf2_parts[kGfLevels] = {nullptr};
     int gf2_max_parts[kGfLevels] = {0};
+    double gf2_longest[kGfLevels] = {0};             // modelled cost of the longest block of a level (units below)
+    double gf_total_cost = 0;                         // modelled cost of all blocks of one sample group
     // tensor-core forward (tile edge 2 or 4, full product): per degree the padded GEMM width N' = 2*tau_out rounded
     // up to 16, the offset (in floats) of the degree's packed weights, and the list of row tiles (l, first m index)
     bool tc_ok = false;

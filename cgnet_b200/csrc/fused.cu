@@ -810,10 +810,19 @@ int gw_slices(const cgb200_plan* p, int64_t G) {
 // two channel groups (CGB200_OPT_GRAD_F_SPLIT).  The plan holds a warp assignment for both.
 bool gf_split(const cgb200_plan* p) { return p->opt[CGB200_OPT_GRAD_F_SPLIT] == 1; }
 
-// Splitting level of the input-gradient kernel: the coarsest one that gives every SM about two blocks.
+// Splitting level of the input-gradient kernel.  One block owns an SM (221 KB of shared memory) and the blocks differ
+// widely in length, so with few blocks per SM the longest ones set the kernel's duration (measured with clock64 at lmax
+// 14 with 16 channels and two blocks per SM: the SMs were busy with blocks 65 % of the time), while a block also has a
+// fixed cost (accumulator set-up, write-out, one more partial sum to add) that makes very short blocks a loss (the
+// 5-channel benchmark layer got 7 % slower one level further down).  The plan models a block's cost as its complex
+// multiply-adds per lane - measured at three shapes: about 1050 units per microsecond - and the launch takes the coarsest
+// level whose longest block is under a tenth of the ideal per-SM time, or under about 80 us.  Against the former
+// "two blocks per SM": backward of the lmax-14 16-channel layer 8.5 -> 6.4 ms, lmax 10 with 32 channels 12.5 -> 10.0 ms.
 int gf_level(const cgb200_plan* p, int64_t G) {
+    const double ideal = p->gf_total_cost * (double)G / std::max(p->num_sms, 1);
+    const double limit = std::max(0.1 * ideal, 85000.0);
     for (int lv = 0; lv < cgb200_plan::kGfLevels; ++lv)
-        if ((int64_t)(p->gf2_blocks[lv].size() / 4) * G >= 2 * (int64_t)p->num_sms) return lv;
+        if (p->gf2_longest[lv] <= limit) return lv;
     return cgb200_plan::kGfLevels - 1;
 }
 

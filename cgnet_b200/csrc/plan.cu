@@ -659,7 +659,9 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
                 parts = std::max(1, std::min(parts, std::max(n_entries, 1)));
                 p->gf2_parts[lv][l] = parts;
                 p->gf2_max_parts[lv] = std::max(p->gf2_max_parts[lv], parts);
+                p->gf2_longest[lv] = std::max(p->gf2_longest[lv], cost[l] / parts);
                 const int ntile = (p->tF[l] + T - 1) / T;
+                if (lv == 0) p->gf_total_cost += cost[l] * ntile;
                 for (int q = 0; q < ntile; ++q)
                     for (int part = 0; part < parts; ++part) {
                         p->gf2_blocks[lv].push_back(l);
