@@ -144,7 +144,7 @@ int cuda_fail(cudaError_t e, const char* what);
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
     K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_GF_TC, K_SH_PACK, K_SH_PROJECT,
-    K_RAY_PACK, K_RAY_CAST, K_COUNT
+    K_RAY_PACK, K_RAY_CAST, K_FWD_REDUCE, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.
@@ -200,8 +200,11 @@ int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const
                  int max_slices, int G, cudaStream_t st);
 void launch_gw_reduce(const cgb200_plan* p, const float2* partial, int slices, float2* gW, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
-int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
-                  cudaStream_t st);
+int tc_fwd_level(const cgb200_plan* p, int64_t G);
+int launch_fwd_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
+                  float2* O_part, int B, int G, cudaStream_t st);
+void launch_parts_reduce(int kid, const int64_t* cum, int n_deg, int64_t n_total, const int* parts, const float2* partial,
+                         int64_t part_stride, float2* out, int B, bool skip_single, cudaStream_t st);
 }  // namespace cgb200
 
 // The opaque handle of the C ABI.
@@ -253,10 +256,20 @@ struct cgb200_plan {
     bool tc_gw_ok = false;            // the tensor-core weight gradient's tables exist (tile edge 4 or 5)
     std::vector<int> tc_npad;
     std::vector<int64_t> tc_pack_off;   // [lmax+2]
-    std::vector<int> tc_tiles;          // (l, m0) pairs, longest K first
+    // Row tiles of the tensor-core forward, per splitting level: (l, first m index, part, parts) with the longest
+    // contraction first.  At level v the degree with the most cells is cut into 2^v parts of its cells and every other
+    // degree into as many parts as keep its parts no longer than that; a part writes a partial output that
+    // parts_reduce_kernel adds up in part order.
+    static constexpr int kTcLevels = 7;
+    std::vector<int> tc_tiles[kTcLevels];
+    const int* d_tc_tiles[kTcLevels] = {nullptr};
+    std::vector<int> tc_parts[kTcLevels];           // [lmax+1] parts per degree
+    const int* d_tc_parts[kTcLevels] = {nullptr};
+    int tc_max_parts[kTcLevels] = {0};
+    int tc_longest[kTcLevels] = {0};                // cells of the longest part
+    int64_t tc_total_cells = 0;                     // cells summed over the row tiles of one sample group
     const int* d_tc_npad = nullptr;
     const int64_t* d_tc_pack_off = nullptr;
-    const int* d_tc_tiles = nullptr;
     std::vector<int> tc_gw_tiles;       // tensor-core weight gradient: (l, first cell of a block of four) pairs, longest first
     const int* d_tc_gw_tiles = nullptr;
     // CG table with every band row padded to a multiple of four floats (16-byte aligned rows: the four band rows a row

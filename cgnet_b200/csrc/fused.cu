@@ -756,23 +756,35 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     }
 }
 
-// gF[b][e] = sum over the parts of e's fragment, in part order
+// out[b][e] = sum over the parts of e's fragment, in part order (partial: [part][B][n_total]).  With skip_single the
+// fragments that were not split are left alone: their only part was written to `out` directly.
 __global__ void __launch_bounds__(256)
-gf_reduce_kernel(PlanDev P, const int* __restrict__ parts, const float2* __restrict__ partial, int64_t part_stride,
-                 float2* __restrict__ gF, int B) {
+parts_reduce_kernel(const int64_t* __restrict__ cum, int n_deg, int64_t n_total, const int* __restrict__ parts,
+                    const float2* __restrict__ partial, int64_t part_stride, float2* __restrict__ out, int B, int skip_single) {
     const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= P.n_F) return;
-    const int np = parts[find_degree(P.cumF, P.lmax + 1, e)];
+    if (e >= n_total) return;
+    const int np = parts[find_degree(cum, n_deg, e)];
+    if (skip_single && np <= 1) return;
     for (int b = blockIdx.y; b < B; b += gridDim.y) {
-        const float2* src = partial + (int64_t)b * P.n_F + e;
+        const float2* src = partial + (int64_t)b * n_total + e;
         float2 s = src[0];
         for (int k = 1; k < np; ++k) {
             const float2 v = src[(int64_t)k * part_stride];
             s.x += v.x;
             s.y += v.y;
         }
-        gF[(int64_t)b * P.n_F + e] = s;
+        out[(int64_t)b * n_total + e] = s;
     }
+}
+
+void launch_parts_reduce(int kid, const int64_t* cum, int n_deg, int64_t n_total, const int* parts, const float2* partial,
+                         int64_t part_stride, float2* out, int B, bool skip_single, cudaStream_t st) {
+    if (n_total <= 0 || B <= 0) return;
+    const unsigned gx = (unsigned)((n_total + 255) / 256);
+    launch_begin(kid, st);
+    parts_reduce_kernel<<<dim3(gx, (unsigned)std::min<int64_t>(B, 65535)), 256, 0, st>>>(cum, n_deg, n_total, parts, partial, part_stride,
+                                                                                       out, B, skip_single ? 1 : 0);
+    launch_end(kid, st);
 }
 
 }  // namespace cgb200
@@ -789,6 +801,8 @@ struct Workspace {
     float2* gf_part; // partial input gradients, [parts][B][n_F], when the input-gradient blocks are split
     int gf_level;
     float* tc_pack;  // packed TF32 weights of the tensor-core forward
+    float2* fwd_part; // partial outputs, [parts][B][n_O], when the tensor-core forward splits its contraction
+    int fwd_level;
     float2* gw_part; // partial weight gradients, [slices][w_len], when the sample groups are split over warps
     int gw_slices;
     int64_t bytes;
@@ -851,6 +865,10 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
         off += align256((int64_t)p->gf2_max_parts[w.gf_level] * B * std::max<int64_t>(p->d.n_F, 1) * (int64_t)sizeof(float2));
     w.tc_pack = (float*)(c + off);
     if (tc_wanted(p)) off += align256(tc_pack_floats(p) * (int64_t)sizeof(float));
+    w.fwd_level = tc_wanted(p) ? tc_fwd_level(p, G) : 0;
+    w.fwd_part = (float2*)(c + off);
+    if (tc_wanted(p) && p->tc_max_parts[w.fwd_level] > 1)
+        off += align256((int64_t)p->tc_max_parts[w.fwd_level] * B * std::max<int64_t>(p->d.n_O, 1) * (int64_t)sizeof(float2));
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
     if (!fwd_only && w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
@@ -966,7 +984,8 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     }
     const int n_rows = (int)p->fwd_rows.size() / 2;
     if (n_rows == 0) return CGB200_OK;
-    if (tc_wanted(p)) return launch_fwd_tc(p, ws.SF, (const float2*)W, ws.inv, ws.tc_pack, (float2*)O, (int)B, G, st);
+    if (tc_wanted(p))
+        return launch_fwd_tc(p, ws.fwd_level, ws.SF, (const float2*)W, ws.inv, ws.tc_pack, (float2*)O, ws.fwd_part, (int)B, G, st);
     // persistent shared-memory variant when one group's slab (plus reduction buffer and staging areas) fits in an SM
     const int NVh = p->d.depthwise ? T : T * T;
     // output channels per pass: the smallest instantiated width that covers the widest degree (at most kFwdTo)
@@ -1113,10 +1132,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             CGB_CUDA(cudaGetLastError());
         }
         if (split) {
-            const int gx = (int)((p->d.n_F + 255) / 256);
-            launch_begin(K_GF_REDUCE, st);
-            gf_reduce_kernel<<<dim3(gx, (unsigned)std::min<int64_t>(B, 65535)), 256, 0, st>>>(p->d, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF, (int)B);
-            launch_end(K_GF_REDUCE, st);
+            launch_parts_reduce(K_GF_REDUCE, p->d.cumF, p->d.lmax + 1, p->d.n_F, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF,
+                                (int)B, false, st);
             CGB_CUDA(cudaGetLastError());
         }
         return CGB200_OK;

@@ -86,7 +86,8 @@ tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restric
 template <int T>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
-                    const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O, int B, int n_max,
+                    const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O,
+                    float2* __restrict__ O_part, int64_t part_stride, int B, int n_max,
                     int max_n, int* __restrict__ status, int n_stages, int n_flush, uint32_t wait_limit, int idle_mma) {
     constexpr int Kc = 2 * T * T;            // real K extent of one cell
     constexpr int NV = T * T;
@@ -97,13 +98,18 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
-    const int l = tiles[2 * blockIdx.x], m0 = tiles[2 * blockIdx.x + 1];
+    const int l = tiles[4 * blockIdx.x], m0 = tiles[4 * blockIdx.x + 1];
+    const int part = tiles[4 * blockIdx.x + 2], parts = tiles[4 * blockIdx.x + 3];
     // group-major block order (all tiles of group 0, then group 1, ...): consecutive blocks on an SM read the same group's
     // slab, which the generators fetch through L1; tile-major order measured 30-60 % slower
     const int g = blockIdx.y;
     const int n = 2 * l + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
+    // this block's share of the degree's cells: k0 .. k0 + ncell - 1 (all of them unless the contraction is split)
+    const int ncell_deg = P.cell_begin[l + 1] - P.cell_begin[l];
+    const int k0 = (int)((int64_t)ncell_deg * part / parts);
+    const int ncell = (int)((int64_t)ncell_deg * (part + 1) / parts) - k0;
+    const int c_begin = P.cell_begin[l] + k0;
     const int N = npad[l];
     const int to_n = P.tO[l];
     const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
@@ -150,7 +156,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
             if (!ok) break;
             if (wq == 0 && lane == 0) {
                 mbar_expect_tx(&full_bar[s], b_bytes);
-                bulk_g2s(b_st, pack + pack_off[l] + (int64_t)k * 2 * N * Kc, b_bytes, &full_bar[s]);
+                bulk_g2s(b_st, pack + pack_off[l] + (int64_t)(k0 + k) * 2 * N * Kc, b_bytes, &full_bar[s]);
             }
             float2 v[NV];
             if (live_m) {
@@ -244,7 +250,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
         }
         const int b = g * 32 + lane;
         if (live_m && b < B) {
-            float2* out = O + (int64_t)b * P.n_O + P.cumO[l] + mi;
+            float2* out = (parts > 1 ? O_part + (int64_t)part * part_stride : O) + (int64_t)b * P.n_O + P.cumO[l] + mi;
             const float nanv = __uint_as_float(kNaNBits);   // a block that gave up marks the outputs it owns
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
@@ -305,7 +311,7 @@ fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* 
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed_flag;
 
-    const int l = tiles[2 * blockIdx.x], m0 = tiles[2 * blockIdx.x + 1];
+    const int l = tiles[4 * blockIdx.x], m0 = tiles[4 * blockIdx.x + 1];   // level 0 of the tile lists: whole contractions
     const int g = blockIdx.y;
     const int n = 2 * l + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1106,14 +1112,34 @@ bool tc_wanted(const cgb200_plan* p) {
 
 int64_t tc_pack_floats(const cgb200_plan* p) { return p->tc_ok ? p->tc_pack_off.back() : 0; }
 
+// Splitting level of the tensor-core forward's contraction.  A block owns an SM (its pipeline stages fill the shared
+// memory) and lasts in proportion to its cells, about 0.85 us each, so with few sample groups the degree with the most
+// cells sets the kernel's duration: at lmax 14 with 16 channels and 64 samples there are 128 blocks for 148 SMs and the
+// longest has 1024 of the 92 k cells.  The launch takes the coarsest level whose longest part is under a tenth of an
+// SM's share of the cells (measured over lmax 10, 14, 20 with 16 to 64 channels and 32 to 256 samples: within 2 % of the
+// best level everywhere; against no splitting 2.0x at lmax 10 with 64 channels and 64 samples, 1.2x at lmax 14 with 16
+// channels and 64 samples, 1.07x at 256 samples), as long as the partial outputs stay under 256 MB.  The staged variant
+// does not split.
+int tc_fwd_level(const cgb200_plan* p, int64_t G) {
+    if (!p->tc_ok) return 0;
+    if (p->opt[CGB200_OPT_TC_STAGED] >= 1) return 0;
+    if (p->opt[CGB200_OPT_TC_FWD_SPLIT] != CGB200_AUTO) return p->opt[CGB200_OPT_TC_FWD_SPLIT];
+    const double share = (double)p->tc_total_cells * (double)G / std::max(p->num_sms, 1);
+    const double out_bytes = (double)G * 32 * (double)p->d.n_O * sizeof(float2);
+    int lv = 0;
+    while (lv + 1 < cgb200_plan::kTcLevels && p->tc_longest[lv] > 0.1 * share &&
+           p->tc_max_parts[lv + 1] * out_bytes <= 256.0 * (1 << 20))
+        ++lv;
+    return lv;
+}
+
 template <int T>
-static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B,
-                     int G, cudaStream_t st) {
+static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
+                     float2* O_part, int B, int G, cudaStream_t st) {
     constexpr int Kc = 2 * T * T;
     int n_max = 16;
     for (int v : p->tc_npad) n_max = std::max(n_max, v);
-    const int n_tiles = (int)p->tc_tiles.size() / 2;
-    if (n_tiles == 0) return CGB200_OK;
+    if (p->tc_tiles[0].empty()) return CGB200_OK;
     launch_begin(K_TC_PACK, st);
     if (p->d.n_cells > 0)
         tc_pack_kernel<T><<<p->d.n_cells, 256, 0, st>>>(p->d, p->d_tc_npad, p->d_tc_pack_off, W, inv, pack);
@@ -1161,7 +1187,7 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
             auto kern = fused_fwd_tc_staged_kernel<T>;
             CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             launch_begin(K_FWD_TC, st);
-            kern<<<dim3(n_tiles, G), 32 * (4 * S + 2 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, p->d_cg_pad,
+            kern<<<dim3((unsigned)p->tc_tiles[0].size() / 4, G), 32 * (4 * S + 2 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles[0], p->d_tc_npad, p->d_tc_pack_off, p->d_cg_pad,
                                                                             p->d_cell_cgpad, SF, pack, O, B, p->d_status, S, NA, n_flush, (int)ring,
                                                                             stage_rows ? 1 : 0, wait_polls(p), idle);
             launch_end(K_FWD_TC, st);
@@ -1182,17 +1208,23 @@ static int launch_tc(const cgb200_plan* p, const float2* SF, const float2* W, co
     auto kern = fused_fwd_tc_kernel<T>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
-    kern<<<dim3(n_tiles, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_tiles, p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, B,
-                                                                  n_max, p->max_n, p->d_status, n_stages, n_flush, wait_polls(p), idle);
+    const int64_t part_stride = (int64_t)B * p->d.n_O;
+    kern<<<dim3((unsigned)p->tc_tiles[lv].size() / 4, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(
+        p->d, p->d_tc_tiles[lv], p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, O_part, part_stride, B, n_max, p->max_n, p->d_status,
+        n_stages, n_flush, wait_polls(p), idle);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
+    if (p->tc_max_parts[lv] > 1) {
+        launch_parts_reduce(K_FWD_REDUCE, p->d.cumO, p->d.lmax + 1, p->d.n_O, p->d_tc_parts[lv], O_part, part_stride, O, B, true, st);
+        CGB_CUDA(cudaGetLastError());
+    }
     return CGB200_OK;
 }
 
-int launch_fwd_tc(const cgb200_plan* p, const float2* SF, const float2* W, const float* inv, float* pack, float2* O, int B, int G,
-                  cudaStream_t st) {
-    if (p->d.tile == 4) return launch_tc<4>(p, SF, W, inv, pack, O, B, G, st);
-    if (p->d.tile == 2) return launch_tc<2>(p, SF, W, inv, pack, O, B, G, st);
+int launch_fwd_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
+                  float2* O_part, int B, int G, cudaStream_t st) {
+    if (p->d.tile == 4) return launch_tc<4>(p, lv, SF, W, inv, pack, O, O_part, B, G, st);
+    if (p->d.tile == 2) return launch_tc<2>(p, lv, SF, W, inv, pack, O, O_part, B, G, st);
     set_error("internal: tensor-core forward asked for an unsupported tile edge");
     return CGB200_ERR_UNSUPPORTED;
 }

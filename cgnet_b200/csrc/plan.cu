@@ -31,7 +31,7 @@ static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_pr
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
                                             "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor", "fused_grad_f_tensor",
-                                            "sh_pack", "sh_project_tensor", "raycast_pack", "raycast_sphere"};
+                                            "sh_pack", "sh_project_tensor", "raycast_pack", "raycast_sphere", "fused_fwd_tensor_reduce"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;
@@ -444,14 +444,36 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             p->tc_pack_off[l + 1] = p->tc_pack_off[l] + ncell * 2 * p->tc_npad[l] * Kc;
             if (p->tO[l] > 0) order.push_back({(int)ncell, l});
         }
-        std::stable_sort(order.begin(), order.end(), [](const std::pair<int, int>& a, const std::pair<int, int>& b) { return a.first > b.first; });
-        for (auto& o : order)
-            for (int m0 = 0; m0 < 2 * o.second + 1; m0 += 4) {
-                p->tc_tiles.push_back(o.second);
-                p->tc_tiles.push_back(m0);
-            }
+        int ncell_max = 0;
+        for (auto& o : order) {
+            ncell_max = std::max(ncell_max, o.first);
+            p->tc_total_cells += (int64_t)o.first * ((2 * o.second + 1 + 3) / 4);
+        }
         if ((rc = upload(p, p->tc_pack_off, &p->d_tc_pack_off))) return rc;
-        if ((rc = upload(p, p->tc_tiles, &p->d_tc_tiles))) return rc;
+        constexpr int kMinPartCells = 24;   // a part pays for its set-up (tensor memory, barriers, pipeline fill) and one partial output
+        for (int lv = 0; lv < cgb200_plan::kTcLevels; ++lv) {
+            const int target = std::max((ncell_max + (1 << lv) - 1) >> lv, std::min(kMinPartCells, std::max(ncell_max, 1)));
+            p->tc_parts[lv].assign(L1, 1);
+            std::vector<std::pair<int, int>> by_len;   // (cells of the longest part, l)
+            for (auto& o : order) {
+                const int parts = std::max(1, (o.first + target - 1) / target);
+                p->tc_parts[lv][o.second] = parts;
+                p->tc_max_parts[lv] = std::max(p->tc_max_parts[lv], parts);
+                by_len.push_back({(o.first + parts - 1) / parts, o.second});
+                p->tc_longest[lv] = std::max(p->tc_longest[lv], by_len.back().first);
+            }
+            std::stable_sort(by_len.begin(), by_len.end(), [](const std::pair<int, int>& a, const std::pair<int, int>& b) { return a.first > b.first; });
+            for (auto& o : by_len)
+                for (int part = 0; part < p->tc_parts[lv][o.second]; ++part)
+                    for (int m0 = 0; m0 < 2 * o.second + 1; m0 += 4) {
+                        p->tc_tiles[lv].push_back(o.second);
+                        p->tc_tiles[lv].push_back(m0);
+                        p->tc_tiles[lv].push_back(part);
+                        p->tc_tiles[lv].push_back(p->tc_parts[lv][o.second]);
+                    }
+            if ((rc = upload(p, p->tc_tiles[lv], &p->d_tc_tiles[lv]))) return rc;
+            if ((rc = upload(p, p->tc_parts[lv], &p->d_tc_parts[lv]))) return rc;
+        }
     }
     if (p->tc_gw_ok) {   // weight gradient: blocks of 128 / (2 T^2) cells, degrees with the longest contraction (2l+1) first
         const int per_block = 128 / (2 * T * T);
@@ -744,6 +766,9 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
             case CGB200_OPT_TC_STAGES: CGB_REQUIRE(value >= 2, "CGB200_OPT_TC_STAGES must be at least 2"); break;
             case CGB200_OPT_TC_ABUF: CGB_REQUIRE(value >= 2, "CGB200_OPT_TC_ABUF must be at least 2"); break;
             case CGB200_OPT_TC_STAGED: CGB_REQUIRE(value >= 0 && value <= 2, "CGB200_OPT_TC_STAGED must be CGB200_AUTO, 0, 1 or 2"); break;
+            case CGB200_OPT_TC_FWD_SPLIT:
+                CGB_REQUIRE(value >= 0 && value < cgb200_plan::kTcLevels, "CGB200_OPT_TC_FWD_SPLIT must be CGB200_AUTO or 0..6");
+                break;
             case CGB200_OPT_WAIT_POLLS: CGB_REQUIRE(value >= 1, "CGB200_OPT_WAIT_POLLS must be positive"); break;
             default: CGB_REQUIRE(value == 0 || value == 1, "option value must be CGB200_AUTO, 0 or 1"); break;
         }

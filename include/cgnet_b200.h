@@ -111,7 +111,10 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
                                            band rows, operand rows and packed weights into a shared-memory ring ahead of the
                                            generators, 2 = band rows and weights only                                       */
 #define CGB200_OPT_TC_ABUF          11  /* staged tensor-core forward: upper limit of the A-tile buffers (>= 2)                */
-#define CGB200_OPT_COUNT            12
+#define CGB200_OPT_TC_FWD_SPLIT     12  /* tensor-core forward: splitting level 0..6 of the contraction (the degree with the
+                                           most cells in 2^level parts, partial outputs added in part order); default: by
+                                           the batch size, so that the longest block stays a fraction of an SM's share      */
+#define CGB200_OPT_COUNT            13
 int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
 int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
 

@@ -223,7 +223,32 @@ def test_staged_tensor_core_forward_equals_unstaged(taus, tau_out, B, mode, stag
     case = make_case(taus, tau_out, B, mode, seed=59)
     plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
     assert plan.tile == 4
-    want, _ = _forward(plan, case, True, False, tc=True)
+    with option(plan, _lib.OPT_TC_FWD_SPLIT, 0):   # the staged kernel never splits the contraction
+        want, _ = _forward(plan, case, True, False, tc=True)
     with option(plan, _lib.OPT_TC_STAGED, staged):
         got, _ = _forward(plan, case, True, False, tc=True)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
+                                                 ([8] * 11, [32] * 11, 20, "default"), ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default"),
+                                                 ([2] * 5, [8] * 5, 3, "default")])
+def test_split_contraction_of_tensor_core_forward(taus, tau_out, B, mode):
+    """Every splitting level of the tensor-core forward (the degree with the most cells cut into 1, 2, 4, ... 64 parts of
+    its cells, partial outputs added in part order) against the oracle; the level the launch would pick by itself is one
+    of them, and each level is deterministic."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, mode, seed=60)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
+    assert plan.tile in (2, 4)
+    O_want, _, _, _ = oracle_layer(case, True, False, cnt=2.0)
+    auto, _ = _forward(plan, case, True, False, tc=True)
+    hits = 0
+    for level in range(7):
+        with option(plan, _lib.OPT_TC_FWD_SPLIT, level):
+            got, _ = _forward(plan, case, True, False, tc=True)
+            again, _ = _forward(plan, case, True, False, tc=True)
+        assert np.array_equal(got, again), f"level {level} is not deterministic"
+        assert_fragments_close(got, O_want, tau_out, f"O (tensor-core forward, splitting level {level}) vs oracle")
+        hits += int(np.array_equal(got, auto))
+    assert hits >= 1
