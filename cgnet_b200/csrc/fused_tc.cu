@@ -8,8 +8,11 @@
 //
 // The complex product is run as a real GEMM of doubled dimensions: a row of A holds (re, im) of every mid channel, the
 // columns of B hold, for output (to, re): (Wr, -Wi) and for (to, im): (Wi, Wr).  3xTF32: A = Ah + Al, B = Bh + Bl with
-// Ah, Bh rounded to TF32; D += Ah*Bh + Al*Bh + Ah*Bl, accumulated in fp32 by the tensor core (the dropped Al*Bl term
-// is ~2^-22 relative).
+// Ah, Bh rounded to TF32; D = Ah*Bh + Al*Bh + Ah*Bl, accumulated in fp32 by the tensor core (the dropped Al*Bl term
+// is ~2^-22 relative).  The packed weights hold Bl directly behind Bh, which makes [Bh | Bl] one K-major matrix of 2 N
+// rows: one MMA of width 2 N computes Ah*Bh into accumulator columns 0 .. N and Ah*Bl into N .. 2 N, a second of width N
+// adds Al*Bh - two instructions per K step instead of three (an MMA costs about 65 cycles to issue whatever its width,
+// and each one re-reads its A tile from shared memory); the two column halves are added when the accumulator is read.
 //
 // Block = one row tile: degree l, four consecutive m, one group of 32 samples (row r = 32*(m - m0) + sample, the same
 // one-sample-per-lane scheme as the other fused kernels, so the generator is gen_slab unchanged).  Warps:
@@ -112,7 +115,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     const int c_begin = P.cell_begin[l] + k0;
     const int N = npad[l];
     const int to_n = P.tO[l];
-    const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
+    const uint32_t tmem_cols = 4 * N <= 64 ? 64u : 4 * N <= 128 ? 128u : 4 * N <= 256 ? 256u : 512u;   // two regions of 2 N columns
     const size_t stage_floats = (size_t)2 * 128 * Kc + (size_t)2 * n_max * Kc;
     float* stages = reinterpret_cast<float*>(smem_raw);
     float* cbuf = stages + n_stages * stage_floats + (size_t)warp * max_n;
@@ -185,7 +188,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
     } else if (warp == gen_warps) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && !idle_mma) {
-            const uint32_t idesc = tc_idesc(128, N);
+            const uint32_t idesc = tc_idesc(128, N), idesc_wide = tc_idesc(128, 2 * N);
             bool ok = true;
             for (int k = 0; k < ncell && ok; ++k) {
                 const int s = k % n_stages, u = k / n_stages;
@@ -197,20 +200,18 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
                 ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(r * N);
+                const uint32_t d = tmem_base + (uint32_t)(r * 2 * N);
                 const uint32_t a_hi = smem_u32(stages + s * stage_floats);
                 const uint32_t a_lo = a_hi + 128 * Kc * 4;
-                const uint32_t b_hi = a_lo + 128 * Kc * 4;
-                const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
+                const uint32_t b_hi = a_lo + 128 * Kc * 4;   // high part; the low part follows as rows N .. 2 N - 1 of the same K-major matrix
                 const uint64_t dah0 = smem_desc(a_hi, 128, kSbo), dal0 = smem_desc(a_lo, 128, kSbo);
-                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo), dbl0 = smem_desc(b_lo, 128, kSbo);
+                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo);
 #pragma unroll
                 for (int ks = 0; ks < Kc / 8; ++ks) {
                     const uint64_t dah = desc_advance(dah0, ks * 256), dal = desc_advance(dal0, ks * 256);
-                    const uint64_t dbh = desc_advance(dbh0, ks * 256), dbl = desc_advance(dbl0, ks * 256);
-                    tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
-                    tc_mma_tf32(d, dal, dbh, idesc, 1u);
-                    tc_mma_tf32(d, dah, dbl, idesc, 1u);
+                    const uint64_t dbh = desc_advance(dbh0, ks * 256);
+                    tc_mma_tf32(d, dah, dbh, idesc_wide, (!first || ks > 0) ? 1u : 0u);   // Ah x [Bh | Bl] -> columns 0 .. 2 N
+                    tc_mma_tf32(d, dal, dbh, idesc, 1u);                                   // Al x Bh       -> columns 0 .. N
                 }
                 tc_commit(&empty_bar[s]);   // arrives when the MMAs above have finished reading the stage
                 if (k - j * kChunkCells == kChunkCells - 1 || k == ncell - 1) tc_commit(&chunk_full[r]);   // chunk j is summed
@@ -238,10 +239,11 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
             for (int c4 = 0; c4 < 4; ++c4) {
                 const int col0 = col_base + 16 * c4;
                 if (col0 < N) {   // warp-uniform
-                    uint32_t rr[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * N + col0), rr);
+                    uint32_t rr[16], rl[16];   // the chunk's Ah Bh + Al Bh and its Ah Bl
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * 2 * N + col0), rr);
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * 2 * N + N + col0), rl);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]);
+                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]) + __uint_as_float(rl[i]);
                 }
             }
             tc_fence_before();
@@ -318,7 +320,7 @@ fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* 
     const int c_begin = P.cell_begin[l], ncell = P.cell_begin[l + 1] - c_begin;
     const int N = npad[l];
     const int to_n = P.tO[l];
-    const uint32_t tmem_cols = 2 * N <= 32 ? 32u : 2 * N <= 64 ? 64u : 2 * N <= 128 ? 128u : 256u;   // two regions of N columns
+    const uint32_t tmem_cols = 4 * N <= 64 ? 64u : 4 * N <= 128 ? 128u : 4 * N <= 256 ? 256u : 512u;   // two regions of 2 N columns
     constexpr size_t stage_floats = (size_t)2 * 128 * Kc;   // A tile, high and low part
     float* stages = reinterpret_cast<float*>(smem_raw);
     unsigned char* ring = smem_raw + (size_t)n_abuf * stage_floats * sizeof(float);
@@ -397,7 +399,7 @@ fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* 
     } else if (warp == gen_warps) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && !idle_mma) {
-            const uint32_t idesc = tc_idesc(128, N);
+            const uint32_t idesc = tc_idesc(128, N), idesc_wide = tc_idesc(128, 2 * N);
             bool ok = true;
             for (int k = 0; k < ncell && ok; ++k) {
                 const int s = k % n_abuf, u = k / n_abuf;   // A buffer of the cell and its use count
@@ -412,20 +414,18 @@ fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* 
                 ok = mbar_wait(&full_bar[s], (uint32_t)(u & 1), failed, wait_limit);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(r * N);
+                const uint32_t d = tmem_base + (uint32_t)(r * 2 * N);
                 const uint32_t a_hi = smem_u32(stages + s * stage_floats);
                 const uint32_t a_lo = a_hi + 128 * Kc * 4;
-                const uint32_t b_hi = wgt;
-                const uint32_t b_lo = b_hi + (uint32_t)N * Kc * 4;
+                const uint32_t b_hi = wgt;   // high part; the low part follows as rows N .. 2 N - 1 of the same K-major matrix
                 const uint64_t dah0 = smem_desc(a_hi, 128, kSbo), dal0 = smem_desc(a_lo, 128, kSbo);
-                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo), dbl0 = smem_desc(b_lo, 128, kSbo);
+                const uint64_t dbh0 = smem_desc(b_hi, 128, kSbo);
 #pragma unroll
                 for (int ks = 0; ks < Kc / 8; ++ks) {
                     const uint64_t dah = desc_advance(dah0, ks * 256), dal = desc_advance(dal0, ks * 256);
-                    const uint64_t dbh = desc_advance(dbh0, ks * 256), dbl = desc_advance(dbl0, ks * 256);
-                    tc_mma_tf32(d, dah, dbh, idesc, (!first || ks > 0) ? 1u : 0u);
-                    tc_mma_tf32(d, dal, dbh, idesc, 1u);
-                    tc_mma_tf32(d, dah, dbl, idesc, 1u);
+                    const uint64_t dbh = desc_advance(dbh0, ks * 256);
+                    tc_mma_tf32(d, dah, dbh, idesc_wide, (!first || ks > 0) ? 1u : 0u);   // Ah x [Bh | Bl] -> columns 0 .. 2 N
+                    tc_mma_tf32(d, dal, dbh, idesc, 1u);                                   // Al x Bh       -> columns 0 .. N
                 }
                 tc_commit(&empty_bar[s]);    // the MMAs above have finished reading the A stage ...
                 tc_commit(&op_empty[e]);     // ... and the entry's weights
@@ -536,10 +536,11 @@ fused_fwd_tc_staged_kernel(PlanDev P, const int* __restrict__ tiles, const int* 
             for (int c4 = 0; c4 < 4; ++c4) {
                 const int col0 = col_base + 16 * c4;
                 if (col0 < N) {   // warp-uniform
-                    uint32_t rr[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * N + col0), rr);
+                    uint32_t rr[16], rl[16];   // the chunk's Ah Bh + Al Bh and its Ah Bl
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * 2 * N + col0), rr);
+                    tmem_ld16(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(r * 2 * N + N + col0), rl);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]);
+                    for (int i = 0; i < 16; ++i) run[16 * c4 + i] += __uint_as_float(rr[i]) + __uint_as_float(rl[i]);
                 }
             }
             tc_fence_before();
