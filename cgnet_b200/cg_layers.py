@@ -65,7 +65,8 @@ def _expect(t, name, shape_tail, device, allow_none=False):
         raise RuntimeError(f"{name} lives on {t.device}, the plan on {device}")
     if not t.is_contiguous():
         raise RuntimeError(f"{name} must be contiguous")
-    if tuple(t.shape[t.dim() - len(shape_tail):]) != tuple(shape_tail) or t.dim() > len(shape_tail) + 1:
+    nd, k = t.dim(), len(shape_tail)
+    if nd < k or nd > k + 1 or tuple(t.shape[nd - k:]) != tuple(shape_tail):
         raise RuntimeError(f"{name} has shape {tuple(t.shape)}, expected (..., {', '.join(str(x) for x in shape_tail)})")
 
 
@@ -117,6 +118,8 @@ class Plan(PlanShapes):
         super().__init__(self.device, self.query(_lib.Q_N_F), self.query(_lib.Q_N_FF), self.query(_lib.Q_N_O),
                          self.query(_lib.Q_W_LEN), self.query(_lib.Q_SUM_TFF))
         self.tile = self.query(_lib.Q_TILE)
+        self._ws_bytes = {}
+        self._fn_layer_fwd, self._fn_layer_bwd = lib.cgb200_layer_fwd, lib.cgb200_layer_bwd
 
     def query(self, what):
         v = _lib.ctypes.c_int64()
@@ -131,6 +134,7 @@ class Plan(PlanShapes):
     def set_option(self, option, value):
         """Select a kernel variant for this plan (``_lib.OPT_*``; ``_lib.AUTO`` restores the library's default)."""
         _lib.check(_lib.load().cgb200_plan_set_option(self.handle, int(option), int(value)), "cgb200_plan_set_option")
+        self._ws_bytes.clear()
 
     def get_option(self, option):
         v = _lib.ctypes.c_int32()
@@ -186,33 +190,48 @@ class Plan(PlanShapes):
         return gFF, gW
 
     def _workspace(self, B, fwd_only=False):
-        lib = _lib.load()
-        n = int((lib.cgb200_layer_fwd_workspace_bytes if fwd_only else lib.cgb200_layer_workspace_bytes)(self.handle, B))
-        if n < 0:
-            _lib.check(1, "cgb200_layer_workspace_bytes")
+        # the size depends on the batch and on the plan's options only: asked once per (batch, kind), forgotten when an
+        # option changes (set_option)
+        key = (B, fwd_only)
+        n = self._ws_bytes.get(key)
+        if n is None:
+            lib = _lib.load()
+            n = int((lib.cgb200_layer_fwd_workspace_bytes if fwd_only else lib.cgb200_layer_workspace_bytes)(self.handle, B))
+            if n < 0:
+                _lib.check(1, "cgb200_layer_workspace_bytes")
+            self._ws_bytes[key] = n
         return torch.empty(max(n, 256), dtype=torch.uint8, device=self.device), n
+
+    def _call(self, fn, name, *args):
+        """Call a library entry point with this plan's device current (the per-step path of a training loop: the device
+        is switched only when it is not current already)."""
+        if torch.cuda.current_device() == self.device.index:
+            status = fn(self.handle, *args, torch.cuda.current_stream().cuda_stream)
+        else:
+            with torch.cuda.device(self.device):
+                status = fn(self.handle, *args, torch.cuda.current_stream().cuda_stream)
+        if status != 0:
+            _lib.check(status, name)
 
     def layer_fwd(self, F, W, stds, cnt, eps, flags):
         B = F.shape[0]
         self.check_batch(B, F=(F, self.n_F))
         self.check_weights(W, stds, flags)
-        O = torch.empty(B, self.n_O, 2, device=F.device, dtype=torch.float32)
+        O = torch.empty(B, self.n_O, 2, device=self.device, dtype=torch.float32)
         ws, n = self._workspace(B, fwd_only=True)
-        with torch.cuda.device(self.device):
-            _lib.check(_lib.load().cgb200_layer_fwd(self.handle, _ptr(F), _ptr(W), _ptr(stds), cnt, eps, flags, _ptr(O), B,
-                                                    _ptr(ws), n, _stream_ptr(self.device)), "cgb200_layer_fwd")
+        self._call(self._fn_layer_fwd, "cgb200_layer_fwd", F.data_ptr(), W.data_ptr(), _ptr(stds), cnt, eps, flags, O.data_ptr(),
+                   B, ws.data_ptr(), n)
         return O
 
     def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True):
-        self.check_batch(F.shape[0], F=(F, self.n_F), gO=(gO, self.n_O))
+        B = F.shape[0]
+        self.check_batch(B, F=(F, self.n_F), gO=(gO, self.n_O))
         self.check_weights(W, stds, flags)
         gF = torch.empty_like(F) if need_gF else None
         gW = torch.empty_like(W)
-        ws, n = self._workspace(F.shape[0])
-        with torch.cuda.device(self.device):
-            _lib.check(_lib.load().cgb200_layer_bwd(self.handle, _ptr(F), _ptr(W), _ptr(stds), eps, flags, _ptr(gO), _ptr(gF),
-                                                    _ptr(gW), F.shape[0], _ptr(ws), n, _stream_ptr(self.device)),
-                       "cgb200_layer_bwd")
+        ws, n = self._workspace(B)
+        self._call(self._fn_layer_bwd, "cgb200_layer_bwd", F.data_ptr(), W.data_ptr(), _ptr(stds), eps, flags, gO.data_ptr(),
+                   _ptr(gF), gW.data_ptr(), B, ws.data_ptr(), n)
         return gF, gW
 
 
@@ -378,16 +397,26 @@ class MyBatchNormWeightMM_cuda(nn.Module):
 
     @property
     def bn_cnt(self):
-        return float(self.bn_cnt_buf.item())
+        return self._count()
 
     @bn_cnt.setter
     def bn_cnt(self, v):
+        self._cnt_cache = float(v)
         self.bn_cnt_buf.fill_(float(v))
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        # the counter lives on the host between checkpoints (one device write per layer and step saved); the buffer is
+        # brought up to date when a state dict is taken
+        if getattr(self, "_cnt_cache", None) is not None:
+            self.bn_cnt_buf.fill_(self._cnt_cache)
+        super()._save_to_state_dict(destination, prefix, keep_vars)
 
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
         # checkpoints written by the reference have no counter: keep the current one instead of failing
         key = prefix + "bn_cnt_buf"
         if key not in state_dict:
+            if getattr(self, "_cnt_cache", None) is not None:
+                self.bn_cnt_buf.fill_(self._cnt_cache)
             state_dict[key] = self.bn_cnt_buf.detach().clone()
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
         self._cnt_cache = None
@@ -411,12 +440,11 @@ class MyBatchNormWeightMM_cuda(nn.Module):
     def _count(self):
         # the counter is read on the host every training step; keep a host copy so the buffer needs no device sync
         if getattr(self, "_cnt_cache", None) is None:
-            self._cnt_cache = self.bn_cnt
+            self._cnt_cache = float(self.bn_cnt_buf.item())
         return self._cnt_cache
 
     def _bump(self):
         self._cnt_cache = self._count() + 1.0
-        self.bn_cnt_buf.fill_(self._cnt_cache)
 
     def _mix_plan(self):
         if self._plan is None:
