@@ -10,7 +10,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu", "sh_project.cu", "raycast.cu"]
+SOURCES = ["plan.cu", "unfused.cu", "fused.cu", "fused_tc.cu", "gff_tc.cu", "sh_project.cu", "raycast.cu"]
 LIB = os.path.join(HERE, "libcgnet_b200.so")
 # raycast.cu: no fused multiply-add, so that its float64 hit tests round exactly like a host evaluation of the same
 # expressions and rays through shared edges pick the same triangle on both sides

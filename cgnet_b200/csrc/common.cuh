@@ -81,6 +81,8 @@ struct GfInfo {
     short role;       // 0: the owned fragment is the first operand, 1: the second
     short in0;        // first channel of the other operand's tile
     short pad_;
+    int cell0;        // first cell of the triple: cell (tile i of t1, tile j of t2) is cell0 + i * ceil(tau2 / T) + j
+    int pad2_;
     int64_t woff;     // cumW[l] + toff
 };
 
@@ -144,7 +146,7 @@ int cuda_fail(cudaError_t e, const char* what);
 enum KernelId {
     K_CG_TABLE = 0, K_CG_FWD, K_CG_BWD, K_FN_STATS, K_WMM_FWD, K_WMM_BWD_W, K_WMM_BWD_MID,
     K_PREP, K_STATS, K_FWD, K_GW, K_GF, K_GF_REDUCE, K_GW_REDUCE, K_TC_PACK, K_FWD_TC, K_GW_TC, K_GF_TC, K_SH_PACK, K_SH_PROJECT,
-    K_RAY_PACK, K_RAY_CAST, K_FWD_REDUCE, K_COUNT
+    K_RAY_PACK, K_RAY_CAST, K_FWD_REDUCE, K_GFF_PACK, K_GFF_GEMM, K_COUNT
 };
 // Bracket every kernel launch with these: they count the launch and, while timing is enabled, record a CUDA event on
 // the launching stream before and after it.
@@ -201,6 +203,10 @@ int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const
 void launch_gw_reduce(const cgb200_plan* p, const float2* partial, int slices, float2* gW, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
 int tc_fwd_level(const cgb200_plan* p, int64_t G);
+int64_t gff_pack_floats(const cgb200_plan* p);
+int64_t gff_group_elems(const cgb200_plan* p);
+int launch_gff_tc(const cgb200_plan* p, int lv, const float2* SG, const float2* W, const float* inv, float* pack, float2* gff,
+                  int G, cudaStream_t st);
 int launch_fwd_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
                   float2* O_part, int B, int G, cudaStream_t st);
 void launch_parts_reduce(int kid, const int64_t* cum, int n_deg, int64_t n_total, const int* parts, const float2* partial,
@@ -270,6 +276,13 @@ struct cgb200_plan {
     int64_t tc_total_cells = 0;                     // cells summed over the row tiles of one sample group
     const int* d_tc_npad = nullptr;
     const int64_t* d_tc_pack_off = nullptr;
+    // mid-activation gradient as a tensor-core GEMM (tile edge 4, full product): per degree the offset of its packed
+    // weights (floats) and of its tiles inside one sample group of the gradient workspace (units of 32 lanes of float2;
+    // the tile of a degree's cell k starts at offset + k (2l+1) T^2)
+    bool gff_ok = false;
+    std::vector<int64_t> gff_pack_off, gff_off;   // [lmax+2]
+    const int64_t* d_gff_pack_off = nullptr;
+    const int64_t* d_gff_off = nullptr;
     std::vector<int> tc_gw_tiles;       // tensor-core weight gradient: (l, first cell of a block of four) pairs, longest first
     const int* d_tc_gw_tiles = nullptr;
     // CG table with every band row padded to a multiple of four floats (16-byte aligned rows: the four band rows a row

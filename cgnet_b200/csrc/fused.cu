@@ -611,12 +611,15 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
     for (int k = 0; k < KN; ++k) h[(K0 + k) * 32] = gt[k];
 }
 
-template <int T, bool DW, bool SPLIT>
+// PRE: the gFF tiles were computed beforehand by the tensor-core GEMM (gff_tc.cu) and sit in the workspace `gff` in the
+// layout of H; phase 1 is then an asynchronous copy of the entry's tile (the launch makes H hold a whole entry).
+template <int T, bool DW, bool SPLIT, bool PRE = false>
 __global__ void __launch_bounds__(kGfWarps * kWarp)
 fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
                 const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
-                float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats) {
+                float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats,
+                const float2* __restrict__ gff = nullptr, int64_t gff_stride = 0, const int64_t* __restrict__ gff_off = nullptr) {
     using S = GfShape<T, DW>;
     constexpr int NH = S::NH, NHP = S::NHP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -704,9 +707,49 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     if (e < e_end) {
         en = entries[e];
         stage_async(en, 0);
-        wt_prefetch(en, wreg);
+        if constexpr (!PRE) wt_prefetch(en, wreg);
     }
-    while (e < e_end) {
+    if constexpr (PRE) {
+        // The tiles come from the workspace: per entry one asynchronous copy of its tile into H, then the gather.  (Tried:
+        // H as two half buffers with the next chunk's copy under way during the gather - the chunked gather cost more
+        // than the hidden copy saved, 3.04 against 2.91 ms at lmax 14 with 16 channels.)
+        GfInfo nxt;
+        while (e < e_end) {
+            const int l = en.l, n = 2 * l + 1, n2 = 2 * en.l2 + 1;
+            const bool has_next = e + parts < e_end;
+            const bool first = en.role == 0;
+            if (has_next) nxt = entries[e + parts];
+            __syncthreads();             // the previous entry's gather is over: H and the idle staging halves are free
+            const bool live = en.to_n > 0;   // a degree without output channels has no tiles and contributes nothing
+            if (live) {
+                const int nt2 = (en.tau2 + T - 1) / T;
+                const int cell = en.cell0 + (first ? q * nt2 + en.in0 / T : (en.in0 / T) * nt2 + q);
+                const int64_t hoff = gff_off[l] + (int64_t)(cell - P.cell_begin[l]) * n * NH;
+                const float4* src = reinterpret_cast<const float4*>(gff + ((int64_t)g * gff_stride + hoff) * 32);
+                float4* dst = reinterpret_cast<float4*>(H);
+                for (int i = threadIdx.x; i < n * NH * 16; i += blockDim.x) __pipeline_memcpy_async(dst + i, src + i, 16);
+                __pipeline_commit();
+            }
+            if (has_next) {
+                stage_async(nxt, buf ^ 1);
+                __pipeline_wait_prior(1);   // the tile and this entry's staging have landed; the next entry's may still fly
+            } else {
+                __pipeline_wait_prior(0);
+            }
+            __syncthreads();
+            const float2* fo = fo2 + (size_t)buf * T * max_n * 32;
+            const float* band = band2 + buf * band_floats;
+            const int lo_ = first ? en.l2 : en.l1;
+            for (int k = 0; live && k < n_units; ++k) {
+                const int u = ulist[warp * 2 * max_n + k];
+                gf_phase2_unit<T, DW, SPLIT>(u, first, H, fo, band, acc, lt, nt, l, lo_, en.l2, n2, 0, n, lane);
+            }
+            en = nxt;
+            e += parts;
+            buf ^= 1;
+        }
+    }
+    while (!PRE && e < e_end) {
         const bool has_next = e + parts < e_end;
         GfInfo nxt;
         if (has_next) nxt = entries[e + parts];
@@ -715,12 +758,12 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
         const bool first = en.role == 0;   // the owned fragment is the first operand of this triple
         const float2* fo = fo2 + (size_t)buf * T * max_n * 32;
         const float* band = band2 + buf * band_floats;
+        const int lo_ = first ? en.l2 : en.l1;
         wt_store(en, wreg);          // phase 1 of the previous entry ended before its second barrier
         __pipeline_wait_prior(0);    // this thread's copies for this entry have landed
         __syncthreads();             // staging visible; the previous entry's phase 2 is over: H and the other halves are free
         if (has_next) stage_async(nxt, buf ^ 1);
         const float2* go = slabG + (int64_t)en.go_off * 32;
-        const int lo_ = first ? en.l2 : en.l1;
         for (int mc0 = 0; mc0 < n; mc0 += Mc) {
             const int mcn = min(Mc, n - mc0);
             if (mc0 > 0) __syncthreads();   // the previous chunk's readers are done with H
@@ -805,6 +848,9 @@ struct Workspace {
     int fwd_level;
     float2* gw_part; // partial weight gradients, [slices][w_len], when the sample groups are split over warps
     int gw_slices;
+    float* gff_pack; // packed conj(W)/std of the mid-gradient GEMM
+    float2* gff;     // its output: the gFF tiles of every cell, [group][cell][m][tile entry][32 lanes]
+    int gff_level;
     int64_t bytes;
 };
 
@@ -842,6 +888,35 @@ int gf_level(const cgb200_plan* p, int64_t G) {
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
+// Shared memory of the input-gradient kernel: the part that does not depend on how many rows of a gFF tile H holds, and
+// the bytes per row.
+void gf_smem(const cgb200_plan* p, size_t* fixed, size_t* per_m) {
+    const int T = p->d.tile;
+    const int NHh = p->d.depthwise ? T : T * T;
+    const int max_to = std::max(p->max_tau_out, 1);
+    *fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
+             2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
+    *per_m = (size_t)NHh * 32 * sizeof(float2);
+}
+
+// The mid activation's gradient by a tensor-core GEMM into the workspace (gff_tc.cu) instead of tile by tile inside the
+// input-gradient kernel.  Needs the plan's tables (tile edge 4, full product), a whole entry's tile in that kernel's
+// shared memory, and 8 bytes of workspace per sample and element of the (tile-padded) mid activation - at most 16 GB
+// by default.  On from 12 output channels (measured on B200, backward of one layer: lmax 14 with 16 channels and 64
+// samples 4.84 -> 3.41 ms, lmax 10 with 32 channels 8.06 -> 3.92 ms, lmax 10 with 16 channels 1.51 -> 1.10 ms; the GEMM
+// writes its output at 5.1 TB/s); CGB200_OPT_GRAD_MID_GEMM overrides.
+bool gff_wanted(const cgb200_plan* p, int64_t G) {
+    if (!p->gff_ok || p->d.depthwise || p->opt[CGB200_OPT_GRAD_F_SPLIT] == 1 || tc_gf_wanted(p)) return false;
+    const int opt = p->opt[CGB200_OPT_GRAD_MID_GEMM];
+    if (opt == 0) return false;
+    size_t fixed = 0, per_m = 0;
+    gf_smem(p, &fixed, &per_m);
+    if (fixed + (size_t)p->max_n * per_m > kMaxDynSmem) return false;
+    if (opt == 1) return true;
+    const double bytes = (double)gff_group_elems(p) * (double)G * 32 * sizeof(float2);
+    return p->max_tau_out >= 12 && bytes <= 16.0 * (1ull << 30);
+}
+
 // Layout of the caller's workspace.  The forward needs only the input slab, the norm factors, the row counters and
 // (tensor-core forward) the packed weights; the backward adds the slab of the output gradient and the partial sums.
 // Both layouts start at the same base and nothing in the workspace survives a call, so a buffer sized for the larger
@@ -872,6 +947,14 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
     if (!fwd_only && w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
+    w.gff_level = tc_fwd_level(p, G);
+    w.gff_pack = (float*)(c + off);
+    w.gff = nullptr;
+    if (!fwd_only && gff_wanted(p, G)) {
+        off += align256(gff_pack_floats(p) * (int64_t)sizeof(float));
+        w.gff = (float2*)(c + off);
+        off += align256(gff_group_elems(p) * G * 32 * (int64_t)sizeof(float2));
+    }
     w.bytes = off;
     return w;
 }
@@ -1106,12 +1189,10 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const int rc2 = launch_gf_tc(p, lv, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, G, st);
             if (rc2) return rc2;
         } else {
-            const int NHh = p->d.depthwise ? T : T * T;
             const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
             const int max_to = std::max(p->max_tau_out, 1);
-            const size_t fixed = (size_t)3 * T * p->max_n * 32 * sizeof(float2) + (size_t)max_to * ((NHh + 1) & ~1) * sizeof(float2) +
-                                 2 * p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
-            const size_t per_m = (size_t)NHh * 32 * sizeof(float2);
+            size_t fixed = 0, per_m = 0;
+            gf_smem(p, &fixed, &per_m);
             if (fixed + per_m > kMaxDynSmem) {
                 set_error("lmax or tau_out too large for the fused input-gradient kernel");
                 return CGB200_ERR_UNSUPPORTED;
@@ -1119,6 +1200,20 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const size_t budget = kMaxDynSmem;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
             const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
             const size_t smem = fixed + (size_t)Mc * per_m;
+            if (ws.gff != nullptr && Mc == p->max_n && T == 4 && !gf_split(p)) {   // H must hold a whole entry's tile
+                const int Mc_pre = Mc;
+                const size_t smem_pre = smem;
+                const int rc2 = launch_gff_tc(p, ws.gff_level, ws.SG, (const float2*)W, ws.inv, ws.gff_pack, ws.gff, G, st);
+                if (rc2) return rc2;
+                auto kern = fused_gf_kernel<4, false, false, true>;
+                if (smem_pre > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pre));
+                launch_begin(K_GF, st);
+                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem_pre, st>>>(
+                    p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out,
+                    part_stride, (int)B, Mc_pre, p->max_n, max_to, band_floats, ws.gff, gff_group_elems(p), p->d_gff_off);
+                launch_end(K_GF, st);
+                CGB_CUDA(cudaGetLastError());
+            } else {
             launch_begin(K_GF, st);
             // phase-2 shape: whole rows, or the owned channels of a row split over two units (see gf_split)
             const bool split_units = gf_split(p);
@@ -1126,10 +1221,11 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             CGB_DISPATCH_TILE(T, p->d.depthwise, {
                 auto kern = split_units ? fused_gf_kernel<TT, DD, true> : fused_gf_kernel<TT, DD, false>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats);
+                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats, nullptr, 0, nullptr);
             });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());
+            }
         }
         if (split) {
             launch_parts_reduce(K_GF_REDUCE, p->d.cumF, p->d.lmax + 1, p->d.n_F, p->d_gf2_parts[lv], ws.gf_part, part_stride, (float2*)gF,

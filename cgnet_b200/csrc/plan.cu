@@ -31,7 +31,8 @@ static const char* kKernelNames[K_COUNT] = {"cg_table", "cg_product_fwd", "cg_pr
                                             "wmm_bwd_w", "wmm_bwd_mid", "prep_transpose", "fused_stats", "fused_fwd",
                                             "fused_grad_w", "fused_grad_f", "fused_grad_f_reduce",
                                             "fused_grad_w_reduce", "tc_pack_weights", "fused_fwd_tensor", "fused_grad_w_tensor", "fused_grad_f_tensor",
-                                            "sh_pack", "sh_project_tensor", "raycast_pack", "raycast_sphere", "fused_fwd_tensor_reduce"};
+                                            "sh_pack", "sh_project_tensor", "raycast_pack", "raycast_sphere", "fused_fwd_tensor_reduce", "grad_mid_pack_weights",
+                                            "grad_mid_tensor"};
 struct TimedLaunch {
     int kid;
     cudaEvent_t a, b;
@@ -475,6 +476,19 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
             if ((rc = upload(p, p->tc_parts[lv], &p->d_tc_parts[lv]))) return rc;
         }
     }
+    p->gff_ok = p->tc_ok && T == 4;
+    if (p->gff_ok) {
+        p->gff_pack_off.assign(L1 + 1, 0);
+        p->gff_off.assign(L1 + 1, 0);
+        for (int l = 0; l < L1; ++l) {
+            const int64_t ncell = p->cell_begin[l + 1] - p->cell_begin[l];
+            const int Kb = (2 * p->tO[l] + 7) & ~7;
+            p->gff_pack_off[l + 1] = p->gff_pack_off[l] + ncell * 64 * Kb;
+            p->gff_off[l + 1] = p->gff_off[l] + (p->tO[l] > 0 ? ncell * (2 * l + 1) * T * T : 0);
+        }
+        if ((rc = upload(p, p->gff_pack_off, &p->d_gff_pack_off))) return rc;
+        if ((rc = upload(p, p->gff_off, &p->d_gff_off))) return rc;
+    }
     if (p->tc_gw_ok) {   // weight gradient: blocks of 128 / (2 T^2) cells, degrees with the longest contraction (2l+1) first
         const int per_block = 128 / (2 * T * T);
         for (int l = L1 - 1; l >= 0; --l) {
@@ -618,6 +632,8 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         gi.role = en.role;
         gi.in0 = en.in0;
         gi.pad_ = 0;
+        gi.cell0 = t.cell0;
+        gi.pad2_ = 0;
         gi.woff = t.woff;
         p->gf_info.push_back(gi);
     }
@@ -777,6 +793,7 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
         if (option == CGB200_OPT_TC_FWD) have = p->tc_ok;
         if (option == CGB200_OPT_TC_GRAD_W) have = p->tc_gw_ok && !p->tc_gw_tiles.empty();
         if (option == CGB200_OPT_TC_GRAD_F) have = p->tc_ok && p->d.tile == 4 && p->max_n <= 64;
+        if (option == CGB200_OPT_GRAD_MID_GEMM) have = p->gff_ok;
         if (needs_tables && !have) {
             set_error("this plan has no tables for the requested tensor-core variant (tile edge, depthwise product or channel counts)");
             return CGB200_ERR_UNSUPPORTED;

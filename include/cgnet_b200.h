@@ -114,7 +114,10 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 #define CGB200_OPT_TC_FWD_SPLIT     12  /* tensor-core forward: splitting level 0..6 of the contraction (the degree with the
                                            most cells in 2^level parts, partial outputs added in part order); default: by
                                            the batch size, so that the longest block stays a fraction of an SM's share      */
-#define CGB200_OPT_COUNT            13
+#define CGB200_OPT_GRAD_MID_GEMM    13  /* input gradient: the mid activation's gradient by a tensor-core GEMM into the
+                                           workspace, read back by the input-gradient kernel, instead of rebuilt tile by
+                                           tile on the CUDA cores (tile edge 4, full product)                             */
+#define CGB200_OPT_COUNT            14
 int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
 int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
 

@@ -184,11 +184,12 @@ def test_bounded_wait_gives_up_cleanly():
         with pytest.raises(RuntimeError, match="gave up"):
             plan.check_status()
         assert torch.isnan(O_bad).all(), "a forward that gave up must mark every output it owns"
-        with option(plan, _lib.OPT_TC_GRAD_W, 1):
-            _, gW_bad = plan.layer_bwd(F, W, None, 1e-5, 0, gO)
+        with option(plan, _lib.OPT_TC_GRAD_W, 1), option(plan, _lib.OPT_GRAD_MID_GEMM, 1):
+            gF_bad, gW_bad = plan.layer_bwd(F, W, None, 1e-5, 0, gO)
         with pytest.raises(RuntimeError, match="gave up"):
             plan.check_status()
         assert torch.isnan(gW_bad).all()
+        assert torch.isnan(gF_bad).all(), "the mid-gradient GEMM marks its tiles, so every input gradient built on them is NaN"
     finally:
         plan.set_option(_lib.OPT_TEST_IDLE_MMA, _lib.AUTO)
         plan.set_option(_lib.OPT_WAIT_POLLS, _lib.AUTO)
@@ -252,3 +253,37 @@ def test_split_contraction_of_tensor_core_forward(taus, tau_out, B, mode):
         assert_fragments_close(got, O_want, tau_out, f"O (tensor-core forward, splitting level {level}) vs oracle")
         hits += int(np.array_equal(got, auto))
     assert hits >= 1
+
+
+def _input_gradient_gemm(plan, case, bn, gemm):
+    from cgnet_b200 import _lib
+    dev = torch.device("cuda", 0)
+    with option(plan, _lib.OPT_GRAD_MID_GEMM, 1 if gemm else 0):
+        F = torch.tensor(case["F"], device=dev)
+        W = torch.tensor(case["W"], device=dev)
+        gO = torch.tensor(case["gO"], device=dev)
+        stds = torch.tensor(case["stds"], device=dev) if bn else None
+        gF, _ = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT if bn else 0, gO)
+        plan.check_status()
+        return gF.cpu().numpy()
+
+
+@pytest.mark.parametrize("bn", [False, True])
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
+                                                 ([8] * 11, [32] * 11, 20, "default"), ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default"),
+                                                 ([8] * 8, [12] * 8, 64, "mst"), ([8] * 3, [64] * 3, 3, "default"),
+                                                 ([6, 0, 8, 4], [8, 4, 0, 20], 4, "default")])
+def test_input_gradient_through_mid_gradient_gemm(taus, tau_out, B, mode, bn):
+    """The input gradient whose first phase is a tensor-core GEMM into the workspace (the gradient of the mid activation,
+    every tile once, in the layout the gather kernel keeps it in shared memory) against the oracle and against the kernel
+    that rebuilds the tiles on the CUDA cores; ragged channel counts, empty fragments on both sides, every group size of
+    the GEMM (4, 2 and 1 cells per group at 16, 32 and 64 output channels)."""
+    from cgnet_b200 import get_plan
+    case = make_case(taus, tau_out, B, mode, seed=61)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0), tile=4)
+    _, gF_want, _, _ = oracle_layer(case, bn, False)
+    got = _input_gradient_gemm(plan, case, bn, gemm=True)
+    again = _input_gradient_gemm(plan, case, bn, gemm=True)
+    assert np.array_equal(got, again), "not deterministic"
+    assert_fragments_close(got, gF_want, taus, "gF (mid-gradient GEMM) vs oracle")
+    assert_fragments_close(got, _input_gradient_gemm(plan, case, bn, gemm=False), taus, "gF (mid-gradient GEMM) vs CUDA-core tiles")
