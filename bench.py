@@ -456,6 +456,8 @@ def measure(args, wl_name, wl, dev, rank, world, batch, steps, warmup, scaling, 
             flops = [w["cg_flops"] for w in kworks]
         elif top.startswith("fused_grad_w"):
             flops = [w["mix_flops"] for w in kworks]                      # gW = gO^T conj(FF): one mixing-sized contraction
+        elif top.startswith("fused_grad_f") and "grad_mid_tensor" in kernels:
+            flops = [2 * w["cg_flops"] for w in kworks]                   # the product's two operand roles; gFF comes from grad_mid_tensor
         elif top.startswith("fused_grad_f"):
             flops = [2 * w["cg_flops"] + w["mix_flops"] for w in kworks]  # gFF (mixing-sized) + the product's two operand roles
         else:

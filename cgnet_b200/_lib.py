@@ -55,7 +55,8 @@ FN_PRESENT, FN_UPDATE = 0x1, 0x2
 PLAN_DEPTHWISE = 0x1
 AUTO = -1
 (OPT_TC_FWD, OPT_TC_GRAD_W, OPT_TC_GRAD_F, OPT_TC_STAGES, OPT_FWD_SLAB, OPT_GRAD_F_SPLIT, OPT_STATS_SPLIT, OPT_BWD_SERIAL,
- OPT_WAIT_POLLS, OPT_TEST_IDLE_MMA, OPT_TC_STAGED, OPT_TC_ABUF, OPT_TC_FWD_SPLIT, OPT_GRAD_MID_GEMM) = range(14)
+ OPT_WAIT_POLLS, OPT_TEST_IDLE_MMA, OPT_TC_STAGED, OPT_TC_ABUF, OPT_TC_FWD_SPLIT, OPT_GRAD_MID_GEMM,
+ OPT_FWD_KEEP_MID) = range(15)
 
 
 def plan_tile_flag(tile):

@@ -208,7 +208,7 @@ int64_t gff_group_elems(const cgb200_plan* p);
 int launch_gff_tc(const cgb200_plan* p, int lv, const float2* SG, const float2* W, const float* inv, float* pack, float2* gff,
                   int G, cudaStream_t st);
 int launch_fwd_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
-                  float2* O_part, int B, int G, cudaStream_t st);
+                  float2* O_part, int B, int G, const float2* ff, cudaStream_t st);
 void launch_parts_reduce(int kid, const int64_t* cum, int n_deg, int64_t n_total, const int* parts, const float2* partial,
                          int64_t part_stride, float2* out, int B, bool skip_single, cudaStream_t st);
 }  // namespace cgb200

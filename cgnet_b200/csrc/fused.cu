@@ -128,7 +128,8 @@ __device__ __forceinline__ float moving_std_f(float old, double sigma, float cnt
 template <int T, bool DW, int I0, int IN>
 __device__ __forceinline__ void stats_body(const PlanDev& P, const CellRec& cell, const TripleRec& tr, const float2* __restrict__ SF,
                                            float* __restrict__ stds, float* __restrict__ inv, float cnt, float eps, int B, int G,
-                                           const float* __restrict__ C, double (*red)[TileShape<T, DW>::NV][2]) {
+                                           const float* __restrict__ C, double (*red)[TileShape<T, DW>::NV][2],
+                                           float2* __restrict__ ff_tile = nullptr, int64_t ff_stride = 0) {
     constexpr int NE = DW ? IN : IN * T;      // tile entries handled here
     constexpr int E0 = DW ? I0 : I0 * T;      // first of them
     const int n = 2 * tr.l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
@@ -143,6 +144,13 @@ __device__ __forceinline__ void stats_body(const PlanDev& P, const CellRec& cell
         float2 v[NE];
         if constexpr (!DW && IN < T) gen_slab_rows<T, I0, IN>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
         else gen_slab<T, DW, true>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
+        if constexpr (!DW && IN == T) {
+            if (ff_tile != nullptr) {   // keep the tile for the tensor-core forward: [group][cell][m][entry][lane]
+                float2* dst = ff_tile + ((int64_t)g * ff_stride + (int64_t)mi * NE) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < NE; ++i) dst[i * 32] = v[i];
+            }
+        }
 #pragma unroll
         for (int i = 0; i < NE; ++i) {
             const float nrm = v[i].x * v[i].x + v[i].y * v[i].y;
@@ -182,7 +190,7 @@ __device__ __forceinline__ void stats_body(const PlanDev& P, const CellRec& cell
 template <int T, bool DW, bool SPLIT>
 __global__ void __launch_bounds__(256, (SPLIT || T <= 4) ? 2 : 1)
 fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__ stds, float* __restrict__ inv, float cnt,
-                   float eps, int B, int G) {
+                   float eps, int B, int G, float2* __restrict__ ff, int64_t ff_stride, const int64_t* __restrict__ ff_off) {
     constexpr int NV = TileShape<T, DW>::NV;
     __shared__ double red[8][NV][2];
     extern __shared__ __align__(16) float sband[];   // the triple's CG band, (2l+1) x (2l2+1)
@@ -198,7 +206,10 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
         if ((blockIdx.x & 1) == 0) stats_body<T, DW, 0, AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
         else stats_body<T, DW, AH, T - AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
     } else {
-        stats_body<T, DW, 0, T>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
+        // ff: the generated tiles are also written out (tile edge 4, full product), so that the tensor-core forward that
+        // follows reads them back instead of generating them again
+        float2* tile = (ff == nullptr || P.tO[tr.l] == 0) ? nullptr : ff + (ff_off[tr.l] + (int64_t)(cidx - P.cell_begin[tr.l]) * n * TileShape<T, DW>::NV) * 32;
+        stats_body<T, DW, 0, T>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red, tile, ff_stride);
     }
 }
 
@@ -848,6 +859,8 @@ struct Workspace {
     int fwd_level;
     float2* gw_part; // partial weight gradients, [slices][w_len], when the sample groups are split over warps
     int gw_slices;
+    float2* ff;      // forward with a statistics update: the generated tiles, written by the statistics kernel and read
+                     // back by the tensor-core forward (same layout as gff); null when not used
     float* gff_pack; // packed conj(W)/std of the mid-gradient GEMM
     float2* gff;     // its output: the gFF tiles of every cell, [group][cell][m][tile entry][32 lanes]
     int gff_level;
@@ -917,6 +930,22 @@ bool gff_wanted(const cgb200_plan* p, int64_t G) {
     return p->max_tau_out >= 12 && bytes <= 16.0 * (1ull << 30);
 }
 
+// Forward with a statistics update on the tensor-core path: the statistics kernel generates every tile of the mid
+// activation anyway; it then also writes them to the workspace and the forward kernel's generator warps load their
+// tile instead of generating it a second time (same bits: both run the same generator).  Tile edge 4, full product,
+// same workspace limit as the mid-gradient GEMM; CGB200_OPT_FWD_KEEP_MID overrides.  The workspace of the forward is sized
+// for it whenever the variant is possible, also for calls without an update (which do not use it).
+bool ff_store_wanted(const cgb200_plan* p, int64_t G) {
+    if (!p->gff_ok || p->d.depthwise || !tc_wanted(p) || p->opt[CGB200_OPT_TC_STAGED] >= 1) return false;
+    const int opt = p->opt[CGB200_OPT_FWD_KEEP_MID];
+    if (opt == 0) return false;
+    if (opt == 1) return true;
+    const int so = p->opt[CGB200_OPT_STATS_SPLIT];
+    if (so == 1) return false;
+    const double bytes = (double)gff_group_elems(p) * (double)G * 32 * sizeof(float2);
+    return bytes <= 16.0 * (1ull << 30);
+}
+
 // Layout of the caller's workspace.  The forward needs only the input slab, the norm factors, the row counters and
 // (tensor-core forward) the packed weights; the backward adds the slab of the output gradient and the partial sums.
 // Both layouts start at the same base and nothing in the workspace survives a call, so a buffer sized for the larger
@@ -947,6 +976,11 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
     if (!fwd_only && w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
+    w.ff = nullptr;
+    if (ff_store_wanted(p, G)) {
+        w.ff = (float2*)(c + off);
+        off += align256(gff_group_elems(p) * G * 32 * (int64_t)sizeof(float2));
+    }
     w.gff_level = tc_fwd_level(p, G);
     w.gff_pack = (float*)(c + off);
     w.gff = nullptr;
@@ -1050,6 +1084,7 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     PrepJob none{};
     if ((rc = launch_prep(p, jf, none, 1, (int)B, G, fn ? stds : nullptr, eps, update ? nullptr : ws.inv, ws.counters, st)))
         return rc;
+    bool ff_stored = false;
     if (update && p->d.n_cells > 0) {
         const size_t band = p->gen_band_bytes;
         launch_begin(K_STATS, st);
@@ -1060,15 +1095,18 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
         CGB_DISPATCH_TILE(T, p->d.depthwise, {
             auto kern = split_rows ? fused_stats_kernel<TT, DD, true> : fused_stats_kernel<TT, DD, false>;
             if (band > 40 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band));
-            kern<<<p->d.n_cells * (split_rows ? 2 : 1), 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G);
+            kern<<<p->d.n_cells * (split_rows ? 2 : 1), 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G,
+                                                                        split_rows ? nullptr : ws.ff, gff_group_elems(p), p->d_gff_off);
         });
+        ff_stored = ws.ff != nullptr && !split_rows;
         launch_end(K_STATS, st);
         CGB_CUDA(cudaGetLastError());
     }
     const int n_rows = (int)p->fwd_rows.size() / 2;
     if (n_rows == 0) return CGB200_OK;
     if (tc_wanted(p))
-        return launch_fwd_tc(p, ws.fwd_level, ws.SF, (const float2*)W, ws.inv, ws.tc_pack, (float2*)O, ws.fwd_part, (int)B, G, st);
+        return launch_fwd_tc(p, ws.fwd_level, ws.SF, (const float2*)W, ws.inv, ws.tc_pack, (float2*)O, ws.fwd_part, (int)B, G,
+                             ff_stored ? ws.ff : nullptr, st);
     // persistent shared-memory variant when one group's slab (plus reduction buffer and staging areas) fits in an SM
     const int NVh = p->d.depthwise ? T : T * T;
     // output channels per pass: the smallest instantiated width that covers the widest degree (at most kFwdTo)

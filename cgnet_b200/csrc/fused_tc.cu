@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
                     const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O,
                     float2* __restrict__ O_part, int64_t part_stride, int B, int n_max,
-                    int max_n, int* __restrict__ status, int n_stages, int n_flush, uint32_t wait_limit, int idle_mma) {
+                    int max_n, int* __restrict__ status, int n_stages, int n_flush, uint32_t wait_limit, int idle_mma,
+                    const float2* __restrict__ ff, int64_t ff_stride, const int64_t* __restrict__ ff_off) {
     constexpr int Kc = 2 * T * T;            // real K extent of one cell
     constexpr int NV = T * T;
     constexpr uint32_t kSbo = (Kc / 4) * 128;   // bytes between consecutive 8-row groups
@@ -162,7 +163,12 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
                 bulk_g2s(b_st, pack + pack_off[l] + (int64_t)(k0 + k) * 2 * N * Kc, b_bytes, &full_bar[s]);
             }
             float2 v[NV];
-            if (live_m) {
+            if (live_m && ff != nullptr) {
+                // the statistics kernel of this call generated the tile already and kept it: [group][cell][m][entry][lane]
+                const float2* src = ff + ((int64_t)g * ff_stride + ff_off[l] + ((int64_t)(k0 + k) * n + mi) * NV) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = src[i * 32];
+            } else if (live_m) {
                 const CellInfo ci = P.cell_info[c_begin + k];
                 const int n2 = 2 * ci.l2 + 1;
                 __syncwarp();
@@ -1136,7 +1142,7 @@ int tc_fwd_level(const cgb200_plan* p, int64_t G) {
 
 template <int T>
 static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
-                     float2* O_part, int B, int G, cudaStream_t st) {
+                     float2* O_part, int B, int G, const float2* ff, cudaStream_t st) {
     constexpr int Kc = 2 * T * T;
     int n_max = 16;
     for (int v : p->tc_npad) n_max = std::max(n_max, v);
@@ -1212,7 +1218,7 @@ static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float
     const int64_t part_stride = (int64_t)B * p->d.n_O;
     kern<<<dim3((unsigned)p->tc_tiles[lv].size() / 4, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(
         p->d, p->d_tc_tiles[lv], p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, O_part, part_stride, B, n_max, p->max_n, p->d_status,
-        n_stages, n_flush, wait_polls(p), idle);
+        n_stages, n_flush, wait_polls(p), idle, T == 4 ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
     if (p->tc_max_parts[lv] > 1) {
@@ -1223,9 +1229,9 @@ static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float
 }
 
 int launch_fwd_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* W, const float* inv, float* pack, float2* O,
-                  float2* O_part, int B, int G, cudaStream_t st) {
-    if (p->d.tile == 4) return launch_tc<4>(p, lv, SF, W, inv, pack, O, O_part, B, G, st);
-    if (p->d.tile == 2) return launch_tc<2>(p, lv, SF, W, inv, pack, O, O_part, B, G, st);
+                  float2* O_part, int B, int G, const float2* ff, cudaStream_t st) {
+    if (p->d.tile == 4) return launch_tc<4>(p, lv, SF, W, inv, pack, O, O_part, B, G, ff, st);
+    if (p->d.tile == 2) return launch_tc<2>(p, lv, SF, W, inv, pack, O, O_part, B, G, nullptr, st);
     set_error("internal: tensor-core forward asked for an unsupported tile edge");
     return CGB200_ERR_UNSUPPORTED;
 }

@@ -793,7 +793,7 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
         if (option == CGB200_OPT_TC_FWD) have = p->tc_ok;
         if (option == CGB200_OPT_TC_GRAD_W) have = p->tc_gw_ok && !p->tc_gw_tiles.empty();
         if (option == CGB200_OPT_TC_GRAD_F) have = p->tc_ok && p->d.tile == 4 && p->max_n <= 64;
-        if (option == CGB200_OPT_GRAD_MID_GEMM) have = p->gff_ok;
+        if (option == CGB200_OPT_GRAD_MID_GEMM || option == CGB200_OPT_FWD_KEEP_MID) have = p->gff_ok;
         if (needs_tables && !have) {
             set_error("this plan has no tables for the requested tensor-core variant (tile edge, depthwise product or channel counts)");
             return CGB200_ERR_UNSUPPORTED;

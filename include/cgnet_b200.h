@@ -117,7 +117,10 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 #define CGB200_OPT_GRAD_MID_GEMM    13  /* input gradient: the mid activation's gradient by a tensor-core GEMM into the
                                            workspace, read back by the input-gradient kernel, instead of rebuilt tile by
                                            tile on the CUDA cores (tile edge 4, full product)                             */
-#define CGB200_OPT_COUNT            14
+#define CGB200_OPT_FWD_KEEP_MID      14  /* forward with a statistics update on the tensor-core path: the statistics kernel
+                                           keeps the tiles of the mid activation it generates in the workspace and the
+                                           forward kernel reads them back instead of generating them again               */
+#define CGB200_OPT_COUNT            15
 int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
 int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
 
@@ -178,7 +181,11 @@ int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, co
                      const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,
                      void* stream);
 
-/* Scratch bytes the two fused calls need for a batch of B samples (the larger of the two). */
+/* Scratch bytes the two fused calls need for a batch of B samples (the larger of the two).  From 12 output channels on
+   (tile edge 4, full product) the backward keeps the gradient of the mid activation in the workspace between its two
+   kernels: 8 bytes per sample and element of the tile-padded mid activation, i.e. gigabytes for the wide layers (2.1 GB
+   at lmax 14 with 16 channels and 64 samples; above 16 GB the library goes back to rebuilding it tile by tile;
+   CGB200_OPT_GRAD_MID_GEMM 0 does so always). */
 int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
 /* Scratch bytes cgb200_layer_fwd alone needs (input slab, norm factors, row counters, packed tensor-core weights);
    never more than cgb200_layer_workspace_bytes.  Both depend on the plan's options at the time of the call. */

@@ -287,3 +287,24 @@ def test_input_gradient_through_mid_gradient_gemm(taus, tau_out, B, mode, bn):
     assert np.array_equal(got, again), "not deterministic"
     assert_fragments_close(got, gF_want, taus, "gF (mid-gradient GEMM) vs oracle")
     assert_fragments_close(got, _input_gradient_gemm(plan, case, bn, gemm=False), taus, "gF (mid-gradient GEMM) vs CUDA-core tiles")
+
+
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
+                                                 ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default"), ([6, 0, 8, 4], [8, 4, 0, 20], 4, "default"),
+                                                 ([8] * 8, [12] * 8, 64, "mst")])
+def test_forward_reads_back_the_tiles_the_statistics_kernel_kept(taus, tau_out, B, mode):
+    """Forward with a statistics update on the tensor-core path: the statistics kernel keeps the tiles of the mid
+    activation it generates and the forward kernel loads them instead of generating them again.  Both run the same
+    generator, so output and updated statistics must be the same bits as with the variant switched off, and both must
+    match the oracle."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, mode, seed=62)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0), tile=4)
+    O_want, _, _, stds_want = oracle_layer(case, True, True, cnt=2.0)
+    out = {}
+    for keep in (0, 1):
+        with option(plan, _lib.OPT_FWD_KEEP_MID, keep):
+            out[keep] = _forward(plan, case, True, True, tc=True)
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+    assert_fragments_close(out[1][0], O_want, tau_out, "O (tiles kept by the statistics kernel) vs oracle")
+    np.testing.assert_allclose(out[1][1], stds_want, rtol=2e-5, atol=1e-7)
