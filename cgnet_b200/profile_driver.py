@@ -1,13 +1,14 @@
 """One launch of every kernel family of libcgnet_b200.so, for a profiler to capture.
 
     python -m cgnet_b200.profile_driver                      # runs by itself: every call returns, statuses are checked
-    ncu --set full --clock-control none -k regex:'cg_fwd|cg_bwd|fn_stats|wmm_|prep_kernel|tc_pack|fused_|sh_pack|sh_project|reduce_kernel|raycast' \\
-        -c 40 -o all_kernels python -m cgnet_b200.profile_driver
+    ncu --set full --clock-control none -k regex:'cg_fwd|cg_bwd|fn_stats|wmm_|prep_kernel|tc_pack|fused_|gff_|sh_pack|sh_project|reduce_kernel|raycast' \\
+        -c 48 -o all_kernels python -m cgnet_b200.profile_driver
 
 Cases (seeded random inputs; the two-pass case is sized so that the mid activation, 190 MB, exceeds the 126 MB L2):
   two-pass product / statistics / mixing and their gradients   lmax 10, 5 channels, batch 200
   fused layer forward (training statistics) + backward         the same layer (CUDA-core kernels)
-  fused layer forward + backward                               lmax 10, 16 channels, batch 128 (tensor-core forward and weight gradient)
+  fused layer forward + backward                               lmax 10, 16 channels, batch 128 (tensor-core forward, weight gradient
+                                                               and mid-gradient GEMM)
   spherical-harmonic projection                                4096 points, lmax 14, 768 functions
   mesh -> sphere ray casting                                   a 5120-triangle sphere mesh, 64 x 64 grid
 """
