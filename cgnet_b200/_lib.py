@@ -36,6 +36,7 @@ SIGNATURES = {
     "cgb200_layer_bwd": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_int, vp, vp, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
     "cgb200_layer_fwd_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
+    "cgb200_layer_keeps_mid": (ctypes.c_int, [vp, ctypes.c_int64]),
     "cgb200_layer_fwd_static": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp]),
     "cgb200_sh_basis_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int]),
     "cgb200_sh_workspace_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int64]),
@@ -51,7 +52,7 @@ SIGNATURES = {
 }
 
 Q_N_F, Q_N_FF, Q_N_O, Q_W_LEN, Q_SUM_TFF, Q_CG_LEN, Q_N_TRIPLES, Q_TILE = range(8)
-FN_PRESENT, FN_UPDATE = 0x1, 0x2
+FN_PRESENT, FN_UPDATE, FN_KEEP_MID = 0x1, 0x2, 0x4
 PLAN_DEPTHWISE = 0x1
 AUTO = -1
 (OPT_TC_FWD, OPT_TC_GRAD_W, OPT_TC_GRAD_F, OPT_TC_STAGES, OPT_FWD_SLAB, OPT_GRAD_F_SPLIT, OPT_STATS_SPLIT, OPT_BWD_SERIAL,

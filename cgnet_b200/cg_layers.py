@@ -18,6 +18,8 @@ Differences from the reference, all additive:
   * ``bn_cnt`` is also kept in a buffer so that it survives ``state_dict`` round trips (reference: a Python float that
     a resume silently resets, ``CG_layers.py:92``); checkpoints without it still load;
   * ``depthwise=True`` (channel-wise product, tau_l1 == tau_l2 required) is an extension with no reference counterpart;
+  * ``keep_mid`` (``CGBN_cuda``): wide layers in training keep their workspace, with the mid activation's tiles in it, from
+    the forward to the backward (default: while it stays under a sixteenth of the device's memory);
   * gradients of ``W`` are summed in a fixed order (the reference accumulates them with ``atomicAdd``).
 """
 import functools
@@ -189,7 +191,7 @@ class Plan(PlanShapes):
                        "cgb200_fn_wmm_bwd")
         return gFF, gW
 
-    def _workspace(self, B, fwd_only=False):
+    def _workspace_bytes(self, B, fwd_only=False):
         # the size depends on the batch and on the plan's options only: asked once per (batch, kind), forgotten when an
         # option changes (set_option)
         key = (B, fwd_only)
@@ -200,6 +202,10 @@ class Plan(PlanShapes):
             if n < 0:
                 _lib.check(1, "cgb200_layer_workspace_bytes")
             self._ws_bytes[key] = n
+        return n
+
+    def _workspace(self, B, fwd_only=False):
+        n = self._workspace_bytes(B, fwd_only)
         return torch.empty(max(n, 256), dtype=torch.uint8, device=self.device), n
 
     def _call(self, fn, name, *args):
@@ -213,23 +219,41 @@ class Plan(PlanShapes):
         if status != 0:
             _lib.check(status, name)
 
-    def layer_fwd(self, F, W, stds, cnt, eps, flags):
+    def keeps_mid(self, B):
+        """Does a forward with a statistics update for B samples leave the mid activation's tiles in its workspace
+        (tensor-core path, tile edge 4)?  Then ``layer_fwd(..., keep=True)`` hands the workspace back and
+        ``layer_bwd(..., kept=workspace)`` lets the weight gradient read the tiles instead of generating them again."""
+        key = ("keeps", B)
+        v = self._ws_bytes.get(key)
+        if v is None:
+            v = self._ws_bytes[key] = int(_lib.load().cgb200_layer_keeps_mid(self.handle, B))
+        return bool(v)
+
+    def layer_fwd(self, F, W, stds, cnt, eps, flags, keep=False):
+        """``keep=True`` (only where ``keeps_mid(B)`` and with ``FN_UPDATE``): returns ``(O, workspace)``; the workspace, sized
+        for the backward as well, holds the tiles and must reach ``layer_bwd`` untouched."""
         B = F.shape[0]
         self.check_batch(B, F=(F, self.n_F))
         self.check_weights(W, stds, flags)
         O = torch.empty(B, self.n_O, 2, device=self.device, dtype=torch.float32)
-        ws, n = self._workspace(B, fwd_only=True)
+        ws, n = self._workspace(B, fwd_only=not keep)
         self._call(self._fn_layer_fwd, "cgb200_layer_fwd", F.data_ptr(), W.data_ptr(), _ptr(stds), cnt, eps, flags, O.data_ptr(),
                    B, ws.data_ptr(), n)
-        return O
+        return (O, ws) if keep else O
 
-    def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True):
+    def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True, kept=None):
         B = F.shape[0]
         self.check_batch(B, F=(F, self.n_F), gO=(gO, self.n_O))
         self.check_weights(W, stds, flags)
         gF = torch.empty_like(F) if need_gF else None
         gW = torch.empty_like(W)
-        ws, n = self._workspace(B)
+        if kept is not None:
+            ws, n = kept, self._workspace_bytes(B)
+            if kept.device != self.device or kept.numel() < n:
+                raise RuntimeError("the kept workspace does not belong to this plan and batch")
+            flags = flags | _lib.FN_KEEP_MID
+        else:
+            ws, n = self._workspace(B)
         self._call(self._fn_layer_bwd, "cgb200_layer_bwd", F.data_ptr(), W.data_ptr(), _ptr(stds), eps, flags, gO.data_ptr(),
                    _ptr(gF), gW.data_ptr(), B, ws.data_ptr(), n)
         return gF, gW
@@ -336,11 +360,15 @@ class _CGBN_fused(torch.autograd.Function):
     """Whole layer through the fused kernels: the mid activation is regenerated in the backward, never stored."""
 
     @staticmethod
-    def forward(ctx, Fs, W, plan, bn_stds, bn_cnt, bn_eps, bn_updateflag):
+    def forward(ctx, Fs, W, plan, bn_stds, bn_cnt, bn_eps, bn_updateflag, keep_mid=False):
         Fs = _check_cuda_f32(Fs, "activations")
         W = _check_cuda_f32(W, "W")
         flags = _fn_flags(bn_stds, bn_updateflag)
-        out = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags)
+        ctx.kept = None
+        if keep_mid and (flags & _lib.FN_UPDATE) and plan.keeps_mid(Fs.shape[0]):
+            out, ctx.kept = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags, keep=True)
+        else:
+            out = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags)
         ctx.plan, ctx.eps, ctx.flags = plan, float(bn_eps), flags & _lib.FN_PRESENT
         ctx.save_for_backward(Fs, W, None if bn_stds is None else bn_stds.detach().clone())
         return out
@@ -348,9 +376,10 @@ class _CGBN_fused(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         Fs, W, stds = ctx.saved_tensors
+        kept, ctx.kept = ctx.kept, None   # one backward per forward: the workspace is overwritten by it
         gF, gW = ctx.plan.layer_bwd(Fs, W, stds, ctx.eps, ctx.flags, _check_cuda_f32(grad_output, "grad_output"),
-                                    need_gF=ctx.needs_input_grad[0])
-        return gF, gW, None, None, None, None, None
+                                    need_gF=ctx.needs_input_grad[0], kept=kept)
+        return gF, gW, None, None, None, None, None, None
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -531,12 +560,13 @@ class CGBN_cuda(nn.Module):
     """
 
     def __init__(self, lmax, taus_fs, tau_out, batchnorm=True, sparse_flag=False, device="cuda", weight_scale=0.05,
-                 init="random", eps=1e-5, fused=True, depthwise=False, lll_mode=None):
+                 init="random", eps=1e-5, fused=True, depthwise=False, lll_mode=None, keep_mid=None):
         super().__init__()
         self.lmax = lmax
         self._init_method = init
         self.sparse_flag = sparse_flag
         self.fused = fused
+        self.keep_mid = keep_mid
         mode = lll_mode if lll_mode is not None else ("mst" if sparse_flag else None)
         self.cg = CG_woFilter_cuda(lmax, taus_fs, lll_mode=mode, device=device, tau_out=tau_out, depthwise=depthwise)
         self.t_F = self.cg.t_F
@@ -546,12 +576,31 @@ class CGBN_cuda(nn.Module):
                                               plan=self.cg.plan)
         self.to(device)
 
+    def _keeps_mid(self, B):
+        """Keep the layer's workspace from the forward to the backward, so that the weight gradient reads the mid
+        activation's tiles the forward left in it instead of generating them again (wide layers on the tensor-core path
+        only: ``Plan.keeps_mid``)?  ``keep_mid=True`` / ``False`` decide; the default keeps while one layer's workspace stays
+        under a sixteenth of the device's memory (it is held until the layer's backward has run)."""
+        if self.keep_mid is False:
+            return False
+        plan = self.cg.plan
+        if not plan.keeps_mid(B):
+            return False
+        if self.keep_mid:
+            return True
+        if CGBN_cuda._device_bytes.get(plan.device) is None:
+            CGBN_cuda._device_bytes[plan.device] = torch.cuda.get_device_properties(plan.device).total_memory
+        return plan._workspace_bytes(B) * 16 <= CGBN_cuda._device_bytes[plan.device]
+
+    _device_bytes = {}
+
     def forward(self, fs, straight_output=False):
         bn = self.bnWMM
         if self.fused:
             x = _flatten_input(fs)
             update = bool(bn.batchnorm and bn.training)
-            new_fs = _CGBN_fused.apply(x, bn.W, self.cg.plan, bn.bn_stds, bn._count(), bn._eps, update)
+            keep = update and torch.is_grad_enabled() and self._keeps_mid(x.shape[0])
+            new_fs = _CGBN_fused.apply(x, bn.W, self.cg.plan, bn.bn_stds, bn._count(), bn._eps, update, keep)
             if update:
                 bn._bump()
         else:

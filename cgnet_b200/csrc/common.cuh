@@ -199,7 +199,7 @@ bool tc_gf_wanted(const cgb200_plan* p);
 int launch_gf_tc(const cgb200_plan* p, int lv, const float2* SF, const float2* SG, const float2* W, const float* inv, float2* out,
                  int64_t part_stride, int B, int G, cudaStream_t st);
 int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
-                 int max_slices, int G, cudaStream_t st);
+                 int max_slices, int G, const float2* ff, cudaStream_t st);
 void launch_gw_reduce(const cgb200_plan* p, const float2* partial, int slices, float2* gW, cudaStream_t st);
 int64_t tc_pack_floats(const cgb200_plan* p);
 int tc_fwd_level(const cgb200_plan* p, int64_t G);

@@ -955,6 +955,13 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
     Workspace w{};
     int64_t off = 0;
     char* c = (char*)base;
+    // first, at the same place in the forward's and the backward's layout: the tiles a forward with a statistics update
+    // keeps (a backward given the same workspace with CGB200_FN_KEEP_MID reads them)
+    w.ff = nullptr;
+    if (ff_store_wanted(p, G)) {
+        w.ff = (float2*)(c + off);
+        off += align256(gff_group_elems(p) * G * 32 * (int64_t)sizeof(float2));
+    }
     w.SF = (float2*)(c + off);
     off += align256(std::max<int64_t>(p->d.nSF, 1) * G * 32 * (int64_t)sizeof(float2));
     w.SG = (float2*)(c + off);
@@ -976,11 +983,6 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
     w.gw_slices = gw_slices(p, G);
     w.gw_part = (float2*)(c + off);
     if (!fwd_only && w.gw_slices > 1) off += align256((int64_t)w.gw_slices * p->d.w_len * (int64_t)sizeof(float2));
-    w.ff = nullptr;
-    if (ff_store_wanted(p, G)) {
-        w.ff = (float2*)(c + off);
-        off += align256(gff_group_elems(p) * G * 32 * (int64_t)sizeof(float2));
-    }
     w.gff_level = tc_fwd_level(p, G);
     w.gff_pack = (float*)(c + off);
     w.gff = nullptr;
@@ -1055,6 +1057,13 @@ int64_t cgb200_layer_workspace_bytes(const cgb200_plan* p, int64_t B) {
         return -1;
     }
     return carve(p, std::max<int64_t>(B, 1), nullptr).bytes;
+}
+
+int cgb200_layer_keeps_mid(const cgb200_plan* p, int64_t B) {
+    if (p == nullptr || B <= 0) return 0;
+    const int so = p->opt[CGB200_OPT_STATS_SPLIT];
+    const bool split_rows = !p->d.depthwise && (so >= 0 ? so != 0 : p->d.tile >= 5);
+    return ff_store_wanted(p, (B + 31) / 32) && !split_rows && p->d.tile == 4 ? 1 : 0;
 }
 
 int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* p, int64_t B) {
@@ -1179,7 +1188,9 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
     // weight gradient (enqueued on stream gs): every (to, k) of every degree with both output and mid channels belongs to exactly one task
     const int n_tasks = p->gw_begin.empty() ? 0 : p->gw_begin.back();
     auto enqueue_gw = [&](cudaStream_t gs) -> int {
-        if (tc_gw_wanted(p)) return launch_gw_tc(p, ws.SF, ws.SG, ws.inv, (float2*)gW, ws.gw_part, ws.gw_slices, G, gs);
+        if (tc_gw_wanted(p))
+            return launch_gw_tc(p, ws.SF, ws.SG, ws.inv, (float2*)gW, ws.gw_part, ws.gw_slices, G,
+                                (flags & CGB200_FN_KEEP_MID) ? ws.ff : nullptr, gs);
         const int blocks = (n_tasks + kGwWarps - 1) / kGwWarps;
         const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
         const size_t smem = (size_t)kGwWarps * p->gen_band_bytes;

@@ -605,13 +605,21 @@ struct GwTcShape {
 };
 
 // one generator warp's values of a chunk: rows [I0, I0 + IN) of cell `c`'s tile -> TF32 high / low parts in the A' stage
+// (`tile`: the row's kept values, [tile entry][32 lanes] with the lane already added, or null to generate them)
 template <int T, int I0, int IN>
 __device__ __forceinline__ void gw_tc_generate(const CellInfo& ci, const float2* __restrict__ slab, const float* __restrict__ cbuf,
-                                               int mi, int l, int c, unsigned char* __restrict__ a_hi, uint32_t a_bytes) {
+                                               int mi, int l, int c, unsigned char* __restrict__ a_hi, uint32_t a_bytes,
+                                               const float2* __restrict__ tile) {
     constexpr int MR = 2 * T * T;
     float2 v[IN * T];
-    if constexpr (IN == T) gen_slab<T, false, true>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
-    else gen_slab_rows<T, I0, IN>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+    if (tile != nullptr) {
+#pragma unroll
+        for (int e = 0; e < IN * T; ++e) v[e] = tile[(I0 * T + e) * 32];
+    } else if constexpr (IN == T) {
+        gen_slab<T, false, true>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+    } else {
+        gen_slab_rows<T, I0, IN>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+    }
     const int rbase = c * MR + 2 * I0 * T;   // even: a value's (re, im) rows share an 8-row group
 #pragma unroll
     for (int e = 0; e < IN * T; ++e) {
@@ -632,7 +640,7 @@ __global__ void __launch_bounds__(kTcMaxThreads)
 fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
                    int max_n, int* __restrict__ status, int n_stages, int n_flush, int64_t slice_stride, uint32_t wait_limit,
-                   int idle_mma) {
+                   int idle_mma, const float2* __restrict__ ff, int64_t ff_stride, const int64_t* __restrict__ ff_off) {
     using S = GwTcShape<T>;
     constexpr int MR = S::MR;
     constexpr int kFlushChunks = kChunkSteps / 12;   // K chunks (32 samples = 4 K steps x 3 MMAs) summed in tensor memory before a flush
@@ -700,15 +708,20 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
             const int g = slice + gi * slices;
             if (live) {
                 const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
-                __syncwarp();
-                for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
-                __syncwarp();
+                // the tiles the forward kept (same generator, same bits), or the band row to generate them again
+                const float2* tile = ff == nullptr ? nullptr
+                                                   : ff + ((int64_t)g * ff_stride + ff_off[l] + ((int64_t)cell * n + mi) * S::NV) * 32 + lane;
+                if (tile == nullptr) {
+                    __syncwarp();
+                    for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
+                    __syncwarp();
+                }
                 if constexpr (S::kSplit == 1) {
-                    gw_tc_generate<T, 0, T>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
+                    gw_tc_generate<T, 0, T>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes, tile);
                 } else {
                     constexpr int AH = (T + 1) / 2;
-                    if (half == 0) gw_tc_generate<T, 0, AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
-                    else gw_tc_generate<T, AH, T - AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes);
+                    if (half == 0) gw_tc_generate<T, 0, AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes, tile);
+                    else gw_tc_generate<T, AH, T - AH>(ci, slab, cbuf, mi, l, c, a_hi, a_bytes, tile);
                 }
             }
             const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
@@ -1251,7 +1264,7 @@ bool tc_gw_wanted(const cgb200_plan* p) {
 
 template <int T>
 static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
-                          int max_slices, int G, cudaStream_t st) {
+                          int max_slices, int G, const float2* ff, cudaStream_t st) {
     int n_max = 16;
     for (int v : p->tc_npad) n_max = std::max(n_max, v);
     const int n_tiles = (int)p->tc_gw_tiles.size() / 2;
@@ -1276,7 +1289,8 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
                                                                        slices > 1 ? gw_part : gW, G, n_max, p->max_n, p->d_status,
                                                                        n_stages, n_flush, p->d.w_len, wait_polls(p),
-                                                                       p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0);
+                                                                       p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0,
+                                                                       (T == 4 && p->gff_ok) ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
     launch_end(K_GW_TC, st);
     CGB_CUDA(cudaGetLastError());
     if (slices > 1) {
@@ -1287,9 +1301,9 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
 }
 
 int launch_gw_tc(const cgb200_plan* p, const float2* SF, const float2* SG, const float* inv, float2* gW, float2* gw_part,
-                 int max_slices, int G, cudaStream_t st) {
-    if (p->d.tile == 4) return launch_gw_tc_t<4>(p, SF, SG, inv, gW, gw_part, max_slices, G, st);
-    if (p->d.tile == 5) return launch_gw_tc_t<5>(p, SF, SG, inv, gW, gw_part, max_slices, G, st);
+                 int max_slices, int G, const float2* ff, cudaStream_t st) {
+    if (p->d.tile == 4) return launch_gw_tc_t<4>(p, SF, SG, inv, gW, gw_part, max_slices, G, ff, st);
+    if (p->d.tile == 5) return launch_gw_tc_t<5>(p, SF, SG, inv, gW, gw_part, max_slices, G, nullptr, st);
     set_error("internal: tensor-core weight gradient asked for an unsupported tile edge");
     return CGB200_ERR_UNSUPPORTED;
 }

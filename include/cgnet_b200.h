@@ -37,6 +37,11 @@ extern "C" {
 /* fragment-norm flags, same bit meaning as the reference's `bn_flags` (CGNet/CG_layers.py:22-33) */
 #define CGB200_FN_PRESENT       0x1 /* stds is valid: divide every mid channel by max(eps, stds[k])                */
 #define CGB200_FN_UPDATE        0x2 /* training: first fold this batch's statistics into stds, in place            */
+#define CGB200_FN_KEEP_MID      0x4 /* cgb200_layer_bwd only: the workspace is the one the matching cgb200_layer_fwd call
+                                       (same plan, same batch, CGB200_FN_UPDATE set) used, untouched since, and at least
+                                       cgb200_layer_workspace_bytes large: where cgb200_layer_keeps_mid says so, that forward
+                                       left the tiles of the mid activation in it and the weight gradient reads them
+                                       instead of generating them again.  Ignored where the forward keeps nothing.   */
 
 /* plan flags */
 #define CGB200_PLAN_DEPTHWISE   0x1 /* channel-wise product (t1 == t2 only; needs tau_l1 == tau_l2).  Not in the
@@ -187,6 +192,10 @@ int cgb200_layer_bwd(const cgb200_plan* plan, const float* F, const float* W, co
    at lmax 14 with 16 channels and 64 samples; above 16 GB the library goes back to rebuilding it tile by tile;
    CGB200_OPT_GRAD_MID_GEMM 0 does so always). */
 int64_t cgb200_layer_workspace_bytes(const cgb200_plan* plan, int64_t B);
+/* 1 if a cgb200_layer_fwd call with CGB200_FN_UPDATE for B samples leaves the mid activation's tiles at the start of its
+   workspace (tensor-core path, tile edge 4, see CGB200_OPT_FWD_KEEP_MID), so that cgb200_layer_bwd may be given the same
+   workspace with CGB200_FN_KEEP_MID; 0 otherwise. */
+int cgb200_layer_keeps_mid(const cgb200_plan* plan, int64_t B);
 /* Scratch bytes cgb200_layer_fwd alone needs (input slab, norm factors, row counters, packed tensor-core weights);
    never more than cgb200_layer_workspace_bytes.  Both depend on the plan's options at the time of the call. */
 int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* plan, int64_t B);

@@ -308,3 +308,53 @@ def test_forward_reads_back_the_tiles_the_statistics_kernel_kept(taus, tau_out, 
     assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
     assert_fragments_close(out[1][0], O_want, tau_out, "O (tiles kept by the statistics kernel) vs oracle")
     np.testing.assert_allclose(out[1][1], stds_want, rtol=2e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
+                                                 ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default"), ([6, 0, 8, 4], [8, 4, 0, 20], 4, "default")])
+def test_backward_reads_the_tiles_kept_in_the_forwards_workspace(taus, tau_out, B, mode):
+    """A forward with a statistics update leaves the mid activation's tiles at the start of its workspace; handed the same
+    workspace (CGB200_FN_KEEP_MID), the backward's weight gradient loads them instead of generating them again.  Same
+    generator, so the gradients are the same bits as those of a backward with a fresh workspace; both match the oracle."""
+    from cgnet_b200 import _lib, get_plan
+    import cg_oracle as o
+    dev = torch.device("cuda", 0)
+    case = make_case(taus, tau_out, B, mode, seed=63)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], dev, tile=4)
+    assert plan.keeps_mid(B)
+    F = torch.tensor(case["F"], device=dev)
+    W = torch.tensor(case["W"], device=dev)
+    gO = torch.tensor(case["gO"], device=dev)
+    stds = torch.tensor(case["stds"], device=dev)
+    O, ws = plan.layer_fwd(F, W, stds, 2.0, 1e-5, _lib.FN_PRESENT | _lib.FN_UPDATE, keep=True)
+    gF_k, gW_k = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT, gO, kept=ws)
+    gF_n, gW_n = plan.layer_bwd(F, W, stds, 1e-5, _lib.FN_PRESENT, gO)
+    plan.check_status()
+    assert torch.equal(gW_k, gW_n) and torch.equal(gF_k, gF_n)
+    O_want, gF_want, gW_want, _ = oracle_layer(case, True, True, cnt=2.0)
+    assert_fragments_close(O.cpu().numpy(), O_want, tau_out, "O")
+    assert_fragments_close(gF_k.cpu().numpy(), gF_want, taus, "gF with the kept workspace")
+    t_ff, _ = o.tau_ff_and_offsets(case["lmax"], case["taus"], case["llls"])
+    assert_weights_close(gW_k.cpu().numpy(), gW_want, t_ff, tau_out, "gW from the kept tiles")
+
+
+def test_module_keeps_the_workspace_between_forward_and_backward():
+    """CGBN_cuda in training: with keep_mid the layer's workspace travels from the forward to the backward; parameters'
+    and input's gradients are the same bits as without."""
+    from cgnet_b200 import CGBN_cuda
+    dev = torch.device("cuda", 0)
+    grads = {}
+    for keep in (False, True):
+        torch.manual_seed(5)
+        np.random.seed(5)
+        layer = CGBN_cuda(4, [16] * 5, [16] * 5, batchnorm=True, device=dev, keep_mid=keep).train()
+        assert layer.cg.plan.tile == 4
+        torch.manual_seed(6)
+        x = torch.randn(37, 16 * 25, 2, device=dev, requires_grad=True)
+        out = layer(x, straight_output=True)
+        assert layer._keeps_mid(37) == keep
+        (out * torch.linspace(-1, 1, out.numel(), device=dev).reshape(out.shape)).sum().backward()
+        grads[keep] = (x.grad.clone(), layer.bnWMM.W.grad.clone(), layer.bnWMM.bn_stds.detach().clone())
+        layer.cg.plan.check_status()
+    for a, b in zip(grads[False], grads[True]):
+        assert torch.equal(a, b)
