@@ -585,7 +585,7 @@ fused_gw_dw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, con
 //   phase 2  lets every warp own rows m_t of the fragment and gather, in registers,
 //            x[a] = sum C * conj(other[c][.]) * H[m][a, c]  over the band, adding x once to the block's accumulator.
 // This is CGNet/cudaCG/cudaCG_FNWMM.cu:169-211 followed by cudaCG_sparse.cu:231-289 with gFF living only as one tile
-// in shared memory.  Every sum has a fixed order; parts are added by gf_reduce_kernel in part order.
+// in shared memory.  Every sum has a fixed order; parts are added by parts_reduce_kernel in part order.
 // ---------------------------------------------------------------------------------------------------------------
 
 // phase 1 unit: H[m][K0 .. K0+KN) = sum_to wt[to][k] * gO[to, m]
