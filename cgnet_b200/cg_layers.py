@@ -191,21 +191,25 @@ class Plan(PlanShapes):
                        "cgb200_fn_wmm_bwd")
         return gFF, gW
 
-    def _workspace_bytes(self, B, fwd_only=False):
-        # the size depends on the batch and on the plan's options only: asked once per (batch, kind), forgotten when an
-        # option changes (set_option)
-        key = (B, fwd_only)
+    def _workspace_bytes(self, B, fwd_flags=None):
+        """Workspace of the backward (``fwd_flags=None``: it also serves any forward) or of a forward with these flags.
+        The size depends on the batch, the flags and the plan's options only: asked once per combination, forgotten when
+        an option changes (``set_option``)."""
+        key = (B, None if fwd_flags is None else fwd_flags & (_lib.FN_PRESENT | _lib.FN_UPDATE))
         n = self._ws_bytes.get(key)
         if n is None:
             lib = _lib.load()
-            n = int((lib.cgb200_layer_fwd_workspace_bytes if fwd_only else lib.cgb200_layer_workspace_bytes)(self.handle, B))
+            if fwd_flags is None:
+                n = int(lib.cgb200_layer_workspace_bytes(self.handle, B))
+            else:
+                n = int(lib.cgb200_layer_fwd_workspace_bytes_for(self.handle, B, int(fwd_flags)))
             if n < 0:
                 _lib.check(1, "cgb200_layer_workspace_bytes")
             self._ws_bytes[key] = n
         return n
 
-    def _workspace(self, B, fwd_only=False):
-        n = self._workspace_bytes(B, fwd_only)
+    def _workspace(self, B, fwd_flags=None):
+        n = self._workspace_bytes(B, fwd_flags)
         return torch.empty(max(n, 256), dtype=torch.uint8, device=self.device), n
 
     def _call(self, fn, name, *args):
@@ -236,7 +240,7 @@ class Plan(PlanShapes):
         self.check_batch(B, F=(F, self.n_F))
         self.check_weights(W, stds, flags)
         O = torch.empty(B, self.n_O, 2, device=self.device, dtype=torch.float32)
-        ws, n = self._workspace(B, fwd_only=not keep)
+        ws, n = self._workspace(B, None if keep else flags)
         self._call(self._fn_layer_fwd, "cgb200_layer_fwd", F.data_ptr(), W.data_ptr(), _ptr(stds), cnt, eps, flags, O.data_ptr(),
                    B, ws.data_ptr(), n)
         return (O, ws) if keep else O

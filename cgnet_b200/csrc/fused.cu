@@ -950,15 +950,19 @@ bool ff_store_wanted(const cgb200_plan* p, int64_t G) {
 // (tensor-core forward) the packed weights; the backward adds the slab of the output gradient and the partial sums.
 // Both layouts start at the same base and nothing in the workspace survives a call, so a buffer sized for the larger
 // one serves both.
-Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = false) {
+// `mode`: the backward (which also covers everything a forward needs), a forward with a statistics update, or a forward
+// without one (no room for kept tiles).
+enum { kWsBwd = 0, kWsFwdTrain = 1, kWsFwdInfer = 2 };
+Workspace carve(const cgb200_plan* p, int64_t B, void* base, int mode = kWsBwd) {
     const int64_t G = (B + 31) / 32;
+    const bool fwd_only = mode != kWsBwd;
     Workspace w{};
     int64_t off = 0;
     char* c = (char*)base;
     // first, at the same place in the forward's and the backward's layout: the tiles a forward with a statistics update
     // keeps (a backward given the same workspace with CGB200_FN_KEEP_MID reads them)
     w.ff = nullptr;
-    if (ff_store_wanted(p, G)) {
+    if (mode != kWsFwdInfer && ff_store_wanted(p, G)) {
         w.ff = (float2*)(c + off);
         off += align256(gff_group_elems(p) * G * 32 * (int64_t)sizeof(float2));
     }
@@ -995,7 +999,7 @@ Workspace carve(const cgb200_plan* p, int64_t B, void* base, bool fwd_only = fal
     return w;
 }
 
-int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_bytes, bool fwd_only) {
+int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_bytes, int mode) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(p->d.has_out, "the plan was created without tau_out");
     CGB_REQUIRE(B >= 0 && B <= 65535 * 32, "batch size out of range (at most 2097120 samples per call of the fused layer)");
@@ -1003,7 +1007,7 @@ int check_layer(const cgb200_plan* p, int64_t B, const void* ws, int64_t ws_byte
     CGB_CUDA(cudaGetDevice(&dev));
     CGB_REQUIRE(dev == p->device, "the plan belongs to another CUDA device than the current one");
     if (B > 0) {
-        const int64_t need = carve(p, B, nullptr, fwd_only).bytes;
+        const int64_t need = carve(p, B, nullptr, mode).bytes;
         if (ws == nullptr || ws_bytes < need) {
             set_error("workspace too small: need " + std::to_string(need) + " bytes");
             return CGB200_ERR_WORKSPACE;
@@ -1066,27 +1070,37 @@ int cgb200_layer_keeps_mid(const cgb200_plan* p, int64_t B) {
     return ff_store_wanted(p, (B + 31) / 32) && !split_rows && p->d.tile == 4 ? 1 : 0;
 }
 
+int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* p, int64_t B, int flags) {
+    if (p == nullptr || B < 0) {
+        set_error("null plan or negative batch");
+        return -1;
+    }
+    const bool update = (flags & CGB200_FN_PRESENT) && (flags & CGB200_FN_UPDATE);
+    return carve(p, std::max<int64_t>(B, 1), nullptr, update ? kWsFwdTrain : kWsFwdInfer).bytes;
+}
+
 int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* p, int64_t B) {
     if (p == nullptr || B < 0) {
         set_error("null plan or negative batch");
         return -1;
     }
-    return carve(p, std::max<int64_t>(B, 1), nullptr, true).bytes;
+    return carve(p, std::max<int64_t>(B, 1), nullptr, kWsFwdTrain).bytes;
 }
 
 int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float* stds, float cnt, float eps, int flags,
                      float* O, int64_t B, void* workspace, int64_t workspace_bytes, void* stream) {
-    int rc = check_layer(p, B, workspace, workspace_bytes, true);
-    if (rc) return rc;
     const bool fn = (flags & CGB200_FN_PRESENT) != 0;
     const bool update = fn && (flags & CGB200_FN_UPDATE);
+    const int ws_mode = update ? kWsFwdTrain : kWsFwdInfer;
+    int rc = check_layer(p, B, workspace, workspace_bytes, ws_mode);
+    if (rc) return rc;
     CGB_REQUIRE(!fn || stds != nullptr, "stds is null although CGB200_FN_PRESENT is set");
     if (B == 0 || p->d.n_O == 0) return CGB200_OK;
     CGB_REQUIRE(F != nullptr && O != nullptr && (W != nullptr || p->d.w_len == 0), "null buffer");
     CGB_REQUIRE(al8(F) && al8(W) && al8(O), "buffers must be 8-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     const int G = (int)((B + 31) / 32);
-    Workspace ws = carve(p, B, workspace, true);
+    Workspace ws = carve(p, B, workspace, ws_mode);
     const int T = p->d.tile;
 
     PrepJob jf{(const float2*)F, ws.SF, p->d.n_F, p->d.cumF, p->d.cumSF, p->d.tF, p->d.nSF, has_pad(p->tF, T) ? 1 : 0};
@@ -1157,7 +1171,7 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
 int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const float* stds, float eps, int flags,
                      const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,
                      void* stream) {
-    int rc = check_layer(p, B, workspace, workspace_bytes, false);
+    int rc = check_layer(p, B, workspace, workspace_bytes, kWsBwd);
     if (rc) return rc;
     const bool fn = (flags & CGB200_FN_PRESENT) != 0;
     CGB_REQUIRE(!fn || stds != nullptr, "stds is null although CGB200_FN_PRESENT is set");
@@ -1332,7 +1346,7 @@ int cgb200_layer_fwd_static(const cgb200_plan* p, const float* F, const float* W
                             int flags, float* O, int64_t B, void* stream) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(B >= 0, "negative batch size");
-    const int64_t need = cgb200_layer_fwd_workspace_bytes(p, B);   // the forward's own need, not the backward's
+    const int64_t need = cgb200_layer_fwd_workspace_bytes_for(p, B, flags);   // this forward's own need, not the backward's
     if (need < 0) return CGB200_ERR_ARGUMENT;
     if (need > (int64_t)CGB200_STATIC_SCRATCH_BYTES) {
         set_error("cgb200_layer_fwd_static: the forward of this plan and batch needs " + std::to_string(need) +

@@ -199,6 +199,9 @@ int cgb200_layer_keeps_mid(const cgb200_plan* plan, int64_t B);
 /* Scratch bytes cgb200_layer_fwd alone needs (input slab, norm factors, row counters, packed tensor-core weights);
    never more than cgb200_layer_workspace_bytes.  Both depend on the plan's options at the time of the call. */
 int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* plan, int64_t B);
+/* The same for a call with these flags: a forward without CGB200_FN_UPDATE keeps no tiles and needs no room for them
+   (gigabytes less for the wide layers).  cgb200_layer_fwd accepts a workspace of this size for such a call. */
+int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* plan, int64_t B, int flags);
 
 /*
  * cgb200_layer_fwd for callers that cannot allocate device memory (no counterpart in the reference, whose Python
