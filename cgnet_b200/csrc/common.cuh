@@ -279,7 +279,8 @@ struct cgb200_plan {
     // mid-activation gradient as a tensor-core GEMM (tile edge 4, full product): per degree the offset of its packed
     // weights (floats) and of its tiles inside one sample group of the gradient workspace (units of 32 lanes of float2;
     // the tile of a degree's cell k starts at offset + k (2l+1) T^2)
-    bool gff_ok = false;
+    bool gff_ok = false;     // the mid-gradient GEMM's tables exist (tile edge 4, tensor-core tables)
+    bool tiles_ok = false;   // gff_off exists: the mid activation can be kept as tiles (full product, any tile edge)
     std::vector<int64_t> gff_pack_off, gff_off;   // [lmax+2]
     const int64_t* d_gff_pack_off = nullptr;
     const int64_t* d_gff_off = nullptr;

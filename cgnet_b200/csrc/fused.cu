@@ -144,9 +144,9 @@ __device__ __forceinline__ void stats_body(const PlanDev& P, const CellRec& cell
         float2 v[NE];
         if constexpr (!DW && IN < T) gen_slab_rows<T, I0, IN>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
         else gen_slab<T, DW, true>(v, C + mi * n2, slab + o1 * 32, slab + o2 * 32, mi - tr.l, tr.l1, tr.l2);
-        if constexpr (!DW && IN == T) {
-            if (ff_tile != nullptr) {   // keep the tile for the tensor-core forward: [group][cell][m][entry][lane]
-                float2* dst = ff_tile + ((int64_t)g * ff_stride + (int64_t)mi * NE) * 32 + lane;
+        if constexpr (!DW) {
+            if (ff_tile != nullptr) {   // keep the tile for the forward that follows: [group][cell][m][entry][lane]
+                float2* dst = ff_tile + ((int64_t)g * ff_stride + (int64_t)mi * (T * T) + E0) * 32 + lane;
 #pragma unroll
                 for (int i = 0; i < NE; ++i) dst[i * 32] = v[i];
             }
@@ -201,14 +201,14 @@ fused_stats_kernel(PlanDev P, const float2* __restrict__ SF, float* __restrict__
     const int n = 2 * tr.l + 1, n2 = 2 * tr.l2 + 1;
     for (int i = threadIdx.x; i < n * n2; i += 256) sband[i] = P.cg[tr.cgoff + i];
     __syncthreads();
+    // ff: the generated tiles are also written out (full product), so that the forward that follows reads them back
+    // instead of generating them again
+    float2* tile = (DW || ff == nullptr || P.tO[tr.l] == 0) ? nullptr : ff + (ff_off[tr.l] + (int64_t)(cidx - P.cell_begin[tr.l]) * n * TileShape<T, DW>::NV) * 32;
     if constexpr (SPLIT && !DW && T > 1) {
         constexpr int AH = (T + 1) / 2;
-        if ((blockIdx.x & 1) == 0) stats_body<T, DW, 0, AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
-        else stats_body<T, DW, AH, T - AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red);
+        if ((blockIdx.x & 1) == 0) stats_body<T, DW, 0, AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red, tile, ff_stride);
+        else stats_body<T, DW, AH, T - AH>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red, tile, ff_stride);
     } else {
-        // ff: the generated tiles are also written out (tile edge 4, full product), so that the tensor-core forward that
-        // follows reads them back instead of generating them again
-        float2* tile = (ff == nullptr || P.tO[tr.l] == 0) ? nullptr : ff + (ff_off[tr.l] + (int64_t)(cidx - P.cell_begin[tr.l]) * n * TileShape<T, DW>::NV) * 32;
         stats_body<T, DW, 0, T>(P, cell, tr, SF, stds, inv, cnt, eps, B, G, sband, red, tile, ff_stride);
     }
 }
@@ -227,10 +227,13 @@ __host__ __device__ inline int fwd_stage_half_bytes(int step, int nv, int max_n)
 }
 __host__ __device__ inline int fwd_stage_bytes(int step, int nv, int max_n) { return 2 * fwd_stage_half_bytes(step, nv, max_n); }
 
+// (`tiles`: this lane's view of the group's kept tiles, written by the statistics kernel of the same call, or null;
+// their values are what gen_slab would produce, bit for bit.)
 template <int T, bool DW, int NW, int NTO>
 __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restrict__ slab, const float2* __restrict__ W,
                                         const float* __restrict__ inv, float2* __restrict__ O, float2* __restrict__ red,
-                                        unsigned char* __restrict__ stage, int l, int mi, int b, int B, int warp, int lane) {
+                                        unsigned char* __restrict__ stage, int l, int mi, int b, int B, int warp, int lane,
+                                        const float2* __restrict__ tiles, const int64_t* __restrict__ ff_off) {
     constexpr int NV = TileShape<T, DW>::NV;
     const int n = 2 * l + 1;
     const int to_n = P.tO[l];
@@ -287,7 +290,13 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
             const float* ibuf = reinterpret_cast<const float*>(wbuf + step * NV);
             const float* cbuf = ibuf + NV;
             float2 v[NV];
-            gen_slab<T, DW>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+            if (!DW && tiles != nullptr) {
+                const float2* src = tiles + (ff_off[l] + ((int64_t)(c - c_begin) * n + mi) * NV) * 32;
+#pragma unroll
+                for (int idx = 0; idx < NV; ++idx) v[idx] = src[idx * 32];
+            } else {
+                gen_slab<T, DW>(v, cbuf, slab + ci.o1 * 32, slab + ci.o2 * 32, mi - l, ci.l1, ci.l2);
+            }
 #pragma unroll
             for (int idx = 0; idx < NV; ++idx) {
                 const float sc = ibuf[idx];
@@ -321,7 +330,8 @@ __device__ __forceinline__ void fwd_row(const PlanDev& P, const float2* __restri
 template <int T, bool DW, int NTO>
 __global__ void __launch_bounds__(kFwdWarps * kWarp)
 fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restrict__ SF, const float2* __restrict__ W,
-                 const float* __restrict__ inv, float2* __restrict__ O, int B, int stage_bytes) {
+                 const float* __restrict__ inv, float2* __restrict__ O, int B, int stage_bytes, const float2* __restrict__ ff,
+                 int64_t ff_stride, const int64_t* __restrict__ ff_off) {
     constexpr int red_to = NTO;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float2* red = reinterpret_cast<float2*>(smem_raw);
@@ -330,7 +340,7 @@ fused_fwd_kernel(PlanDev P, const int* __restrict__ rows, const float2* __restri
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* stage = smem_raw + (size_t)kFwdWarps * red_to * 32 * sizeof(float2) + (size_t)warp * stage_bytes;
     fwd_row<T, DW, kFwdWarps, NTO>(P, SF + (int64_t)g * P.nSF * 32 + lane, W, inv, O, red, stage, l, mi, g * 32 + lane, B, warp,
-                                   lane);
+                                   lane, ff == nullptr ? nullptr : ff + (int64_t)g * ff_stride * 32 + lane, ff_off);
 }
 
 // persistent blocks: block (p, g) copies group g's slab into shared memory once, then pulls rows (most expensive
@@ -339,7 +349,8 @@ template <int T, bool DW, int NTO>
 __global__ void __launch_bounds__(kSlabWarps * kWarp)
 fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const float2* __restrict__ SF,
                       const float2* __restrict__ W, const float* __restrict__ inv, float2* __restrict__ O, int B,
-                      int* __restrict__ counters, int stage_bytes) {
+                      int* __restrict__ counters, int stage_bytes, const float2* __restrict__ ff, int64_t ff_stride,
+                      const int64_t* __restrict__ ff_off) {
     constexpr int red_to = NTO;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int next_row;
@@ -361,7 +372,7 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
         const int r = next_row;
         if (r >= n_rows) break;
         fwd_row<T, DW, kSlabWarps, NTO>(P, slab + lane, W, inv, O, red, stage, rows[2 * r], rows[2 * r + 1], g * 32 + lane, B, warp,
-                                        lane);
+                                        lane, ff == nullptr ? nullptr : ff + (int64_t)g * ff_stride * 32 + lane, ff_off);
     }
 }
 
@@ -930,20 +941,19 @@ bool gff_wanted(const cgb200_plan* p, int64_t G) {
     return p->max_tau_out >= 12 && bytes <= 16.0 * (1ull << 30);
 }
 
-// Forward with a statistics update on the tensor-core path: the statistics kernel generates every tile of the mid
-// activation anyway; it then also writes them to the workspace and the forward kernel's generator warps load their
-// tile instead of generating it a second time (same bits: both run the same generator).  Tile edge 4, full product,
-// same workspace limit as the mid-gradient GEMM; CGB200_OPT_FWD_KEEP_MID overrides.  The workspace of the forward is sized
-// for it whenever the variant is possible, also for calls without an update (which do not use it).
+// Forward with a statistics update: the statistics kernel generates every tile of the mid activation anyway; it then
+// also writes them to the workspace and the forward kernel loads its tile instead of generating it a second time (same
+// bits: both run the same generator).  Full product; on the tensor-core path tile edge 4 (not the staged variants), on
+// the CUDA-core path tile edges 4 and up (below that generating a tile costs less than fetching it); at most 16 GB;
+// CGB200_OPT_FWD_KEEP_MID overrides.
 bool ff_store_wanted(const cgb200_plan* p, int64_t G) {
-    if (!p->gff_ok || p->d.depthwise || !tc_wanted(p) || p->opt[CGB200_OPT_TC_STAGED] >= 1) return false;
+    if (!p->tiles_ok || p->d.depthwise) return false;
+    if (tc_wanted(p) && (p->d.tile != 4 || p->opt[CGB200_OPT_TC_STAGED] >= 1)) return false;
     const int opt = p->opt[CGB200_OPT_FWD_KEEP_MID];
     if (opt == 0) return false;
     if (opt == 1) return true;
-    const int so = p->opt[CGB200_OPT_STATS_SPLIT];
-    if (so == 1) return false;
     const double bytes = (double)gff_group_elems(p) * (double)G * 32 * sizeof(float2);
-    return bytes <= 16.0 * (1ull << 30);
+    return p->d.tile >= 4 && bytes <= 16.0 * (1ull << 30);
 }
 
 // Layout of the caller's workspace.  The forward needs only the input slab, the norm factors, the row counters and
@@ -1065,9 +1075,8 @@ int64_t cgb200_layer_workspace_bytes(const cgb200_plan* p, int64_t B) {
 
 int cgb200_layer_keeps_mid(const cgb200_plan* p, int64_t B) {
     if (p == nullptr || B <= 0) return 0;
-    const int so = p->opt[CGB200_OPT_STATS_SPLIT];
-    const bool split_rows = !p->d.depthwise && (so >= 0 ? so != 0 : p->d.tile >= 5);
-    return ff_store_wanted(p, (B + 31) / 32) && !split_rows && p->d.tile == 4 ? 1 : 0;
+    // the reader in the backward is the tensor-core weight gradient at tile edge 4
+    return ff_store_wanted(p, (B + 31) / 32) && p->d.tile == 4 && tc_gw_wanted(p) ? 1 : 0;
 }
 
 int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* p, int64_t B, int flags) {
@@ -1119,9 +1128,9 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
             auto kern = split_rows ? fused_stats_kernel<TT, DD, true> : fused_stats_kernel<TT, DD, false>;
             if (band > 40 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)band));
             kern<<<p->d.n_cells * (split_rows ? 2 : 1), 256, band, st>>>(p->d, ws.SF, stds, ws.inv, cnt, eps, (int)B, G,
-                                                                        split_rows ? nullptr : ws.ff, gff_group_elems(p), p->d_gff_off);
+                                                                        ws.ff, gff_group_elems(p), p->d_gff_off);
         });
-        ff_stored = ws.ff != nullptr && !split_rows;
+        ff_stored = ws.ff != nullptr;
         launch_end(K_STATS, st);
         CGB_CUDA(cudaGetLastError());
     }
@@ -1153,14 +1162,16 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
             auto kern = fused_fwd_slab_kernel<TT, DD, NN>;
             CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_slab));
             kern<<<dim3(per_group, G), kSlabWarps * kWarp, smem_slab, st>>>(p->d, p->d_fwd_rows, n_rows, ws.SF, (const float2*)W,
-                                                                         ws.inv, (float2*)O, (int)B, ws.counters, stage_bytes);
+                                                                         ws.inv, (float2*)O, (int)B, ws.counters, stage_bytes,
+                                                                         ff_stored ? ws.ff : nullptr, gff_group_elems(p), p->d_gff_off);
         }));
     } else {
         CGB_DISPATCH_TILE(T, p->d.depthwise, CGB_DISPATCH_NTO(red_to, {
             auto kern = fused_fwd_kernel<TT, DD, NN>;
             if (smem_rows > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows));
             kern<<<dim3(n_rows, G), kFwdWarps * kWarp, smem_rows, st>>>(p->d, p->d_fwd_rows, ws.SF, (const float2*)W, ws.inv, (float2*)O,
-                                                                     (int)B, stage_bytes);
+                                                                     (int)B, stage_bytes, ff_stored ? ws.ff : nullptr,
+                                                                     gff_group_elems(p), p->d_gff_off);
         }));
     }
     launch_end(K_FWD, st);

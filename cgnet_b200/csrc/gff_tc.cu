@@ -247,7 +247,7 @@ gff_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int64_t* __restric
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 int64_t gff_pack_floats(const cgb200_plan* p) { return p->gff_ok ? p->gff_pack_off.back() : 0; }
-int64_t gff_group_elems(const cgb200_plan* p) { return p->gff_ok ? p->gff_off.back() : 0; }
+int64_t gff_group_elems(const cgb200_plan* p) { return p->tiles_ok ? p->gff_off.back() : 0; }
 
 int launch_gff_tc(const cgb200_plan* p, int lv, const float2* SG, const float2* W, const float* inv, float* pack, float2* gff,
                   int G, cudaStream_t st) {

@@ -477,13 +477,14 @@ int cgb200_plan_create(cgb200_plan** out, int lmax, const int32_t* tau_in, const
         }
     }
     p->gff_ok = p->tc_ok && T == 4;
-    if (p->gff_ok) {
+    p->tiles_ok = !dw && has_out;
+    if (p->tiles_ok) {
         p->gff_pack_off.assign(L1 + 1, 0);
         p->gff_off.assign(L1 + 1, 0);
         for (int l = 0; l < L1; ++l) {
             const int64_t ncell = p->cell_begin[l + 1] - p->cell_begin[l];
             const int Kb = (2 * p->tO[l] + 7) & ~7;
-            p->gff_pack_off[l + 1] = p->gff_pack_off[l] + ncell * 64 * Kb;
+            p->gff_pack_off[l + 1] = p->gff_pack_off[l] + (p->gff_ok ? ncell * 64 * Kb : 0);
             p->gff_off[l + 1] = p->gff_off[l] + (p->tO[l] > 0 ? ncell * (2 * l + 1) * T * T : 0);
         }
         if ((rc = upload(p, p->gff_pack_off, &p->d_gff_pack_off))) return rc;
@@ -793,7 +794,8 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
         if (option == CGB200_OPT_TC_FWD) have = p->tc_ok;
         if (option == CGB200_OPT_TC_GRAD_W) have = p->tc_gw_ok && !p->tc_gw_tiles.empty();
         if (option == CGB200_OPT_TC_GRAD_F) have = p->tc_ok && p->d.tile == 4 && p->max_n <= 64;
-        if (option == CGB200_OPT_GRAD_MID_GEMM || option == CGB200_OPT_FWD_KEEP_MID) have = p->gff_ok;
+        if (option == CGB200_OPT_GRAD_MID_GEMM) have = p->gff_ok;
+        if (option == CGB200_OPT_FWD_KEEP_MID) have = p->tiles_ok;
         if (needs_tables && !have) {
             set_error("this plan has no tables for the requested tensor-core variant (tile edge, depthwise product or channel counts)");
             return CGB200_ERR_UNSUPPORTED;

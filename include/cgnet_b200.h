@@ -212,7 +212,7 @@ int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* plan, int64_t B,
  * cudaMalloc after start-up because it stalls the device.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - Returns CGB200_ERR_WORKSPACE, with the needed and available byte counts in cgb200_last_error(), when
- *     cgb200_layer_fwd_workspace_bytes(plan, B) exceeds the array.
+ *     cgb200_layer_fwd_workspace_bytes_for(plan, B, flags) exceeds the array.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress with that device current);
  *     make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps whatever the last call left in it.  The call itself

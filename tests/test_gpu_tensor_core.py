@@ -358,3 +358,22 @@ def test_module_keeps_the_workspace_between_forward_and_backward():
         layer.cg.plan.check_status()
     for a, b in zip(grads[False], grads[True]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("taus,tau_out,B,mode", [([5] * 6, [5] * 6, 37, "default"), ([8] * 4, [8] * 4, 40, "default"),
+                                                 ([6, 0, 3, 5], [2, 7, 0, 3], 4, "default"), ([10] * 5, [5] * 5, 70, "mst")])
+def test_cuda_core_forward_reads_back_the_kept_tiles(taus, tau_out, B, mode):
+    """The same on the CUDA-core forward (under 12 output channels: the benchmark network's layers; the statistics kernel
+    of tile edges 5 and 6 stores its tile in two halves): identical bits with the variant on and off, and the oracle's
+    values."""
+    from cgnet_b200 import _lib, get_plan
+    case = make_case(taus, tau_out, B, mode, seed=64)
+    plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0))
+    O_want, _, _, stds_want = oracle_layer(case, True, True, cnt=2.0)
+    out = {}
+    for keep in (0, 1):   # forced on also where the default leaves it off (tile edge 3 in the ragged case)
+        with option(plan, _lib.OPT_FWD_KEEP_MID, keep):
+            out[keep] = _forward(plan, case, True, True, tc=False)
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+    assert_fragments_close(out[1][0], O_want, tau_out, "O (CUDA-core forward, kept tiles) vs oracle")
+    np.testing.assert_allclose(out[1][1], stds_want, rtol=2e-5, atol=1e-7)
