@@ -86,7 +86,9 @@ tc_pack_kernel(PlanDev P, const int* __restrict__ npad, const int64_t* __restric
 // then one CG band row per generator warp.
 // ---------------------------------------------------------------------------------------------------------------
 
-template <int T>
+// KEPT: the generator warps load the tiles the statistics kernel of the same call kept (`ff`) instead of generating them
+// (a separate instantiation, so that the generating kernel's register allocation is not touched by the extra path).
+template <int T, bool KEPT>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const int64_t* __restrict__ pack_off,
                     const float2* __restrict__ SF, const float* __restrict__ pack, float2* __restrict__ O,
@@ -163,7 +165,7 @@ fused_fwd_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restr
                 bulk_g2s(b_st, pack + pack_off[l] + (int64_t)(k0 + k) * 2 * N * Kc, b_bytes, &full_bar[s]);
             }
             float2 v[NV];
-            if (live_m && ff != nullptr) {
+            if (KEPT && live_m) {
                 // the statistics kernel of this call generated the tile already and kept it: [group][cell][m][entry][lane]
                 const float2* src = ff + ((int64_t)g * ff_stride + ff_off[l] + ((int64_t)(k0 + k) * n + mi) * NV) * 32 + lane;
 #pragma unroll
@@ -635,7 +637,7 @@ __device__ __forceinline__ void gw_tc_generate(const CellInfo& ci, const float2*
 
 // grid = (blocks of cells, slices of the sample groups); slice s handles the groups s, s + slices, ... and, with more
 // than one slice, writes its partial sums to gW + s * slice_stride for gw_reduce_kernel
-template <int T>
+template <int T, bool KEPT>
 __global__ void __launch_bounds__(kTcMaxThreads)
 fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restrict__ npad, const float2* __restrict__ SF,
                    const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G, int n_max,
@@ -709,8 +711,8 @@ fused_gw_tc_kernel(PlanDev P, const int* __restrict__ tiles, const int* __restri
             if (live) {
                 const float2* slab = SF + (int64_t)g * P.nSF * 32 + lane;
                 // the tiles the forward kept (same generator, same bits), or the band row to generate them again
-                const float2* tile = ff == nullptr ? nullptr
-                                                   : ff + ((int64_t)g * ff_stride + ff_off[l] + ((int64_t)cell * n + mi) * S::NV) * 32 + lane;
+                const float2* tile = !KEPT ? nullptr
+                                           : ff + ((int64_t)g * ff_stride + ff_off[l] + ((int64_t)cell * n + mi) * S::NV) * 32 + lane;
                 if (tile == nullptr) {
                     __syncwarp();
                     for (int e = lane; e < n2; e += 32) cbuf[e] = __ldg(P.cg + ci.cgoff + mi * n2 + e);
@@ -1225,13 +1227,14 @@ static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float
         set_error("tensor-core forward: pipeline stages do not fit in shared memory");
         return CGB200_ERR_UNSUPPORTED;
     }
-    auto kern = fused_fwd_tc_kernel<T>;
+    const bool kept = T == 4 && ff != nullptr;
+    auto kern = kept ? fused_fwd_tc_kernel<T, true> : fused_fwd_tc_kernel<T, false>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_FWD_TC, st);
     const int64_t part_stride = (int64_t)B * p->d.n_O;
     kern<<<dim3((unsigned)p->tc_tiles[lv].size() / 4, G), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(
         p->d, p->d_tc_tiles[lv], p->d_tc_npad, p->d_tc_pack_off, SF, pack, O, O_part, part_stride, B, n_max, p->max_n, p->d_status,
-        n_stages, n_flush, wait_polls(p), idle, T == 4 ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
+        n_stages, n_flush, wait_polls(p), idle, kept ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
     launch_end(K_FWD_TC, st);
     CGB_CUDA(cudaGetLastError());
     if (p->tc_max_parts[lv] > 1) {
@@ -1283,14 +1286,15 @@ static int launch_gw_tc_t(const cgb200_plan* p, const float2* SF, const float2* 
     slices = std::max(1, std::min(slices, 65535));
     if (gw_part == nullptr) slices = 1;
     const size_t smem = n_stages * stage_bytes + cbuf_bytes;
-    auto kern = fused_gw_tc_kernel<T>;
+    const bool kept = T == 4 && p->gff_ok && ff != nullptr;
+    auto kern = kept ? fused_gw_tc_kernel<T, true> : fused_gw_tc_kernel<T, false>;
     CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_begin(K_GW_TC, st);
     kern<<<dim3(n_tiles, slices), 32 * (4 * n_stages + 1 + 4 * n_flush), smem, st>>>(p->d, p->d_tc_gw_tiles, p->d_tc_npad, SF, SG, inv,
                                                                        slices > 1 ? gw_part : gW, G, n_max, p->max_n, p->d_status,
                                                                        n_stages, n_flush, p->d.w_len, wait_polls(p),
                                                                        p->opt[CGB200_OPT_TEST_IDLE_MMA] == 1 ? 1 : 0,
-                                                                       (T == 4 && p->gff_ok) ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
+                                                                       kept ? ff : nullptr, gff_group_elems(p), p->d_gff_off);
     launch_end(K_GW_TC, st);
     CGB_CUDA(cudaGetLastError());
     if (slices > 1) {
