@@ -19,7 +19,7 @@ Differences from the reference, all additive:
     a resume silently resets, ``CG_layers.py:92``); checkpoints without it still load;
   * ``depthwise=True`` (channel-wise product, tau_l1 == tau_l2 required) is an extension with no reference counterpart;
   * ``keep_mid`` (``CGBN_cuda``): wide layers in training keep their workspace, with the mid activation's tiles in it, from
-    the forward to the backward (default: while it stays under a sixteenth of the device's memory);
+    the forward to the backward (default: while the workspaces kept on the device stay under a quarter of its memory);
   * gradients of ``W`` are summed in a fixed order (the reference accumulates them with ``atomicAdd``).
 """
 import functools
@@ -360,6 +360,21 @@ class _MyBatchNormWeightMM_cuda(torch.autograd.Function):
         return gFF, gW, None, None, None, None, None
 
 
+# bytes of layer workspaces currently kept for a backward, per device, and the devices' memory sizes
+_kept_bytes = {}
+_device_bytes = {}
+
+
+def _note_kept(ws):
+    """Account for a kept workspace until its tensor is released (after the backward, or when the graph is dropped)."""
+    dev, n = ws.device, ws.numel()
+    _kept_bytes[dev] = _kept_bytes.get(dev, 0) + n
+
+    def release():
+        _kept_bytes[dev] = _kept_bytes.get(dev, 0) - n
+    weakref.finalize(ws, release)
+
+
 class _CGBN_fused(torch.autograd.Function):
     """Whole layer through the fused kernels: the mid activation is regenerated in the backward, never stored."""
 
@@ -371,6 +386,7 @@ class _CGBN_fused(torch.autograd.Function):
         ctx.kept = None
         if keep_mid and (flags & _lib.FN_UPDATE) and plan.keeps_mid(Fs.shape[0]):
             out, ctx.kept = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags, keep=True)
+            _note_kept(ctx.kept)
         else:
             out = plan.layer_fwd(Fs, W, bn_stds, float(bn_cnt), float(bn_eps), flags)
         ctx.plan, ctx.eps, ctx.flags = plan, float(bn_eps), flags & _lib.FN_PRESENT
@@ -583,8 +599,9 @@ class CGBN_cuda(nn.Module):
     def _keeps_mid(self, B):
         """Keep the layer's workspace from the forward to the backward, so that the weight gradient reads the mid
         activation's tiles the forward left in it instead of generating them again (wide layers on the tensor-core path
-        only: ``Plan.keeps_mid``)?  ``keep_mid=True`` / ``False`` decide; the default keeps while one layer's workspace stays
-        under a sixteenth of the device's memory (it is held until the layer's backward has run)."""
+        only: ``Plan.keeps_mid``)?  ``keep_mid=True`` / ``False`` decide; the default keeps while the workspaces kept on the
+        device at that moment (by all layers: each is held until its layer's backward has run), this one included, stay
+        under a quarter of the device's memory."""
         if self.keep_mid is False:
             return False
         plan = self.cg.plan
@@ -592,11 +609,10 @@ class CGBN_cuda(nn.Module):
             return False
         if self.keep_mid:
             return True
-        if CGBN_cuda._device_bytes.get(plan.device) is None:
-            CGBN_cuda._device_bytes[plan.device] = torch.cuda.get_device_properties(plan.device).total_memory
-        return plan._workspace_bytes(B) * 16 <= CGBN_cuda._device_bytes[plan.device]
-
-    _device_bytes = {}
+        dev = plan.device
+        if dev not in _device_bytes:
+            _device_bytes[dev] = torch.cuda.get_device_properties(dev).total_memory
+        return (_kept_bytes.get(dev, 0) + plan._workspace_bytes(B)) * 4 <= _device_bytes[dev]
 
     def forward(self, fs, straight_output=False):
         bn = self.bnWMM
