@@ -58,7 +58,7 @@ PLAN_DEPTHWISE = 0x1
 AUTO = -1
 (OPT_TC_FWD, OPT_TC_GRAD_W, OPT_TC_GRAD_F, OPT_TC_STAGES, OPT_FWD_SLAB, OPT_GRAD_F_SPLIT, OPT_STATS_SPLIT, OPT_BWD_SERIAL,
  OPT_WAIT_POLLS, OPT_TEST_IDLE_MMA, OPT_TC_STAGED, OPT_TC_ABUF, OPT_TC_FWD_SPLIT, OPT_GRAD_MID_GEMM,
- OPT_FWD_KEEP_MID) = range(15)
+ OPT_FWD_KEEP_MID, OPT_SHORT_GROUP) = range(16)
 
 
 def plan_tile_flag(tile):

@@ -383,10 +383,14 @@ fused_fwd_slab_kernel(PlanDev P, const int* __restrict__ rows, int n_rows, const
 // and the cheap tasks fill the tail.
 // ---------------------------------------------------------------------------------------------------------------
 // One task of the weight-gradient kernel with exactly I rows of t1.
+// `last_rep` > 1: the last sample group holds at most 32 / last_rep samples.  Its lanes are then (sample, j) pairs,
+// sample = lane % (32 / last_rep), and lane group j takes the values m2 = -l2 + j, -l2 + j + last_rep, ... of the outer
+// loop instead of every lane walking all of them for an empty sample slot: the group costs 1 / last_rep of a full one
+// (plus what the lanes' different band lengths cost in divergence).  The warp-wide sum at the end adds the lane groups up.
 template <int T, int I, int TO>
 __device__ __forceinline__ void gw_unit(const PlanDev& P, const GwTask tk, int slice, int slices, const float2* __restrict__ SF,
                                         const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ out,
-                                        int G, float* __restrict__ band, int lane) {
+                                        int G, float* __restrict__ band, int lane, int last_rep) {
     const TripleRec tr = P.triples[tk.triple];
     const int l = tr.l, n = 2 * l + 1, n1 = 2 * tr.l1 + 1, n2 = 2 * tr.l2 + 1;
     const int to_n = P.tO[l], tff = P.tFF[l];
@@ -415,10 +419,13 @@ __device__ __forceinline__ void gw_unit(const PlanDev& P, const GwTask tk, int s
             for (int j = 0; j < T; ++j) acc[o][i][j] = make_float2(0.f, 0.f);
 
     for (int g = slice; g < G; g += slices) {
-        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + lane;
-        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + lane;
-        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + lane;
-        for (int m2 = -tr.l2; m2 <= tr.l2; ++m2) {
+        const int rep = (g == G - 1) ? last_rep : 1;         // warp-uniform
+        const int slot = rep > 1 ? lane % (32 / rep) : lane;   // this lane's sample inside the group
+        const int m2_first = -tr.l2 + (rep > 1 ? lane / (32 / rep) : 0);
+        const float2* f1 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l1] + q1 * n1 * T) * 32 + slot;
+        const float2* f2 = SF + ((int64_t)g * P.nSF + P.cumSF[tr.l2] + q2 * n2 * T) * 32 + slot;
+        const float2* go = SG + ((int64_t)g * P.nSO + P.cumSO[l]) * 32 + slot;
+        for (int m2 = m2_first; m2 <= tr.l2; m2 += rep) {
             float2 Y[TO][I];
 #pragma unroll
             for (int o = 0; o < TO; ++o)
@@ -496,7 +503,7 @@ template <int T, int TO>
 __global__ void __launch_bounds__(kGwWarps * kWarp, 3)
 fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float* __restrict__ inv, float2* __restrict__ gW, int G,
-                int band_floats, int slices, int64_t slice_stride) {
+                int band_floats, int slices, int64_t slice_stride, int last_rep) {
     extern __shared__ __align__(16) float sband_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* band = sband_all + (size_t)warp * band_floats;   // this warp's copy of the current triple's CG band
@@ -508,9 +515,9 @@ fused_gw_kernel(PlanDev P, const GwTask* __restrict__ tasks, int n_tasks, const 
         const GwTask tk = tasks[task];
         // the row groups of a tile are exact (GwRows): a task has GwRows<T>::A rows or, for the last group of a tile
         // whose edge is not a multiple of A, GwRows<T>::B rows
-        if (tk.ni == GwRows<T>::A) gw_unit<T, GwRows<T>::A, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane);
+        if (tk.ni == GwRows<T>::A) gw_unit<T, GwRows<T>::A, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane, last_rep);
         if constexpr (GwRows<T>::B > 0)
-            if (tk.ni == GwRows<T>::B) gw_unit<T, GwRows<T>::B, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane);
+            if (tk.ni == GwRows<T>::B) gw_unit<T, GwRows<T>::B, TO>(P, tk, slice, slices, SF, SG, inv, out, G, band, lane, last_rep);
     }
 }
 
@@ -912,6 +919,16 @@ int gf_level(const cgb200_plan* p, int64_t G) {
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
+// How many lane groups share the last sample group's work when it is at most half full (1: none): the kernels whose
+// per-lane results are summed over the whole warp anyway (statistics, CUDA-core weight gradient) let the idle lanes of a
+// short last group take a share of its loop instead of repeating it for empty sample slots.  CGB200_OPT_SHORT_GROUP 0
+// switches it off.
+int last_group_rep(const cgb200_plan* p, int64_t B, int64_t G) {
+    if (p->opt[CGB200_OPT_SHORT_GROUP] == 0) return 1;
+    const int64_t rem = B - 32 * (G - 1);
+    return rem <= 4 ? 8 : rem <= 8 ? 4 : rem <= 16 ? 2 : 1;
+}
+
 // Shared memory of the input-gradient kernel: the part that does not depend on how many rows of a gFF tile H holds, and
 // the bytes per row.
 void gf_smem(const cgb200_plan* p, size_t* fixed, size_t* per_m) {
@@ -1237,7 +1254,8 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 const int slices = ws.gw_slices;
                 const int grid = (int)(((int64_t)n_tasks * slices + kGwWarps - 1) / kGwWarps);
                 kern<<<grid, kGwWarps * kWarp, smem, gs>>>(p->d, p->d_gw_tasks, n_tasks, ws.SF, ws.SG, ws.inv,
-                                                           slices > 1 ? ws.gw_part : (float2*)gW, G, band_floats, slices, p->d.w_len);
+                                                           slices > 1 ? ws.gw_part : (float2*)gW, G, band_floats, slices, p->d.w_len,
+                                                           last_group_rep(p, B, G));
             });
             if (ws.gw_slices > 1) {
                 launch_end(K_GW, gs);
