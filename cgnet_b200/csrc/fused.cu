@@ -1117,7 +1117,12 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
                      float* O, int64_t B, void* workspace, int64_t workspace_bytes, void* stream) {
     const bool fn = (flags & CGB200_FN_PRESENT) != 0;
     const bool update = fn && (flags & CGB200_FN_UPDATE);
-    const int ws_mode = update ? kWsFwdTrain : kWsFwdInfer;
+    // a forward with a statistics update keeps its tiles when the workspace has room for them (the size
+    // cgb200_layer_fwd_workspace_bytes_for gives for these flags); with the smaller workspace of a forward without an update
+    // it runs all the same and keeps nothing
+    int ws_mode = kWsFwdInfer;
+    if (update && B > 0 && p != nullptr && workspace != nullptr && workspace_bytes >= carve(p, B, nullptr, kWsFwdTrain).bytes)
+        ws_mode = kWsFwdTrain;
     int rc = check_layer(p, B, workspace, workspace_bytes, ws_mode);
     if (rc) return rc;
     CGB_REQUIRE(!fn || stds != nullptr, "stds is null although CGB200_FN_PRESENT is set");
@@ -1375,7 +1380,7 @@ int cgb200_layer_fwd_static(const cgb200_plan* p, const float* F, const float* W
                             int flags, float* O, int64_t B, void* stream) {
     CGB_REQUIRE(p != nullptr, "plan is null");
     CGB_REQUIRE(B >= 0, "negative batch size");
-    const int64_t need = cgb200_layer_fwd_workspace_bytes_for(p, B, flags);   // this forward's own need, not the backward's
+    const int64_t need = cgb200_layer_fwd_workspace_bytes_for(p, B, 0);   // the forward's own need without room for kept tiles
     if (need < 0) return CGB200_ERR_ARGUMENT;
     if (need > (int64_t)CGB200_STATIC_SCRATCH_BYTES) {
         set_error("cgb200_layer_fwd_static: the forward of this plan and batch needs " + std::to_string(need) +

@@ -202,7 +202,9 @@ int cgb200_layer_keeps_mid(const cgb200_plan* plan, int64_t B);
    never more than cgb200_layer_workspace_bytes.  Both depend on the plan's options at the time of the call. */
 int64_t cgb200_layer_fwd_workspace_bytes(const cgb200_plan* plan, int64_t B);
 /* The same for a call with these flags: a forward without CGB200_FN_UPDATE keeps no tiles and needs no room for them
-   (gigabytes less for the wide layers).  cgb200_layer_fwd accepts a workspace of this size for such a call. */
+   (gigabytes less for the wide layers).  cgb200_layer_fwd accepts a workspace of that smaller size for any call: a forward
+   with an update then generates its tiles twice instead of keeping them (and the backward must not be told
+   CGB200_FN_KEEP_MID). */
 int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* plan, int64_t B, int flags);
 
 /*
@@ -214,7 +216,7 @@ int64_t cgb200_layer_fwd_workspace_bytes_for(const cgb200_plan* plan, int64_t B,
  * cudaMalloc after start-up because it stalls the device.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - Returns CGB200_ERR_WORKSPACE, with the needed and available byte counts in cgb200_last_error(), when
- *     cgb200_layer_fwd_workspace_bytes_for(plan, B, flags) exceeds the array.
+ *     cgb200_layer_fwd_workspace_bytes_for(plan, B, 0) exceeds the array (kept tiles are not used here).
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress with that device current);
  *     make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps whatever the last call left in it.  The call itself
