@@ -37,6 +37,9 @@ SIGNATURES = {
     "cgb200_layer_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
     "cgb200_layer_fwd_workspace_bytes": (ctypes.c_int64, [vp, ctypes.c_int64]),
     "cgb200_layer_keeps_mid": (ctypes.c_int, [vp, ctypes.c_int64]),
+    "cgb200_layer_packed_weights_bytes": (ctypes.c_int64, [vp]),
+    "cgb200_layer_pack_weights": (ctypes.c_int, [vp, vp, vp, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp]),
+    "cgb200_layer_fwd_packed": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, vp, ctypes.c_int64, vp]),
     "cgb200_layer_fwd_workspace_bytes_for": (ctypes.c_int64, [vp, ctypes.c_int64, ctypes.c_int]),
     "cgb200_layer_fwd_static": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_int, vp, ctypes.c_int64, vp]),
     "cgb200_sh_basis_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int]),

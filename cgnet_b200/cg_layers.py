@@ -121,6 +121,7 @@ class Plan(PlanShapes):
                          self.query(_lib.Q_W_LEN), self.query(_lib.Q_SUM_TFF))
         self.tile = self.query(_lib.Q_TILE)
         self._ws_bytes = {}
+        self._option_epoch = 0      # bumped by set_option: whatever was derived from the options is stale then
         self._fn_layer_fwd, self._fn_layer_bwd = lib.cgb200_layer_fwd, lib.cgb200_layer_bwd
 
     def query(self, what):
@@ -137,6 +138,7 @@ class Plan(PlanShapes):
         """Select a kernel variant for this plan (``_lib.OPT_*``; ``_lib.AUTO`` restores the library's default)."""
         _lib.check(_lib.load().cgb200_plan_set_option(self.handle, int(option), int(value)), "cgb200_plan_set_option")
         self._ws_bytes.clear()
+        self._option_epoch += 1
 
     def get_option(self, option):
         v = _lib.ctypes.c_int32()
@@ -244,6 +246,36 @@ class Plan(PlanShapes):
         self._call(self._fn_layer_fwd, "cgb200_layer_fwd", F.data_ptr(), W.data_ptr(), _ptr(stds), cnt, eps, flags, O.data_ptr(),
                    B, ws.data_ptr(), n)
         return (O, ws) if keep else O
+
+    def packed_weights_bytes(self):
+        """Size of the packed form of the weights the tensor-core forward multiplies by; 0 where the forward does not use one."""
+        v = self._ws_bytes.get("packed")
+        if v is None:
+            v = self._ws_bytes["packed"] = int(_lib.load().cgb200_layer_packed_weights_bytes(self.handle))
+        return v
+
+    def pack_weights(self, W, stds, eps, flags):
+        """Pack W / max(eps, stds) once for ``layer_fwd_packed`` (inference with weights that do not change)."""
+        self.check_weights(W, stds, flags)
+        n = self.packed_weights_bytes()
+        if n <= 0:
+            raise RuntimeError("this plan's forward does not use packed weights")
+        packed = torch.empty(n, dtype=torch.uint8, device=self.device)
+        self._call(_lib.load().cgb200_layer_pack_weights, "cgb200_layer_pack_weights", W.data_ptr(), _ptr(stds), eps,
+                   flags & _lib.FN_PRESENT, packed.data_ptr(), n)
+        return packed
+
+    def layer_fwd_packed(self, F, packed):
+        """The forward of ``layer_fwd`` (stored statistics) with weights packed beforehand by ``pack_weights``: same bits."""
+        B = F.shape[0]
+        self.check_batch(B, F=(F, self.n_F))
+        if packed.device != self.device or packed.numel() < self.packed_weights_bytes() or self.packed_weights_bytes() <= 0:
+            raise RuntimeError("the packed weights do not belong to this plan")
+        O = torch.empty(B, self.n_O, 2, device=self.device, dtype=torch.float32)
+        ws, n = self._workspace(B, 0)
+        self._call(_lib.load().cgb200_layer_fwd_packed, "cgb200_layer_fwd_packed", F.data_ptr(), packed.data_ptr(), O.data_ptr(), B,
+                   ws.data_ptr(), n)
+        return O
 
     def layer_bwd(self, F, W, stds, eps, flags, gO, need_gF=True, kept=None):
         B = F.shape[0]
@@ -587,6 +619,8 @@ class CGBN_cuda(nn.Module):
         self.sparse_flag = sparse_flag
         self.fused = fused
         self.keep_mid = keep_mid
+        self.pack_inference_weights = True
+        self._packed, self._packed_key = None, None
         mode = lll_mode if lll_mode is not None else ("mst" if sparse_flag else None)
         self.cg = CG_woFilter_cuda(lmax, taus_fs, lll_mode=mode, device=device, tau_out=tau_out, depthwise=depthwise)
         self.t_F = self.cg.t_F
@@ -595,6 +629,22 @@ class CGBN_cuda(nn.Module):
         self.bnWMM = MyBatchNormWeightMM_cuda(lmax, self.t_FF, tau_out, batchnorm, weight_scale, init, eps, device,
                                               plan=self.cg.plan)
         self.to(device)
+
+    def _packed_weights(self):
+        """Inference without autograd on the tensor-core path: the packed form of W / max(eps, stds) is built once and
+        reused until W, the statistics, eps or the plan's options change (``pack_inference_weights=False`` switches the
+        cache off; it holds as many bytes again as four times the weights)."""
+        bn, plan = self.bnWMM, self.cg.plan
+        if not self.pack_inference_weights or plan.packed_weights_bytes() <= 0:
+            return None
+        stds = bn.bn_stds if bn.batchnorm else None
+        key = (bn.W.data_ptr(), bn.W._version, None if stds is None else (stds.data_ptr(), stds._version), bn._eps, bn._count(),
+               plan.packed_weights_bytes(), plan._option_epoch)
+        if self._packed_key != key:
+            self._packed = plan.pack_weights(bn.W.detach(), None if stds is None else stds.detach(), bn._eps,
+                                             _lib.FN_PRESENT if stds is not None else 0)
+            self._packed_key = key
+        return self._packed
 
     def _keeps_mid(self, B):
         """Keep the layer's workspace from the forward to the backward, so that the weight gradient reads the mid
@@ -619,6 +669,11 @@ class CGBN_cuda(nn.Module):
         if self.fused:
             x = _flatten_input(fs)
             update = bool(bn.batchnorm and bn.training)
+            if not update and not torch.is_grad_enabled():
+                packed = self._packed_weights()
+                if packed is not None:
+                    new_fs = self.cg.plan.layer_fwd_packed(_check_cuda_f32(x, "activations"), packed)
+                    return new_fs if straight_output else CGutils.reshape_out(new_fs, self.tau_out)
             keep = update and torch.is_grad_enabled() and self._keeps_mid(x.shape[0])
             new_fs = _CGBN_fused.apply(x, bn.W, self.cg.plan, bn.bn_stds, bn._count(), bn._eps, update, keep)
             if update:

@@ -1201,6 +1201,64 @@ int cgb200_layer_fwd(const cgb200_plan* p, const float* F, const float* W, float
     return CGB200_OK;
 }
 
+// ---- inference with weights packed once ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+inv_std_kernel(const float* __restrict__ stds, float eps, float* __restrict__ inv, int n) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < n) inv[k] = stds == nullptr ? 1.f : 1.f / fmaxf(eps, stds[k]);
+}
+
+int64_t cgb200_layer_packed_weights_bytes(const cgb200_plan* p) {
+    if (p == nullptr) {
+        set_error("plan is null");
+        return -1;
+    }
+    if (!p->d.has_out || !tc_wanted(p) || p->opt[CGB200_OPT_TC_STAGED] >= 1) return 0;
+    return align256(tc_pack_floats(p) * (int64_t)sizeof(float)) + align256(std::max<int64_t>(p->d.sum_tff, 1) * (int64_t)sizeof(float));
+}
+
+int cgb200_layer_pack_weights(const cgb200_plan* p, const float* W, const float* stds, float eps, int flags, void* packed,
+                              int64_t packed_bytes, void* stream) {
+    CGB_REQUIRE(p != nullptr, "plan is null");
+    const int64_t need = cgb200_layer_packed_weights_bytes(p);
+    CGB_REQUIRE(need > 0, "this plan's forward does not use packed weights (cgb200_layer_packed_weights_bytes is 0)");
+    CGB_REQUIRE(packed != nullptr && packed_bytes >= need && (reinterpret_cast<uintptr_t>(packed) & 255) == 0,
+                "the buffer for the packed weights is null, too small or not 256-byte aligned");
+    const bool fn = (flags & CGB200_FN_PRESENT) != 0;
+    CGB_REQUIRE(!fn || stds != nullptr, "stds is null although CGB200_FN_PRESENT is set");
+    CGB_REQUIRE(W != nullptr && al8(W), "W is null or not 8-byte aligned");
+    int dev = -1;
+    CGB_CUDA(cudaGetDevice(&dev));
+    CGB_REQUIRE(dev == p->device, "the plan belongs to another CUDA device than the current one");
+    cudaStream_t st = (cudaStream_t)stream;
+    float* pack = (float*)packed;
+    float* inv = (float*)((char*)packed + align256(tc_pack_floats(p) * (int64_t)sizeof(float)));
+    launch_begin(K_PREP, st);
+    inv_std_kernel<<<(p->d.sum_tff + 255) / 256 + 1, 256, 0, st>>>(fn ? stds : nullptr, eps, inv, p->d.sum_tff);
+    launch_end(K_PREP, st);
+    CGB_CUDA(cudaGetLastError());
+    return launch_fwd_tc(p, 0, nullptr, (const float2*)W, inv, pack, nullptr, nullptr, 0, 0, nullptr, st);
+}
+
+int cgb200_layer_fwd_packed(const cgb200_plan* p, const float* F, const void* packed, float* O, int64_t B, void* workspace,
+                            int64_t workspace_bytes, void* stream) {
+    int rc = check_layer(p, B, workspace, workspace_bytes, kWsFwdInfer);
+    if (rc) return rc;
+    CGB_REQUIRE(cgb200_layer_packed_weights_bytes(p) > 0, "this plan's forward does not use packed weights");
+    CGB_REQUIRE(packed != nullptr && (reinterpret_cast<uintptr_t>(packed) & 255) == 0, "packed weights are null or misaligned");
+    if (B == 0 || p->d.n_O == 0) return CGB200_OK;
+    CGB_REQUIRE(F != nullptr && O != nullptr && al8(F) && al8(O), "null or misaligned buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int G = (int)((B + 31) / 32);
+    Workspace ws = carve(p, B, workspace, kWsFwdInfer);
+    const int T = p->d.tile;
+    PrepJob jf{(const float2*)F, ws.SF, p->d.n_F, p->d.cumF, p->d.cumSF, p->d.tF, p->d.nSF, has_pad(p->tF, T) ? 1 : 0};
+    PrepJob none{};
+    if ((rc = launch_prep(p, jf, none, 1, (int)B, G, nullptr, 0.f, ws.inv, ws.counters, st))) return rc;
+    if (p->fwd_rows.empty()) return CGB200_OK;
+    return launch_fwd_tc(p, ws.fwd_level, ws.SF, nullptr, nullptr, (float*)packed, (float2*)O, ws.fwd_part, (int)B, G, nullptr, st);
+}
+
 int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const float* stds, float eps, int flags,
                      const float* gO, float* gF, float* gW, int64_t B, void* workspace, int64_t workspace_bytes,
                      void* stream) {

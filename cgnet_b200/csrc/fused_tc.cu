@@ -1162,11 +1162,14 @@ static int launch_tc(const cgb200_plan* p, int lv, const float2* SF, const float
     int n_max = 16;
     for (int v : p->tc_npad) n_max = std::max(n_max, v);
     if (p->tc_tiles[0].empty()) return CGB200_OK;
-    launch_begin(K_TC_PACK, st);
-    if (p->d.n_cells > 0)
-        tc_pack_kernel<T><<<p->d.n_cells, 256, 0, st>>>(p->d, p->d_tc_npad, p->d_tc_pack_off, W, inv, pack);
-    launch_end(K_TC_PACK, st);
-    CGB_CUDA(cudaGetLastError());
+    if (W != nullptr) {   // null: `pack` already holds the packed weights (cgb200_layer_pack_weights)
+        launch_begin(K_TC_PACK, st);
+        if (p->d.n_cells > 0)
+            tc_pack_kernel<T><<<p->d.n_cells, 256, 0, st>>>(p->d, p->d_tc_npad, p->d_tc_pack_off, W, inv, pack);
+        launch_end(K_TC_PACK, st);
+        CGB_CUDA(cudaGetLastError());
+    }
+    if (SF == nullptr) return CGB200_OK;   // packing only
     // flush groups: one per 64 accumulator columns; generator groups (= stages) take the warps that are left
     const int n_flush = n_max > 64 ? 2 : 1;
     const int s_cap = p->opt[CGB200_OPT_TC_STAGES] >= 2 ? std::min(kTcMaxStages - n_flush, p->opt[CGB200_OPT_TC_STAGES]) : kTcMaxStages - n_flush;

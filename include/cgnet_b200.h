@@ -179,6 +179,20 @@ int cgb200_layer_fwd(const cgb200_plan* plan, const float* F, const float* W, fl
                      int flags, float* O, int64_t B, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Inference with weights that do not change between calls: the tensor-core forward multiplies by the weights in a packed
+ * form (scaled by 1/max(eps, stds), real form, TF32 high / low parts, the MMA's operand order) that cgb200_layer_fwd
+ * rebuilds on every call (4-14 % of a wide layer's forward).  Pack them once into a caller-owned buffer and call
+ * cgb200_layer_fwd_packed: same result as cgb200_layer_fwd with the flags given here and without CGB200_FN_UPDATE, bit for
+ * bit.  cgb200_layer_packed_weights_bytes is 0 for plans whose forward does not run on the tensor cores.  Pack again
+ * after W, stds, eps or a plan option changes.
+ */
+int64_t cgb200_layer_packed_weights_bytes(const cgb200_plan* plan);
+int cgb200_layer_pack_weights(const cgb200_plan* plan, const float* W, const float* stds, float eps, int flags,
+                              void* packed, int64_t packed_bytes, void* stream);
+int cgb200_layer_fwd_packed(const cgb200_plan* plan, const float* F, const void* packed, float* O, int64_t B,
+                            void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Gradients of the whole layer, (F, W, stds, gO) -> (gF, gW), regenerating FF on the fly.
  * Replaces `FN_WMM_backward` + `sparse_backward` issued by autograd (CGNet/CG_layers.py:54-72, 194-203).
  * `stds` must be the values the forward used (i.e. after its update).  gF may be NULL when the gradient with respect

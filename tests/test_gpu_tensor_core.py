@@ -377,3 +377,48 @@ def test_cuda_core_forward_reads_back_the_kept_tiles(taus, tau_out, B, mode):
     assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
     assert_fragments_close(out[1][0], O_want, tau_out, "O (CUDA-core forward, kept tiles) vs oracle")
     np.testing.assert_allclose(out[1][1], stds_want, rtol=2e-5, atol=1e-7)
+
+
+def test_inference_with_weights_packed_once():
+    """cgb200_layer_pack_weights + cgb200_layer_fwd_packed against cgb200_layer_fwd (same bits), and the module-level cache:
+    CGBN_cuda in eval mode under no_grad packs once, notices new weights, new statistics and a training step in between."""
+    from cgnet_b200 import CGBN_cuda, _lib, get_plan
+    dev = torch.device("cuda", 0)
+    case = make_case([8, 4, 12, 8], [6, 9, 16, 3], 7, "default", seed=65)
+    plan = get_plan(case["lmax"], case["taus"], case["tau_out"], case["llls"], dev, tile=4)
+    assert plan.packed_weights_bytes() > 0
+    F = torch.tensor(case["F"], device=dev)
+    W = torch.tensor(case["W"], device=dev)
+    stds = torch.tensor(case["stds"], device=dev)
+    for fl, st in ((_lib.FN_PRESENT, stds), (0, None)):
+        want = plan.layer_fwd(F, W, st, 1.0, 1e-5, fl)
+        got = plan.layer_fwd_packed(F, plan.pack_weights(W, st, 1e-5, fl))
+        plan.check_status()
+        assert torch.equal(got, want)
+    narrow = get_plan(2, [5] * 3, [5] * 3, make_case([5] * 3, [5] * 3, 2, "default", seed=1)["llls"], dev)
+    assert narrow.packed_weights_bytes() == 0        # CUDA-core forward: nothing to pack
+
+    torch.manual_seed(7)
+    np.random.seed(7)
+    layer = CGBN_cuda(3, [16] * 4, [16] * 4, batchnorm=True, device=dev)
+    x = torch.randn(9, 16 * 16, 2, device=dev)
+
+    def both():
+        layer.eval()
+        with torch.no_grad():
+            cached = layer(x, straight_output=True)
+        plain = layer(x, straight_output=True)       # autograd on: the ordinary call, packs inside
+        assert torch.equal(cached, plain)
+        return cached
+
+    a = both()
+    key = layer._packed_key
+    assert key is not None and torch.equal(both(), a) and layer._packed_key == key      # second call: cache hit
+    with torch.no_grad():
+        layer.bnWMM.W.mul_(1.5)
+    b = both()
+    assert layer._packed_key != key and not torch.equal(a, b)
+    layer.train()
+    layer(x, straight_output=True)                   # updates the statistics in place (no tensor version changes)
+    c = both()
+    assert not torch.equal(b, c)
