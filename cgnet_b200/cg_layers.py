@@ -649,9 +649,9 @@ class CGBN_cuda(nn.Module):
     def _keeps_mid(self, B):
         """Keep the layer's workspace from the forward to the backward, so that the weight gradient reads the mid
         activation's tiles the forward left in it instead of generating them again (wide layers on the tensor-core path
-        only: ``Plan.keeps_mid``)?  ``keep_mid=True`` / ``False`` decide; the default keeps while the workspaces kept on the
-        device at that moment (by all layers: each is held until its layer's backward has run), this one included, stay
-        under a quarter of the device's memory."""
+        only: ``Plan.keeps_mid``)?  ``keep_mid=True`` / ``False`` decide; the default keeps workspaces of 64 MB and more while
+        the workspaces kept on the device at that moment (by all layers: each is held until its layer's backward has run),
+        this one included, stay under a quarter of the device's memory."""
         if self.keep_mid is False:
             return False
         plan = self.cg.plan
@@ -659,10 +659,13 @@ class CGBN_cuda(nn.Module):
             return False
         if self.keep_mid:
             return True
+        need = plan._workspace_bytes(B)
+        if need < (64 << 20):
+            return False   # a small layer: what the kept tiles save on the GPU is less than the host time of keeping them
         dev = plan.device
         if dev not in _device_bytes:
             _device_bytes[dev] = torch.cuda.get_device_properties(dev).total_memory
-        return (_kept_bytes.get(dev, 0) + plan._workspace_bytes(B)) * 4 <= _device_bytes[dev]
+        return (_kept_bytes.get(dev, 0) + need) * 4 <= _device_bytes[dev]
 
     def forward(self, fs, straight_output=False):
         bn = self.bnWMM
