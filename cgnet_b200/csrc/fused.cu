@@ -642,13 +642,21 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
 
 // PRE: the gFF tiles were computed beforehand by the tensor-core GEMM (gff_tc.cu) and sit in the workspace `gff` in the
 // layout of H; phase 1 is then an asynchronous copy of the entry's tile (the launch makes H hold a whole entry).
-template <int T, bool DW, bool SPLIT, bool PRE = false>
+//
+// SHORTG (with `last_rep` > 1): the last sample group holds at most 32 / last_rep samples.  In that group a lane is a
+// (row offset j, sample s) pair, s = lane % (32 / last_rep): a phase-1 unit covers last_rep rows m of the tile and a
+// phase-2 unit last_rep rows of the owned fragment, one per lane group, instead of every lane repeating one row for an
+// empty sample slot, so the group costs about 1 / last_rep of a full one.  Every element is still computed by one lane
+// in the same order of operations: the bits do not change.
+template <int T, bool DW, bool SPLIT, bool PRE = false, bool SHORTG = false>
 __global__ void __launch_bounds__(kGfWarps * kWarp)
 fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __restrict__ entry_begin,
                 const int* __restrict__ blocks, const unsigned char* __restrict__ owner_tab, const float2* __restrict__ SF,
                 const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
                 float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats,
-                const float2* __restrict__ gff = nullptr, int64_t gff_stride = 0, const int64_t* __restrict__ gff_off = nullptr) {
+                const float2* __restrict__ gff = nullptr, int64_t gff_stride = 0, const int64_t* __restrict__ gff_off = nullptr,
+                int last_rep = 1) {
+    static_assert(!(SHORTG && SPLIT), "lane sharing of the short last group is written for whole-row units");
     using S = GfShape<T, DW>;
     constexpr int NH = S::NH, NHP = S::NHP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -678,6 +686,25 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     __syncwarp();
     const float2* slabF = SF + (int64_t)g * P.nSF * 32;
     const float2* slabG = SG + (int64_t)g * P.nSO * 32 + lane;
+    const bool shortg = SHORTG && last_rep > 1 && g == G - 1;   // block-uniform
+    const int sh_w = 32 / (shortg ? last_rep : 1);              // sample slots in use
+    const int sh_j = lane / sh_w, sh_s = lane - sh_j * sh_w;    // this lane's row offset inside a unit and its sample slot
+    // phase 2 of one entry over the chunk of H that is resident
+    auto gather = [&](bool first, const float2* fo, const float* band, int l, int lo_, int l2, int n2, int mc0, int mcn) {
+        if constexpr (SHORTG) {
+            if (shortg) {
+                for (int ug = warp; ug * last_rep < nt; ug += nwarps) {
+                    const int r = ug * last_rep + sh_j;
+                    if (r < nt) gf_phase2_unit<T, DW, false>(r, first, H, fo, band, acc, lt, nt, l, lo_, l2, n2, mc0, mcn, sh_s);
+                }
+                return;
+            }
+        }
+        for (int k = 0; k < n_units; ++k) {
+            const int u = ulist[warp * 2 * max_n + k];
+            gf_phase2_unit<T, DW, SPLIT>(u, first, H, fo, band, acc, lt, nt, l, lo_, l2, n2, mc0, mcn, lane);
+        }
+    };
 
     // Staging of an entry runs one entry ahead of its use: the other operand's tile and the CG band go to the idle
     // half of their double buffers by asynchronous copies issued when the previous entry starts; the tile of
@@ -769,10 +796,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
             const float2* fo = fo2 + (size_t)buf * T * max_n * 32;
             const float* band = band2 + buf * band_floats;
             const int lo_ = first ? en.l2 : en.l1;
-            for (int k = 0; live && k < n_units; ++k) {
-                const int u = ulist[warp * 2 * max_n + k];
-                gf_phase2_unit<T, DW, SPLIT>(u, first, H, fo, band, acc, lt, nt, l, lo_, en.l2, n2, 0, n, lane);
-            }
+            if (live) gather(first, fo, band, l, lo_, en.l2, n2, 0, n);
             en = nxt;
             e += parts;
             buf ^= 1;
@@ -796,6 +820,29 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
         for (int mc0 = 0; mc0 < n; mc0 += Mc) {
             const int mcn = min(Mc, n - mc0);
             if (mc0 > 0) __syncthreads();   // the previous chunk's readers are done with H
+            bool h_done = false;
+            if constexpr (SHORTG) {
+                if (shortg) {   // a unit = last_rep rows of the chunk, one per lane group
+                    const float2* gos = go - lane + sh_s;
+                    if constexpr (S::KA > 0) {
+                        for (int u = warp; (u >> 1) * last_rep < mcn; u += nwarps) {
+                            const int mi = mc0 + (u >> 1) * last_rep + sh_j;
+                            if (mi < mc0 + mcn) {
+                                float2* h = H + (size_t)(mi - mc0) * NH * 32 + sh_s;
+                                if (u & 1) gf_h_unit<T, NH, NHP, S::KA, NH - S::KA>(gos, wt, h, to_n, n, mi);
+                                else gf_h_unit<T, NH, NHP, 0, S::KA>(gos, wt, h, to_n, n, mi);
+                            }
+                        }
+                    } else {
+                        for (int u = warp; u * last_rep < mcn; u += nwarps) {
+                            const int mi = mc0 + u * last_rep + sh_j;
+                            if (mi < mc0 + mcn) gf_h_unit<T, NH, NHP, 0, NH>(gos, wt, H + (size_t)(mi - mc0) * NH * 32 + sh_s, to_n, n, mi);
+                        }
+                    }
+                    h_done = true;
+                }
+            }
+            if (!h_done) {
             if constexpr (S::KA > 0) {
                 for (int u = warp; u < 2 * mcn; u += nwarps) {
                     const int mi = mc0 + (u >> 1);
@@ -807,12 +854,10 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
                 for (int mi = mc0 + warp; mi < mc0 + mcn; mi += nwarps)
                     gf_h_unit<T, NH, NHP, 0, NH>(go, wt, H + (size_t)(mi - mc0) * NH * 32 + lane, to_n, n, mi);
             }
+            }
             __syncthreads();
             if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
-            for (int k = 0; k < n_units; ++k) {
-                const int u = ulist[warp * 2 * max_n + k];
-                gf_phase2_unit<T, DW, SPLIT>(u, first, H, fo, band, acc, lt, nt, l, lo_, en.l2, n2, mc0, mcn, lane);
-            }
+            gather(first, fo, band, l, lo_, en.l2, n2, mc0, mcn);
         }
         en = nxt;
         e += parts;
@@ -919,10 +964,9 @@ int gf_level(const cgb200_plan* p, int64_t G) {
 
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
-// How many lane groups share the last sample group's work when it is at most half full (1: none): the kernels whose
-// per-lane results are summed over the whole warp anyway (statistics, CUDA-core weight gradient) let the idle lanes of a
-// short last group take a share of its loop instead of repeating it for empty sample slots.  CGB200_OPT_SHORT_GROUP 0
-// switches it off.
+// How many lane groups share the last sample group's work when it is at most half full (1: none).  The CUDA-core weight
+// gradient, whose per-lane results are summed over the whole warp anyway, lets the idle lanes take a share of its outer
+// loop; the input gradient gives each lane group another row of a unit.  CGB200_OPT_SHORT_GROUP 0 switches it off.
 int last_group_rep(const cgb200_plan* p, int64_t B, int64_t G) {
     if (p->opt[CGB200_OPT_SHORT_GROUP] == 0) return 1;
     const int64_t rem = B - 32 * (G - 1);
@@ -1346,6 +1390,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
         } else {
             const int band_floats = (int)(p->gen_band_bytes / sizeof(float));
             const int max_to = std::max(p->max_tau_out, 1);
+            const int last_rep = last_group_rep(p, B, G);   // lane sharing in a short last sample group
             size_t fixed = 0, per_m = 0;
             gf_smem(p, &fixed, &per_m);
             if (fixed + per_m > kMaxDynSmem) {
@@ -1360,12 +1405,12 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 const size_t smem_pre = smem;
                 const int rc2 = launch_gff_tc(p, ws.gff_level, ws.SG, (const float2*)W, ws.inv, ws.gff_pack, ws.gff, G, st);
                 if (rc2) return rc2;
-                auto kern = fused_gf_kernel<4, false, false, true>;
+                auto kern = last_rep > 1 ? fused_gf_kernel<4, false, false, true, true> : fused_gf_kernel<4, false, false, true, false>;
                 if (smem_pre > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pre));
                 launch_begin(K_GF, st);
                 kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem_pre, st>>>(
                     p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out,
-                    part_stride, (int)B, Mc_pre, p->max_n, max_to, band_floats, ws.gff, gff_group_elems(p), p->d_gff_off);
+                    part_stride, (int)B, Mc_pre, p->max_n, max_to, band_floats, ws.gff, gff_group_elems(p), p->d_gff_off, last_rep);
                 launch_end(K_GF, st);
                 CGB_CUDA(cudaGetLastError());
             } else {
@@ -1374,9 +1419,10 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const bool split_units = gf_split(p);
             const unsigned char* owner = p->d_gf_owner + (size_t)(split_units ? 1 : 0) * 2 * (p->d.lmax + 1) * (p->d.lmax + 1);
             CGB_DISPATCH_TILE(T, p->d.depthwise, {
-                auto kern = split_units ? fused_gf_kernel<TT, DD, true> : fused_gf_kernel<TT, DD, false>;
+                auto kern = split_units ? fused_gf_kernel<TT, DD, true, false, false>
+                                        : last_rep > 1 ? fused_gf_kernel<TT, DD, false, false, true> : fused_gf_kernel<TT, DD, false, false, false>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats, nullptr, 0, nullptr);
+                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats, nullptr, 0, nullptr, split_units ? 1 : last_rep);
             });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());

@@ -125,8 +125,8 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
 #define CGB200_OPT_FWD_KEEP_MID      14  /* forward with a statistics update on the tensor-core path: the statistics kernel
                                            keeps the tiles of the mid activation it generates in the workspace and the
                                            forward kernel reads them back instead of generating them again               */
-#define CGB200_OPT_SHORT_GROUP       15  /* statistics and CUDA-core weight gradient: the idle lanes of a last sample group
-                                           that is at most half full share its loop (0: off)                             */
+#define CGB200_OPT_SHORT_GROUP       15  /* CUDA-core weight gradient and input gradient: the idle lanes of a last sample
+                                           group that is at most half full share its work (0: off)                       */
 #define CGB200_OPT_COUNT            16
 int cgb200_plan_set_option(cgb200_plan* plan, int option, int value);
 int cgb200_plan_get_option(const cgb200_plan* plan, int option, int* value);
