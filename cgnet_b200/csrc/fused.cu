@@ -663,7 +663,17 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     // blockIdx.x = block * G + group: the blocks are listed most expensive first, and the sample groups of one block
     // start together, so the cheap blocks of every group are what is left for the last wave
     const int G = (B + 31) >> 5;
-    const int blk = blockIdx.x / G, g = blockIdx.x - blk * G;
+    int blk = blockIdx.x / G, g = blockIdx.x - blk * G;
+    if (SHORTG && last_rep > 1 && G > 1) {   // the cheap blocks of the short last group come after all others
+        const int n_full = (int)(gridDim.x / G) * (G - 1);
+        if ((int)blockIdx.x < n_full) {
+            blk = blockIdx.x / (G - 1);
+            g = blockIdx.x - blk * (G - 1);
+        } else {
+            blk = blockIdx.x - n_full;
+            g = G - 1;
+        }
+    }
     const int lt = blocks[4 * blk], q = blocks[4 * blk + 1];
     const int part = blocks[4 * blk + 2], parts = blocks[4 * blk + 3];
     const int nt = 2 * lt + 1, t_0 = q * T;
