@@ -43,6 +43,17 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _current_stream(index):
+    """Handle of PyTorch's current stream on device ``index``.  The raw getter skips building a ``torch.cuda.Stream``
+    object, which costs several microseconds on a path that runs twice per layer and step."""
+    if _raw_stream is not None:
+        return _raw_stream(index)
+    return torch.cuda.current_stream(index).cuda_stream
+
+
 def _check_cuda_f32(t, name):
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor (cgnet_b200 has no CPU path)")
@@ -218,10 +229,10 @@ class Plan(PlanShapes):
         """Call a library entry point with this plan's device current (the per-step path of a training loop: the device
         is switched only when it is not current already)."""
         if torch.cuda.current_device() == self.device.index:
-            status = fn(self.handle, *args, torch.cuda.current_stream().cuda_stream)
+            status = fn(self.handle, *args, _current_stream(self.device.index))
         else:
             with torch.cuda.device(self.device):
-                status = fn(self.handle, *args, torch.cuda.current_stream().cuda_stream)
+                status = fn(self.handle, *args, _current_stream(self.device.index))
         if status != 0:
             _lib.check(status, name)
 
