@@ -701,14 +701,12 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     const int sh_j = lane / sh_w, sh_s = lane - sh_j * sh_w;    // this lane's row offset inside a unit and its sample slot
     // phase 2 of one entry over the chunk of H that is resident
     auto gather = [&](bool first, const float2* fo, const float* band, int l, int lo_, int l2, int n2, int mc0, int mcn) {
-        if constexpr (SHORTG) {
-            if (shortg) {
-                for (int ug = warp; ug * last_rep < nt; ug += nwarps) {
-                    const int r = ug * last_rep + sh_j;
-                    if (r < nt) gf_phase2_unit<T, DW, false>(r, first, H, fo, band, acc, lt, nt, l, lo_, l2, n2, mc0, mcn, sh_s);
-                }
-                return;
+        if (shortg) {   // (a constant false without SHORTG)  a unit = last_rep rows of the fragment, one per lane group
+            for (int ug = warp; ug * last_rep < nt; ug += nwarps) {
+                const int r = ug * last_rep + sh_j;
+                if (r < nt) gf_phase2_unit<T, DW, false>(r, first, H, fo, band, acc, lt, nt, l, lo_, l2, n2, mc0, mcn, sh_s);
             }
+            return;
         }
         for (int k = 0; k < n_units; ++k) {
             const int u = ulist[warp * 2 * max_n + k];
@@ -830,30 +828,24 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
         for (int mc0 = 0; mc0 < n; mc0 += Mc) {
             const int mcn = min(Mc, n - mc0);
             if (mc0 > 0) __syncthreads();   // the previous chunk's readers are done with H
-            bool h_done = false;
-            if constexpr (SHORTG) {
-                if (shortg) {   // a unit = last_rep rows of the chunk, one per lane group
-                    const float2* gos = go - lane + sh_s;
-                    if constexpr (S::KA > 0) {
-                        for (int u = warp; (u >> 1) * last_rep < mcn; u += nwarps) {
-                            const int mi = mc0 + (u >> 1) * last_rep + sh_j;
-                            if (mi < mc0 + mcn) {
-                                float2* h = H + (size_t)(mi - mc0) * NH * 32 + sh_s;
-                                if (u & 1) gf_h_unit<T, NH, NHP, S::KA, NH - S::KA>(gos, wt, h, to_n, n, mi);
-                                else gf_h_unit<T, NH, NHP, 0, S::KA>(gos, wt, h, to_n, n, mi);
-                            }
-                        }
-                    } else {
-                        for (int u = warp; u * last_rep < mcn; u += nwarps) {
-                            const int mi = mc0 + u * last_rep + sh_j;
-                            if (mi < mc0 + mcn) gf_h_unit<T, NH, NHP, 0, NH>(gos, wt, H + (size_t)(mi - mc0) * NH * 32 + sh_s, to_n, n, mi);
+            if (shortg) {   // (a constant false without SHORTG)  a unit = last_rep rows of the chunk, one per lane group
+                const float2* gos = go - lane + sh_s;
+                if constexpr (S::KA > 0) {
+                    for (int u = warp; (u >> 1) * last_rep < mcn; u += nwarps) {
+                        const int mi = mc0 + (u >> 1) * last_rep + sh_j;
+                        if (mi < mc0 + mcn) {
+                            float2* h = H + (size_t)(mi - mc0) * NH * 32 + sh_s;
+                            if (u & 1) gf_h_unit<T, NH, NHP, S::KA, NH - S::KA>(gos, wt, h, to_n, n, mi);
+                            else gf_h_unit<T, NH, NHP, 0, S::KA>(gos, wt, h, to_n, n, mi);
                         }
                     }
-                    h_done = true;
+                } else {
+                    for (int u = warp; u * last_rep < mcn; u += nwarps) {
+                        const int mi = mc0 + u * last_rep + sh_j;
+                        if (mi < mc0 + mcn) gf_h_unit<T, NH, NHP, 0, NH>(gos, wt, H + (size_t)(mi - mc0) * NH * 32 + sh_s, to_n, n, mi);
+                    }
                 }
-            }
-            if (!h_done) {
-            if constexpr (S::KA > 0) {
+            } else if constexpr (S::KA > 0) {
                 for (int u = warp; u < 2 * mcn; u += nwarps) {
                     const int mi = mc0 + (u >> 1);
                     float2* h = H + (size_t)(mi - mc0) * NH * 32 + lane;
@@ -863,7 +855,6 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
             } else {
                 for (int mi = mc0 + warp; mi < mc0 + mcn; mi += nwarps)
                     gf_h_unit<T, NH, NHP, 0, NH>(go, wt, H + (size_t)(mi - mc0) * NH * 32 + lane, to_n, n, mi);
-            }
             }
             __syncthreads();
             if (has_next && mc0 + Mc >= n) wt_prefetch(nxt, wreg);   // in flight during the last chunk's phase 2
