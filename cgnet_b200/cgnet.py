@@ -43,13 +43,14 @@ class SphericalCNN(nn.Module):
         else:
             B = f_input.shape[0]
             fs = f_input
-        embedding = [fs[:, : int(self.taus[0][0]), :].reshape(B, -1)] if self.skipconn else []
+        # the l=0 fragments are the first tau_0 rows of the flat activations: strided views, gathered by one concatenation
+        embedding = [fs[:, : int(self.taus[0][0]), :]] if self.skipconn else []
         for i in range(self.n_layers):
             fs = self.cgs[i](fs, straight_output=True)
             if self.skipconn:
-                embedding.append(fs[:, : int(self.taus[i + 1][0]), :].reshape(B, -1))
+                embedding.append(fs[:, : int(self.taus[i + 1][0]), :])
         if self.skipconn:
-            return torch.cat(embedding, 1)
+            return torch.cat(embedding, 1).reshape(B, -1)
         return fs[:, : int(self.taus[-1][0]), :].reshape(B, -1)
 
 
