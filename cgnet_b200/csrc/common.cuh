@@ -17,6 +17,7 @@ constexpr int kMaxLmax = 511;        // same ceiling the reference asserts (cuda
 // Dynamic shared memory a launch may ask for: the 227 KB a block can own less 1 KB for the kernels' static __shared__
 // variables (barriers, counters, reduction scratch), which count against the same limit.
 constexpr size_t kMaxDynSmem = 226 * 1024;
+constexpr size_t kSmemPerSM = 228 * 1024;   // shared memory of an SM; every resident block reserves 1 KB of it
 constexpr int kMaxTile = 6;          // largest channel-tile edge the register-tiled kernels are instantiated for
 
 // One admissible (l, l1, l2) triple with everything a kernel needs to find its operands and its outputs.

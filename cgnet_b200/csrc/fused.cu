@@ -655,7 +655,7 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
                 const float2* __restrict__ SG, const float2* __restrict__ W, const float* __restrict__ inv,
                 float2* __restrict__ out, int64_t part_stride, int B, int Mc, int max_n, int max_to, int band_floats,
                 const float2* __restrict__ gff = nullptr, int64_t gff_stride = 0, const int64_t* __restrict__ gff_off = nullptr,
-                int last_rep = 1) {
+                int last_rep = 1, int nbuf = 2) {
     static_assert(!(SHORTG && SPLIT), "lane sharing of the short last group is written for whole-row units");
     using S = GfShape<T, DW>;
     constexpr int NH = S::NH, NHP = S::NHP;
@@ -682,9 +682,9 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     const int tau_t = P.tF[lt];
     float2* acc = reinterpret_cast<float2*>(smem_raw);          // [T][nt][32]
     float2* fo2 = acc + (size_t)T * max_n * 32;                  // 2 x [n_o][T][32]  other operand's tile, two entries
-    float2* wt = fo2 + (size_t)2 * T * max_n * 32;               // [to_n][NHP]   conj(W) / std
+    float2* wt = fo2 + (size_t)nbuf * T * max_n * 32;            // [to_n][NHP]   conj(W) / std
     float* band2 = reinterpret_cast<float*>(wt + (size_t)max_to * NHP);   // 2 x [n][n2]
-    unsigned short* ulist = reinterpret_cast<unsigned short*>(band2 + 2 * band_floats);   // [warps][2 max_n] phase-2 units of each warp
+    unsigned short* ulist = reinterpret_cast<unsigned short*>(band2 + nbuf * band_floats);   // [warps][2 max_n] phase-2 units of each warp
     float2* H = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(ulist) + ((kGfWarps * 4 * max_n + 15) & ~15));   // [Mc][NH][32]
     for (int i = threadIdx.x; i < T * nt * 32; i += blockDim.x) acc[i] = make_float2(0.f, 0.f);
     int n_units = 0;   // this warp's phase-2 units, listed once per block (every lane keeps the same count)
@@ -770,10 +770,41 @@ fused_gf_kernel(PlanDev P, const GfInfo* __restrict__ entries, const int* __rest
     int buf = 0;
     if (e < e_end) {
         en = entries[e];
-        stage_async(en, 0);
+        if (!PRE || nbuf == 2) stage_async(en, 0);
         if constexpr (!PRE) wt_prefetch(en, wreg);
     }
     if constexpr (PRE) {
+        if (nbuf == 1) {
+            // Two blocks per SM: one staging buffer and the tile in chunks of Mc rows; while this block waits for its
+            // copies the SM's other block computes.
+            while (e < e_end) {
+                const int l = en.l, n = 2 * l + 1, n2 = 2 * en.l2 + 1;
+                const bool first = en.role == 0;
+                GfInfo nx2 = en;
+                if (e + parts < e_end) nx2 = entries[e + parts];
+                if (en.to_n > 0) {
+                    const int nt2 = (en.tau2 + T - 1) / T;
+                    const int cell = en.cell0 + (first ? q * nt2 + en.in0 / T : (en.in0 / T) * nt2 + q);
+                    const int64_t hoff = gff_off[l] + (int64_t)(cell - P.cell_begin[l]) * n * NH;
+                    const float4* src = reinterpret_cast<const float4*>(gff + ((int64_t)g * gff_stride + hoff) * 32);
+                    const int lo_ = first ? en.l2 : en.l1;
+                    for (int mc0 = 0; mc0 < n; mc0 += Mc) {
+                        const int mcn = min(Mc, n - mc0);
+                        __syncthreads();   // the gather before this one is over: H (and for a new entry the staging buffer) is free
+                        if (mc0 == 0) stage_async(en, 0);
+                        float4* dst = reinterpret_cast<float4*>(H);
+                        const float4* sc = src + (size_t)mc0 * NH * 16;
+                        for (int i = threadIdx.x; i < mcn * NH * 16; i += blockDim.x) __pipeline_memcpy_async(dst + i, sc + i, 16);
+                        __pipeline_commit();
+                        __pipeline_wait_prior(0);
+                        __syncthreads();
+                        gather(first, fo2, band2, l, lo_, en.l2, n2, mc0, mcn);
+                    }
+                }
+                en = nx2;
+                e += parts;
+            }
+        }
         // The tiles come from the workspace: per entry one asynchronous copy of its tile into H, then the gather.  (Tried:
         // H as two half buffers with the next chunk's copy under way during the gather - the chunked gather cost more
         // than the hidden copy saved, 3.04 against 2.91 ms at lmax 14 with 16 channels.)
@@ -998,7 +1029,7 @@ bool gff_wanted(const cgb200_plan* p, int64_t G) {
     size_t fixed = 0, per_m = 0;
     gf_smem(p, &fixed, &per_m);
     if (fixed + (size_t)p->max_n * per_m > kMaxDynSmem) return false;
-    if (opt == 1) return true;
+    if (opt >= 1) return true;
     const double bytes = (double)gff_group_elems(p) * (double)G * 32 * sizeof(float2);
     return p->max_tau_out >= 12 && bytes <= 16.0 * (1ull << 30);
 }
@@ -1402,16 +1433,38 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
             const size_t smem = fixed + (size_t)Mc * per_m;
             if (ws.gff != nullptr && Mc == p->max_n && T == 4 && !gf_split(p)) {   // H must hold a whole entry's tile
-                const int Mc_pre = Mc;
-                const size_t smem_pre = smem;
+                int Mc_pre = Mc;
+                size_t smem_pre = smem;
+                int nbuf = 2, max_to_pre = max_to;
+                // Two blocks per SM (the gather variant needs 64 registers per thread, so shared memory decides): one
+                // staging buffer instead of two, no staged weights, and the tile in chunks of as many rows as half an
+                // SM's shared memory leaves.  The SM's other block computes while a block waits for its copies, which
+                // the single block could only hide for the small staging copies.  Measured at 64 samples: lmax 10 with
+                // 16 channels 801 -> 709 us, with 32 channels 2892 -> 2582 us, lmax 14 with 16 channels (three chunks
+                // per tile) 2816 -> 2767 us.  Taken when the launch has at least two blocks for every SM;
+                // CGB200_OPT_GRAD_MID_GEMM 2 / 3 force it on / off.
+                {
+                    const size_t limit = (kSmemPerSM - 2 * 1024) / 2;   // two blocks, 1 KB reserved for each
+                    const size_t fixed2 = (size_t)2 * T * p->max_n * 32 * sizeof(float2) + p->gen_band_bytes +
+                                          (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
+                    const int mode = p->opt[CGB200_OPT_GRAD_MID_GEMM];
+                    const bool fits = fixed2 + 4 * per_m <= limit;
+                    if (fits && mode != 3 && (mode == 2 || (int64_t)nblk * G >= 2 * (int64_t)p->num_sms)) {
+                        nbuf = 1;
+                        max_to_pre = 0;
+                        Mc_pre = (int)std::min<size_t>(p->max_n, (limit - fixed2) / per_m);
+                        smem_pre = fixed2 + (size_t)Mc_pre * per_m;
+                    }
+                }
                 const int rc2 = launch_gff_tc(p, ws.gff_level, ws.SG, (const float2*)W, ws.inv, ws.gff_pack, ws.gff, G, st);
                 if (rc2) return rc2;
                 auto kern = last_rep > 1 ? fused_gf_kernel<4, false, false, true, true> : fused_gf_kernel<4, false, false, true, false>;
                 if (smem_pre > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pre));
+                if (nbuf == 1) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
                 launch_begin(K_GF, st);
                 kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem_pre, st>>>(
                     p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out,
-                    part_stride, (int)B, Mc_pre, p->max_n, max_to, band_floats, ws.gff, gff_group_elems(p), p->d_gff_off, last_rep);
+                    part_stride, (int)B, Mc_pre, p->max_n, max_to_pre, band_floats, ws.gff, gff_group_elems(p), p->d_gff_off, last_rep, nbuf);
                 launch_end(K_GF, st);
                 CGB_CUDA(cudaGetLastError());
             } else {
@@ -1423,7 +1476,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 auto kern = split_units ? fused_gf_kernel<TT, DD, true, false, false>
                                         : last_rep > 1 ? fused_gf_kernel<TT, DD, false, false, true> : fused_gf_kernel<TT, DD, false, false, false>;
                 if (smem > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats, nullptr, 0, nullptr, split_units ? 1 : last_rep);
+                kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem, st>>>(p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out, part_stride, (int)B, Mc, p->max_n, max_to, band_floats, nullptr, 0, nullptr, split_units ? 1 : last_rep, 2);
             });
             launch_end(K_GF, st);
             CGB_CUDA(cudaGetLastError());

@@ -819,9 +819,10 @@ int cgb200_plan_set_option(cgb200_plan* p, int option, int value) {
                 CGB_REQUIRE(value >= 0 && value < cgb200_plan::kTcLevels, "CGB200_OPT_TC_FWD_SPLIT must be CGB200_AUTO or 0..6");
                 break;
             case CGB200_OPT_WAIT_POLLS: CGB_REQUIRE(value >= 1, "CGB200_OPT_WAIT_POLLS must be positive"); break;
+            case CGB200_OPT_GRAD_MID_GEMM: CGB_REQUIRE(value >= 0 && value <= 3, "CGB200_OPT_GRAD_MID_GEMM must be CGB200_AUTO or 0..3"); break;
             default: CGB_REQUIRE(value == 0 || value == 1, "option value must be CGB200_AUTO, 0 or 1"); break;
         }
-        const bool needs_tables = value == 1;
+        const bool needs_tables = value == 1 || (option == CGB200_OPT_GRAD_MID_GEMM && value >= 1);
         bool have = true;
         if (option == CGB200_OPT_TC_FWD) have = p->tc_ok;
         if (option == CGB200_OPT_TC_GRAD_W) have = p->tc_gw_ok && !p->tc_gw_tiles.empty();

@@ -121,7 +121,8 @@ int cgb200_plan_status(const cgb200_plan* plan, int32_t* status);
                                            the batch size, so that the longest block stays a fraction of an SM's share      */
 #define CGB200_OPT_GRAD_MID_GEMM    13  /* input gradient: the mid activation's gradient by a tensor-core GEMM into the
                                            workspace, read back by the input-gradient kernel, instead of rebuilt tile by
-                                           tile on the CUDA cores (tile edge 4, full product)                             */
+                                           tile on the CUDA cores (tile edge 4, full product); 2 / 3: on, with the kernel
+                                           that reads the tiles forced to / kept from running two blocks per SM             */
 #define CGB200_OPT_FWD_KEEP_MID      14  /* forward with a statistics update on the tensor-core path: the statistics kernel
                                            keeps the tiles of the mid activation it generates in the workspace and the
                                            forward kernel reads them back instead of generating them again               */

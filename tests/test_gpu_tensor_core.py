@@ -258,7 +258,7 @@ def test_split_contraction_of_tensor_core_forward(taus, tau_out, B, mode):
 def _input_gradient_gemm(plan, case, bn, gemm):
     from cgnet_b200 import _lib
     dev = torch.device("cuda", 0)
-    with option(plan, _lib.OPT_GRAD_MID_GEMM, 1 if gemm else 0):
+    with option(plan, _lib.OPT_GRAD_MID_GEMM, int(gemm)):   # 0 off, 1 on, 2 / 3 on with two / one block per SM forced
         F = torch.tensor(case["F"], device=dev)
         W = torch.tensor(case["W"], device=dev)
         gO = torch.tensor(case["gO"], device=dev)
@@ -287,6 +287,11 @@ def test_input_gradient_through_mid_gradient_gemm(taus, tau_out, B, mode, bn):
     assert np.array_equal(got, again), "not deterministic"
     assert_fragments_close(got, gF_want, taus, "gF (mid-gradient GEMM) vs oracle")
     assert_fragments_close(got, _input_gradient_gemm(plan, case, bn, gemm=False), taus, "gF (mid-gradient GEMM) vs CUDA-core tiles")
+    # the gather kernel as one block per SM with the whole tile resident, and as two blocks per SM with the tile in chunks
+    for forced in (2, 3):
+        one = _input_gradient_gemm(plan, case, bn, gemm=forced)
+        assert np.array_equal(one, _input_gradient_gemm(plan, case, bn, gemm=forced)), "not deterministic"
+        assert_fragments_close(one, gF_want, taus, f"gF (mid-gradient GEMM, gather variant {forced}) vs oracle")
 
 
 @pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
