@@ -1016,6 +1016,12 @@ void gf_smem(const cgb200_plan* p, size_t* fixed, size_t* per_m) {
     *per_m = (size_t)NHh * 32 * sizeof(float2);
 }
 
+// Shared memory of the input-gradient kernel's gather form (tiles read back from the workspace) with one staging buffer
+// and no staged weights, without the rows of the tile.
+size_t gf_gather_fixed(const cgb200_plan* p) {
+    return (size_t)2 * p->d.tile * p->max_n * 32 * sizeof(float2) + p->gen_band_bytes + (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
+}
+
 // The mid activation's gradient by a tensor-core GEMM into the workspace (gff_tc.cu) instead of tile by tile inside the
 // input-gradient kernel.  Needs the plan's tables (tile edge 4, full product), a whole entry's tile in that kernel's
 // shared memory, and 8 bytes of workspace per sample and element of the (tile-padded) mid activation - at most 16 GB
@@ -1028,7 +1034,9 @@ bool gff_wanted(const cgb200_plan* p, int64_t G) {
     if (opt == 0) return false;
     size_t fixed = 0, per_m = 0;
     gf_smem(p, &fixed, &per_m);
-    if (fixed + (size_t)p->max_n * per_m > kMaxDynSmem) return false;
+    // the kernel that reads the tiles back holds a whole tile, or - with one staging buffer - a third of its rows or more
+    if (fixed + (size_t)p->max_n * per_m > kMaxDynSmem && gf_gather_fixed(p) + (size_t)((p->max_n + 2) / 3) * per_m > kMaxDynSmem)
+        return false;
     if (opt >= 1) return true;
     const double bytes = (double)gff_group_elems(p) * (double)G * 32 * sizeof(float2);
     return p->max_tau_out >= 12 && bytes <= 16.0 * (1ull << 30);
@@ -1432,10 +1440,19 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
             const size_t budget = kMaxDynSmem;   // measured: one block of 16 warps with all m of an entry beats two half-size blocks
             const int Mc = (int)std::min<size_t>(p->max_n, (budget - fixed) / per_m);
             const size_t smem = fixed + (size_t)Mc * per_m;
-            if (ws.gff != nullptr && Mc == p->max_n && T == 4 && !gf_split(p)) {   // H must hold a whole entry's tile
+            if (ws.gff != nullptr && T == 4 && !gf_split(p)) {
                 int Mc_pre = Mc;
                 size_t smem_pre = smem;
                 int nbuf = 2, max_to_pre = max_to;
+                const size_t fixed2 = gf_gather_fixed(p);
+                if (Mc < p->max_n) {
+                    // The whole tile does not fit beside two staging buffers (lmax 15 and more): one staging buffer and
+                    // the tile in chunks, one block per SM.
+                    nbuf = 1;
+                    max_to_pre = 0;
+                    Mc_pre = (int)std::min<size_t>(p->max_n, (kMaxDynSmem - fixed2) / per_m);
+                    smem_pre = fixed2 + (size_t)Mc_pre * per_m;
+                }
                 // Two blocks per SM (the gather variant needs 64 registers per thread, so shared memory decides): one
                 // staging buffer instead of two, no staged weights, and the tile in chunks of as many rows as half an
                 // SM's shared memory leaves.  The SM's other block computes while a block waits for its copies, which
@@ -1445,14 +1462,14 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 // CGB200_OPT_GRAD_MID_GEMM 2 / 3 force it on / off.
                 {
                     const size_t limit = (kSmemPerSM - 2 * 1024) / 2;   // two blocks, 1 KB reserved for each
-                    const size_t fixed2 = (size_t)2 * T * p->max_n * 32 * sizeof(float2) + p->gen_band_bytes +
-                                          (size_t)((kGfWarps * 4 * p->max_n + 15) & ~15);
                     const int mode = p->opt[CGB200_OPT_GRAD_MID_GEMM];
                     const bool fits = fixed2 + 4 * per_m <= limit;
-                    if (fits && mode != 3 && (mode == 2 || (int64_t)nblk * G >= 2 * (int64_t)p->num_sms)) {
+                    const int Mc2 = fits ? (int)std::min<size_t>(p->max_n, (limit - fixed2) / per_m) : 0;
+                    const bool pays = 3 * Mc2 >= p->max_n && (int64_t)nblk * G >= 2 * (int64_t)p->num_sms;   // at most three chunks
+                    if (fits && mode != 3 && (mode == 2 || pays)) {
                         nbuf = 1;
                         max_to_pre = 0;
-                        Mc_pre = (int)std::min<size_t>(p->max_n, (limit - fixed2) / per_m);
+                        Mc_pre = Mc2;
                         smem_pre = fixed2 + (size_t)Mc_pre * per_m;
                     }
                 }
@@ -1460,7 +1477,7 @@ int cgb200_layer_bwd(const cgb200_plan* p, const float* F, const float* W, const
                 if (rc2) return rc2;
                 auto kern = last_rep > 1 ? fused_gf_kernel<4, false, false, true, true> : fused_gf_kernel<4, false, false, true, false>;
                 if (smem_pre > 48 * 1024) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pre));
-                if (nbuf == 1) CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+                CGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
                 launch_begin(K_GF, st);
                 kern<<<(unsigned)((int64_t)nblk * G), kGfWarps * kWarp, smem_pre, st>>>(
                     p->d, p->d_gf_info, p->d_gf_begin, p->d_gf2_blocks[lv], p->d_gf_owner, ws.SF, ws.SG, (const float2*)W, ws.inv, gf_out,

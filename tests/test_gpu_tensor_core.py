@@ -272,12 +272,14 @@ def _input_gradient_gemm(plan, case, bn, gemm):
 @pytest.mark.parametrize("taus,tau_out,B,mode", [([8] * 4, [16] * 4, 40, "default"), ([16] * 6, [16] * 6, 33, "default"),
                                                  ([8] * 11, [32] * 11, 20, "default"), ([8, 4, 12, 8], [6, 9, 16, 3], 7, "default"),
                                                  ([8] * 8, [12] * 8, 64, "mst"), ([8] * 3, [64] * 3, 3, "default"),
-                                                 ([6, 0, 8, 4], [8, 4, 0, 20], 4, "default")])
+                                                 ([6, 0, 8, 4], [8, 4, 0, 20], 4, "default"),
+                                                 ([4] * 16, [12] * 16, 3, "mst"), ([4] * 21, [12] * 21, 2, "mst")])
 def test_input_gradient_through_mid_gradient_gemm(taus, tau_out, B, mode, bn):
     """The input gradient whose first phase is a tensor-core GEMM into the workspace (the gradient of the mid activation,
     every tile once, in the layout the gather kernel keeps it in shared memory) against the oracle and against the kernel
     that rebuilds the tiles on the CUDA cores; ragged channel counts, empty fragments on both sides, every group size of
-    the GEMM (4, 2 and 1 cells per group at 16, 32 and 64 output channels)."""
+    the GEMM (4, 2 and 1 cells per group at 16, 32 and 64 output channels); lmax 15 and 20, where the gather kernel cannot
+    hold a whole tile beside two staging buffers and reads it in chunks."""
     from cgnet_b200 import get_plan
     case = make_case(taus, tau_out, B, mode, seed=61)
     plan = get_plan(case["lmax"], taus, tau_out, case["llls"], torch.device("cuda", 0), tile=4)
