@@ -641,7 +641,9 @@ __device__ __forceinline__ void gf_h_unit(const float2* __restrict__ go, const f
 }
 
 // PRE: the gFF tiles were computed beforehand by the tensor-core GEMM (gff_tc.cu) and sit in the workspace `gff` in the
-// layout of H; phase 1 is then an asynchronous copy of the entry's tile (the launch makes H hold a whole entry).
+// layout of H; phase 1 is then an asynchronous copy of the entry's tile - whole, with the next entry's staging under way
+// (`nbuf` 2), or in chunks of Mc rows with one staging buffer (`nbuf` 1), which lets two blocks share an SM or a tile be
+// larger than the buffer.
 //
 // SHORTG (with `last_rep` > 1): the last sample group holds at most 32 / last_rep samples.  In that group a lane is a
 // (row offset j, sample s) pair, s = lane % (32 / last_rep): a phase-1 unit covers last_rep rows m of the tile and a
@@ -1023,9 +1025,9 @@ size_t gf_gather_fixed(const cgb200_plan* p) {
 }
 
 // The mid activation's gradient by a tensor-core GEMM into the workspace (gff_tc.cu) instead of tile by tile inside the
-// input-gradient kernel.  Needs the plan's tables (tile edge 4, full product), a whole entry's tile in that kernel's
-// shared memory, and 8 bytes of workspace per sample and element of the (tile-padded) mid activation - at most 16 GB
-// by default.  On from 12 output channels (measured on B200, backward of one layer: lmax 14 with 16 channels and 64
+// input-gradient kernel.  Needs the plan's tables (tile edge 4, full product), at least a third of an entry's tile in that
+// kernel's shared memory, and 8 bytes of workspace per sample and element of the (tile-padded) mid activation - at most
+// 16 GB by default.  On from 12 output channels (measured on B200, backward of one layer: lmax 14 with 16 channels and 64
 // samples 4.84 -> 3.41 ms, lmax 10 with 32 channels 8.06 -> 3.92 ms, lmax 10 with 16 channels 1.51 -> 1.10 ms; the GEMM
 // writes its output at 5.1 TB/s); CGB200_OPT_GRAD_MID_GEMM overrides.
 bool gff_wanted(const cgb200_plan* p, int64_t G) {
